@@ -1,0 +1,237 @@
+/*
+ * tops_b200 — C ABI of the B200 (sm_100a) gated-linear-attention kernels.
+ *
+ * The reference (`tops`, a pure-Python JAX package) has no native interface:
+ * its boundary for this path is the Python signature of each op.  Every entry
+ * point below therefore names the reference function it replaces; the Python
+ * package `tops_b200` keeps those signatures and calls these symbols through
+ * ctypes (and, where JAX is installed, through a `jax.ffi` shim).
+ *
+ * Conventions
+ *  - All tensors are dense row-major.  Activations are `[B, T, H, D]`
+ *    (time-major, head-minor), states are `[N, H, K, V]` fp32, chunk states
+ *    are `[B, NT, H, K, V]` with NT = ceil(T / chunk).
+ *  - Pointers are device pointers owned by the caller.  Nothing is allocated,
+ *    freed or synchronised here; all work is enqueued on `stream`.
+ *  - `workspace` is caller-provided scratch of at least
+ *    `*_workspace_bytes(params)` bytes, 256-byte aligned.
+ *  - Return value: 0 on success, a negative `TOPS_E_*` code otherwise
+ *    (`tops_b200_strerror` gives the text).  No entry point aborts or traps.
+ *  - Optional pointers may be NULL where the comment says so.
+ */
+#ifndef TOPS_B200_H_
+#define TOPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TOPS_OK = 0,
+  TOPS_E_BAD_SHAPE = -1,   /* a dimension is outside what the kernels accept */
+  TOPS_E_BAD_DTYPE = -2,
+  TOPS_E_NULL = -3,        /* a required pointer is NULL */
+  TOPS_E_WORKSPACE = -4,   /* workspace missing or too small */
+  TOPS_E_CUDA = -5,        /* a CUDA runtime / driver call failed */
+  TOPS_E_UNSUPPORTED = -6, /* valid request that no kernel covers */
+  TOPS_E_ALIGN = -7        /* a pointer is not 16-byte aligned */
+};
+
+enum { TOPS_F32 = 0, TOPS_BF16 = 1, TOPS_F16 = 2 };
+
+/* Which gate drives the recurrence. */
+enum {
+  TOPS_GATE_NONE = 0,
+  TOPS_GATE_PER_CHANNEL = 1, /* GLA: g is [B,T,H,K]            */
+  TOPS_GATE_SCALAR = 2,      /* simple_gla: g is [B,T,H]       */
+  TOPS_GATE_GAMMA = 3        /* simple_gla: constant g_gamma[H] */
+};
+
+/* Kernel selection.  AUTO picks the tcgen05 path when the shape allows it. */
+enum { TOPS_IMPL_AUTO = 0, TOPS_IMPL_GENERIC = 1, TOPS_IMPL_SM100 = 2 };
+
+const char* tops_b200_strerror(int code);
+/* Number of kernels launched by this library since load (all entry points). */
+int64_t tops_b200_launch_count(void);
+
+/* Per-kernel device timing (no counterpart behind the reference's op API; its
+ * benchmarks wrap timed loops in jax.profiler traces, `benchmarks/utils.py:71-83`).
+ * While enabled, every kernel this library launches is bracketed by a CUDA event
+ * pair on its stream.  `tops_b200_profile_read` waits for the recorded events,
+ * writes one line per kernel label — "<label> <launches> <total_ms>\n" — into
+ * `buf` (NUL-terminated, truncated to `cap`), and clears the records. */
+int tops_b200_profile_enable(int on);
+int tops_b200_profile_read(char* buf, size_t cap);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_local_cumsum — replaces `tops/cpu/ops/common/chunk_o.py:18-112`
+ * (accelerator: `tops/ops/common/cumsum.py:472-540`).
+ * Inclusive (or, reversed, suffix) sum of `g` inside each chunk along T.
+ * `D` is K for per-channel gates, 1 for scalar gates.  Output is fp32.
+ * cu_seqlens (device int32 [N+1], B must be 1) restarts chunks per sequence.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, D, chunk;
+  int32_t dtype;   /* dtype of g */
+  int32_t reverse; /* 0 prefix sums, 1 suffix sums */
+  const void* g;
+  float* out;
+  const int32_t* cu_seqlens; /* NULL: dense batch */
+  int32_t N;                 /* number of sequences when cu_seqlens != NULL */
+} tops_cumsum_params;
+int tops_b200_chunk_local_cumsum(const tops_cumsum_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Problem description shared by the chunked GLA / simple_gla entry points.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V, chunk;
+  int32_t dtype;      /* dtype of q, k, v, o, do, dv */
+  int32_t gate_dtype; /* dtype of g */
+  int32_t gate_kind;  /* TOPS_GATE_* */
+  int32_t impl;       /* TOPS_IMPL_* */
+  float scale;
+  const int32_t* cu_seqlens; /* device int32 [N+1] or NULL */
+  const int32_t* cu_seqlens_host; /* the same values in host memory (needed when cu_seqlens != NULL) */
+  int32_t N;                 /* sequences when packed; else ignored (N = B) */
+} tops_chunk_problem;
+
+/* ------------------------------------------------------------------------ *
+ * chunk_fwd_h — replaces `tops/cpu/ops/common/chunk_h.py:31-226`
+ * (accelerator `tops/ops/common/chunk_h.py:100-272`): chunk-start states of
+ * h <- h*exp(g_last) + k~^T v.  `g_cumsum` is the chunk-local cumsum (fp32),
+ * `[B,T,H,K]`, `[B,T,H]` or, for TOPS_GATE_GAMMA, the raw `g_gamma[H]`.
+ * h is written as `[B,NT,H,K,V]` in `h_dtype` (TOPS_F32 or the input dtype).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  tops_chunk_problem pb;
+  const void *k, *v;
+  const float* g_cumsum;
+  const float* h0; /* [N,H,K,V] or NULL */
+  void* h;         /* [B,NT,H,K,V] or NULL (only ht wanted) */
+  int32_t h_dtype;
+  float* ht;       /* [N,H,K,V] or NULL */
+} tops_fwd_h_params;
+int tops_b200_chunk_fwd_h(const tops_fwd_h_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_bwd_dh — replaces `tops/cpu/ops/common/chunk_h.py:229-427`
+ * (accelerator `tops/ops/common/chunk_h.py:781-884`): reverse scan
+ * dh <- dh*exp(g_last) + (q*scale*exp(g))^T do, seeded by dht.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  tops_chunk_problem pb;
+  const void *q, *do_;
+  const float* g_cumsum;
+  const float* dht; /* [N,H,K,V] or NULL */
+  float* dh;        /* [B,NT,H,K,V] fp32 or NULL */
+  float* dh0;       /* [N,H,K,V] or NULL */
+} tops_bwd_dh_params;
+int tops_b200_chunk_bwd_dh(const tops_bwd_dh_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_gla_fwd / chunk_simple_gla_fwd — replace
+ * `tops/cpu/ops/gla/chunk.py:159-269` (public `chunk_gla` :648-709,
+ * `fused_chunk_gla` `tops/cpu/ops/gla/fused_chunk.py:4-44`) and
+ * `tops/cpu/ops/simple_gla/chunk.py:53-129` (public :796-889):
+ * cumsum, state scan, masked intra-chunk product and output combine.
+ * Optional outputs (NULL to skip): g_cumsum fp32 (shape of g), A fp32
+ * `[B,T,H,chunk]`, h `[B,NT,H,K,V]` in the input dtype, ht fp32.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  tops_chunk_problem pb;
+  const void *q, *k, *v;
+  const void* g;   /* raw log-gates: [B,T,H,K] / [B,T,H] / g_gamma[H] fp32 / NULL */
+  const float* h0; /* [N,H,K,V] or NULL */
+  void* o;         /* [B,T,H,V] input dtype */
+  float* ht;       /* NULL unless the final state is wanted */
+  float* g_cumsum_out;
+  float* A_out;
+  void* h_out;
+} tops_chunk_fwd_params;
+size_t tops_b200_chunk_fwd_workspace_bytes(const tops_chunk_fwd_params* p);
+int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_gla_bwd / chunk_simple_gla_bwd — replace
+ * `tops/cpu/ops/gla/chunk.py:469-640` and
+ * `tops/cpu/ops/simple_gla/chunk.py:668-788`: recompute cumsum, states and
+ * the intra matrix, reverse-scan dh, then dq, dk, dv, dg (and dh0 when h0 is
+ * given).  Output dtypes: `grad_dtype` for dq/dk (TOPS_F32 for GLA as in the
+ * reference, the input dtype for simple_gla), dv in the input dtype, dg fp32
+ * (`[B,T,H,K]` per-channel, `[B,T,H]` scalar; NULL for GAMMA/NONE).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  tops_chunk_problem pb;
+  const void *q, *k, *v;
+  const void* g;
+  const float* h0;
+  const void* do_;
+  const float* dht; /* NULL: zero */
+  void *dq, *dk;
+  int32_t grad_dtype;
+  void* dv;
+  float* dg;
+  float* dh0; /* NULL unless h0 given and wanted */
+} tops_chunk_bwd_params;
+size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);
+int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * fused_recurrent_gla forward — replaces
+ * `tops/cpu/ops/gla/fused_recurrent.py:51-162` (public :362-422): token-serial
+ * h*=exp(gk); h*=exp(gv); h+=k(x)v; o=scale*q^T h.  `state_in` may equal
+ * `state_out` (in-place decode).  o is written in `o_dtype`.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V;
+  int32_t dtype;      /* q, k, v */
+  int32_t gate_dtype; /* gk, gv */
+  int32_t o_dtype;
+  int32_t reverse;
+  float scale;
+  const void *q, *k, *v;
+  const void* gk; /* [B,T,H,K] or NULL */
+  const void* gv; /* [B,T,H,V] or NULL */
+  const float* state_in; /* [N,H,K,V] or NULL (zero) */
+  float* state_out;      /* [N,H,K,V] or NULL */
+  void* o;
+  const int32_t* cu_seqlens;
+  int32_t N;
+} tops_recurrent_fwd_params;
+int tops_b200_fused_recurrent_gla_fwd(const tops_recurrent_fwd_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * fused_recurrent_gla backward — replaces
+ * `tops/cpu/ops/gla/fused_recurrent.py:171-353`.  Two passes over time.
+ * workspace: see tops_b200_fused_recurrent_gla_bwd_workspace_bytes.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V;
+  int32_t dtype, gate_dtype;
+  int32_t reverse;
+  float scale;
+  const void *q, *k, *v, *gk, *gv;
+  const float* o; /* fp32 forward output; required with gv */
+  const void* do_;
+  const float* h0;
+  const float* dht;
+  void *dq, *dk, *dv; /* input dtype */
+  void *dgk, *dgv;    /* gate dtype, NULL when the gate is absent */
+  float* dh0;         /* NULL unless h0 given */
+  const int32_t* cu_seqlens;
+  int32_t N;
+} tops_recurrent_bwd_params;
+size_t tops_b200_fused_recurrent_gla_bwd_workspace_bytes(const tops_recurrent_bwd_params* p);
+int tops_b200_fused_recurrent_gla_bwd(const tops_recurrent_bwd_params* p, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TOPS_B200_H_ */

@@ -1,0 +1,15 @@
+// Host-side interface of the tcgen05 / TMA (sm_100a) chunked GLA kernels.
+#pragma once
+#include "common.cuh"
+
+namespace tops {
+namespace sm100 {
+// True when the tcgen05 kernels take this problem (bf16, K = V = 128, chunk 64,
+// whole chunks, dense batch, per-channel gates).
+bool supported(const tops_chunk_problem& pb);
+size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p);
+int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p);
+int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+}  // namespace sm100
+}  // namespace tops

@@ -1,0 +1,358 @@
+// extern "C" entry points: validation, workspace carving, kernel selection.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "gla_generic.cuh"
+#include "gla_sm100.cuh"
+#include "recurrent.cuh"
+
+namespace tops {
+static std::atomic<int64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+struct ProfRecord { const char* label; cudaEvent_t start, stop; };
+std::atomic<int> g_prof_on{0};
+std::mutex g_prof_mu;
+std::vector<ProfRecord> g_prof;
+constexpr size_t kMaxProfRecords = 1 << 16;
+}  // namespace
+
+KernelScope::KernelScope(const char* label, cudaStream_t s) : slot(-1), st(s) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof.size() >= kMaxProfRecords) return;
+  ProfRecord r{label, nullptr, nullptr};
+  if (cudaEventCreate(&r.start) != cudaSuccess || cudaEventCreate(&r.stop) != cudaSuccess) return;
+  cudaEventRecord(r.start, st);
+  g_prof.push_back(r);
+  slot = (int)g_prof.size() - 1;
+}
+KernelScope::~KernelScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  cudaEventRecord(g_prof[slot].stop, st);
+}
+
+namespace {
+
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(reinterpret_cast<char*>(p)) {}
+  template <class T> T* take(size_t count) {
+    T* r = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += align_up(count * sizeof(T));
+    return r;
+  }
+};
+
+bool valid_dtype(int dt) { return dt == TOPS_F32 || dt == TOPS_BF16 || dt == TOPS_F16; }
+
+int check_problem(const tops_chunk_problem& pb) {
+  if (pb.B < 1 || pb.T < 1 || pb.H < 1 || pb.K < 1 || pb.V < 1) return TOPS_E_BAD_SHAPE;
+  if (pb.chunk != 16 && pb.chunk != 32 && pb.chunk != 64) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(pb.dtype) || !valid_dtype(pb.gate_dtype)) return TOPS_E_BAD_DTYPE;
+  if (pb.gate_kind < TOPS_GATE_NONE || pb.gate_kind > TOPS_GATE_GAMMA) return TOPS_E_BAD_SHAPE;
+  if (pb.gate_kind == TOPS_GATE_GAMMA && pb.gate_dtype != TOPS_F32) return TOPS_E_BAD_DTYPE;
+  if (pb.cu_seqlens) {
+    if (pb.B != 1 || pb.N < 1 || pb.cu_seqlens_host == nullptr) return TOPS_E_BAD_SHAPE;
+    if (pb.cu_seqlens_host[0] != 0 || pb.cu_seqlens_host[pb.N] != pb.T) return TOPS_E_BAD_SHAPE;
+    for (int n = 0; n < pb.N; ++n)
+      if (pb.cu_seqlens_host[n + 1] <= pb.cu_seqlens_host[n]) return TOPS_E_BAD_SHAPE;
+  }
+  return TOPS_OK;
+}
+
+int count_chunks(const tops_chunk_problem& pb) {
+  if (!pb.cu_seqlens) return pb.B * cdiv(pb.T, pb.chunk);
+  int tot = 0;
+  for (int n = 0; n < pb.N; ++n) tot += cdiv(pb.cu_seqlens_host[n + 1] - pb.cu_seqlens_host[n], pb.chunk);
+  return tot;
+}
+
+size_t gate_elems(const tops_chunk_problem& pb) {
+  size_t tok = (size_t)pb.B * pb.T * pb.H;
+  if (pb.gate_kind == TOPS_GATE_PER_CHANNEL) return tok * pb.K;
+  if (pb.gate_kind == TOPS_GATE_SCALAR) return tok;
+  return 0;
+}
+
+// Fills Problem (minus gcum) and the packed-batch tables carved from `cv`.
+int make_problem(const tops_chunk_problem& in, Carver& cv, cudaStream_t st, Problem* out, bool launch) {
+  Problem pb{};
+  pb.H = in.H; pb.K = in.K; pb.V = in.V; pb.dtype = in.dtype; pb.gate_kind = in.gate_kind; pb.scale = in.scale;
+  pb.total_chunks = count_chunks(in);
+  pb.m.T = in.T; pb.m.C = in.chunk;
+  if (in.cu_seqlens) {
+    int32_t* cs = cv.take<int32_t>(in.N + 1);
+    int32_t* chunk_seq = cv.take<int32_t>(pb.total_chunks);
+    pb.m.cu = in.cu_seqlens; pb.m.cs = cs; pb.m.chunk_seq = chunk_seq; pb.m.N = in.N; pb.m.NT = pb.total_chunks;
+    if (launch) {
+      int rc = generic::launch_prepare_chunks(in.cu_seqlens, in.N, in.chunk, cs, chunk_seq, st);
+      if (rc) return rc;
+    }
+  } else {
+    pb.m.cu = nullptr; pb.m.cs = nullptr; pb.m.chunk_seq = nullptr; pb.m.N = in.B; pb.m.NT = cdiv(in.T, in.chunk);
+  }
+  *out = pb;
+  return TOPS_OK;
+}
+
+size_t state_elems(const tops_chunk_problem& pb) {
+  return (size_t)count_chunks(pb) * pb.H * pb.K * pb.V;
+}
+
+bool use_sm100(const tops_chunk_problem& pb) {
+  if (pb.impl == TOPS_IMPL_GENERIC) return false;
+  return sm100::supported(pb);
+}
+
+}  // namespace
+}  // namespace tops
+
+using namespace tops;
+
+extern "C" const char* tops_b200_strerror(int code) {
+  switch (code) {
+    case TOPS_OK: return "ok";
+    case TOPS_E_BAD_SHAPE: return "bad shape or unsupported dimension";
+    case TOPS_E_BAD_DTYPE: return "bad dtype";
+    case TOPS_E_NULL: return "required pointer is NULL";
+    case TOPS_E_WORKSPACE: return "workspace missing or too small";
+    case TOPS_E_CUDA: return "CUDA call failed";
+    case TOPS_E_UNSUPPORTED: return "no kernel covers this request";
+    case TOPS_E_ALIGN: return "pointer is not 16-byte aligned";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int64_t tops_b200_launch_count(void) { return g_launches.load(); }
+
+extern "C" int tops_b200_profile_enable(int on) {
+  g_prof_on.store(on ? 1 : 0);
+  return TOPS_OK;
+}
+
+extern "C" int tops_b200_profile_read(char* buf, size_t cap) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  std::map<std::string, std::pair<int, double>> agg;
+  int rc = TOPS_OK;
+  for (auto& r : g_prof) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.stop) != cudaSuccess || cudaEventElapsedTime(&ms, r.start, r.stop) != cudaSuccess)
+      rc = TOPS_E_CUDA;
+    auto& a = agg[r.label];
+    a.first += 1;
+    a.second += ms;
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  g_prof.clear();
+  size_t off = 0;
+  if (buf && cap) buf[0] = 0;
+  for (auto& kv : agg) {
+    char line[256];
+    int n = snprintf(line, sizeof line, "%s %d %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    if (buf && off + n + 1 <= cap) { memcpy(buf + off, line, n + 1); off += n; }
+  }
+  return rc;
+}
+
+extern "C" int tops_b200_chunk_local_cumsum(const tops_cumsum_params* p, void* stream) {
+  if (!p || !p->g || !p->out) return TOPS_E_NULL;
+  tops_chunk_problem in{};
+  in.B = p->B; in.T = p->T; in.H = p->H; in.K = p->D; in.V = 1; in.chunk = p->chunk;
+  in.dtype = p->dtype; in.gate_dtype = p->dtype; in.gate_kind = TOPS_GATE_NONE;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->D < 1) return TOPS_E_BAD_SHAPE;
+  if (p->chunk < 1 || (p->chunk & (p->chunk - 1))) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
+  if (p->cu_seqlens) return TOPS_E_UNSUPPORTED;  // packed cumsum goes through the chunked entry points
+  SeqMap m{};
+  m.N = p->B; m.T = p->T; m.C = p->chunk; m.NT = cdiv(p->T, p->chunk);
+  return generic::launch_cumsum(m, p->H, p->D, p->dtype, p->reverse, p->g, p->out, p->B * m.NT,
+                                (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_chunk_fwd_h(const tops_fwd_h_params* p, void* stream) {
+  if (!p || !p->k || !p->v) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  if (p->pb.cu_seqlens) return TOPS_E_UNSUPPORTED;
+  if (p->pb.gate_kind != TOPS_GATE_NONE && !p->g_cumsum) return TOPS_E_NULL;
+  if (p->h && p->h_dtype != TOPS_F32 && p->h_dtype != p->pb.dtype) return TOPS_E_BAD_DTYPE;
+  Carver cv(nullptr);
+  Problem pb;
+  if ((rc = make_problem(p->pb, cv, (cudaStream_t)stream, &pb, true))) return rc;
+  pb.gcum = p->g_cumsum;
+  return generic::launch_scan(pb, false, p->k, p->v, p->h0, p->h, p->h_dtype == TOPS_F32, p->ht,
+                              (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_chunk_bwd_dh(const tops_bwd_dh_params* p, void* stream) {
+  if (!p || !p->q || !p->do_) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  if (p->pb.cu_seqlens) return TOPS_E_UNSUPPORTED;
+  if (p->pb.gate_kind != TOPS_GATE_NONE && !p->g_cumsum) return TOPS_E_NULL;
+  Carver cv(nullptr);
+  Problem pb;
+  if ((rc = make_problem(p->pb, cv, (cudaStream_t)stream, &pb, true))) return rc;
+  pb.gcum = p->g_cumsum;
+  return generic::launch_scan(pb, true, p->q, p->do_, p->dht, p->dh, 1, p->dh0, (cudaStream_t)stream);
+}
+
+// ---- forward ----------------------------------------------------------------
+static size_t fwd_layout(const tops_chunk_fwd_params* p, void* ws, cudaStream_t st, bool launch, Problem* pb,
+                         float** gcum, void** h, int* rc_out) {
+  Carver cv(ws);
+  int rc = make_problem(p->pb, cv, st, pb, launch);
+  if (rc_out) *rc_out = rc;
+  size_t ge = gate_elems(p->pb);
+  float* g = (p->g_cumsum_out || ge == 0) ? p->g_cumsum_out : cv.take<float>(ge);
+  if (p->g_cumsum_out == nullptr && ge != 0 && ws == nullptr) g = nullptr;
+  char* hh = p->h_out ? reinterpret_cast<char*>(p->h_out)
+                      : reinterpret_cast<char*>(cv.take<char>(state_elems(p->pb) * dtype_size(p->pb.dtype)));
+  if (gcum) *gcum = g;
+  if (h) *h = hh;
+  return cv.off;
+}
+
+extern "C" size_t tops_b200_chunk_fwd_workspace_bytes(const tops_chunk_fwd_params* p) {
+  if (!p || check_problem(p->pb)) return 0;
+  if (use_sm100(p->pb)) return sm100::fwd_workspace_bytes(*p);
+  Problem pb;
+  return fwd_layout(p, nullptr, nullptr, false, &pb, nullptr, nullptr, nullptr) + 256;
+}
+
+extern "C" int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->o) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  if (p->pb.gate_kind != TOPS_GATE_NONE && !p->g) return TOPS_E_NULL;
+  if (p->pb.impl == TOPS_IMPL_SM100 && !sm100::supported(p->pb)) return TOPS_E_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tops_b200_chunk_fwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (use_sm100(p->pb)) return sm100::chunk_fwd(*p, workspace, workspace_bytes, st);
+
+  Problem pb;
+  float* gcum = nullptr;
+  void* h = nullptr;
+  fwd_layout(p, workspace, st, true, &pb, &gcum, &h, &rc);
+  if (rc) return rc;
+  if (p->pb.gate_kind == TOPS_GATE_PER_CHANNEL || p->pb.gate_kind == TOPS_GATE_SCALAR) {
+    int D = p->pb.gate_kind == TOPS_GATE_PER_CHANNEL ? p->pb.K : 1;
+    if ((rc = generic::launch_cumsum(pb.m, pb.H, D, p->pb.gate_dtype, 0, p->g, gcum, pb.total_chunks, st))) return rc;
+    pb.gcum = gcum;
+  } else if (p->pb.gate_kind == TOPS_GATE_GAMMA) {
+    pb.gcum = reinterpret_cast<const float*>(p->g);
+  }
+  if ((rc = generic::launch_scan(pb, false, p->k, p->v, p->h0, h, 0, p->ht, st))) return rc;
+  int round_A = p->pb.gate_kind == TOPS_GATE_PER_CHANNEL || p->pb.gate_kind == TOPS_GATE_NONE;
+  return generic::launch_fwd_o(pb, p->q, p->k, p->v, h, 0, p->o, p->A_out, round_A, st);
+}
+
+// ---- backward ---------------------------------------------------------------
+struct BwdLayout {
+  float *gcum, *h, *dh, *A, *dA, *dg_part;
+  size_t dg_stride;
+  int tilesK;
+};
+
+static size_t bwd_layout(const tops_chunk_bwd_params* p, void* ws, cudaStream_t st, bool launch, Problem* pb,
+                         BwdLayout* L, int* rc_out) {
+  Carver cv(ws);
+  int rc = make_problem(p->pb, cv, st, pb, launch);
+  if (rc_out) *rc_out = rc;
+  BwdLayout l{};
+  size_t ge = gate_elems(p->pb);
+  l.gcum = ge ? cv.take<float>(ge) : nullptr;
+  size_t se = state_elems(p->pb);
+  l.h = cv.take<float>(se);
+  l.dh = cv.take<float>(se);
+  size_t ae = (size_t)pb->total_chunks * p->pb.H * p->pb.chunk * p->pb.chunk;
+  l.A = cv.take<float>(ae);
+  l.dA = cv.take<float>(ae);
+  l.tilesK = cdiv(p->pb.K, 64);
+  l.dg_stride = (size_t)p->pb.B * p->pb.T * p->pb.H;
+  l.dg_part = p->pb.gate_kind == TOPS_GATE_SCALAR ? cv.take<float>(l.dg_stride * l.tilesK) : nullptr;
+  if (L) *L = l;
+  return cv.off;
+}
+
+extern "C" size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p) {
+  if (!p || check_problem(p->pb)) return 0;
+  if (use_sm100(p->pb)) return sm100::bwd_workspace_bytes(*p);
+  Problem pb;
+  return bwd_layout(p, nullptr, nullptr, false, &pb, nullptr, nullptr) + 256;
+}
+
+extern "C" int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->do_ || !p->dq || !p->dk || !p->dv) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  if (p->pb.gate_kind != TOPS_GATE_NONE && !p->g) return TOPS_E_NULL;
+  if (!valid_dtype(p->grad_dtype)) return TOPS_E_BAD_DTYPE;
+  if (p->pb.impl == TOPS_IMPL_SM100 && !sm100::supported(p->pb)) return TOPS_E_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tops_b200_chunk_bwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (use_sm100(p->pb)) return sm100::chunk_bwd(*p, workspace, workspace_bytes, st);
+
+  Problem pb;
+  BwdLayout L;
+  bwd_layout(p, workspace, st, true, &pb, &L, &rc);
+  if (rc) return rc;
+  const int kind = p->pb.gate_kind;
+  if (kind == TOPS_GATE_PER_CHANNEL || kind == TOPS_GATE_SCALAR) {
+    int D = kind == TOPS_GATE_PER_CHANNEL ? p->pb.K : 1;
+    if ((rc = generic::launch_cumsum(pb.m, pb.H, D, p->pb.gate_dtype, 0, p->g, L.gcum, pb.total_chunks, st))) return rc;
+    pb.gcum = L.gcum;
+  } else if (kind == TOPS_GATE_GAMMA) {
+    pb.gcum = reinterpret_cast<const float*>(p->g);
+  }
+  if ((rc = generic::launch_scan(pb, false, p->k, p->v, p->h0, L.h, 1, nullptr, st))) return rc;
+  if ((rc = generic::launch_scan(pb, true, p->q, p->do_, p->dht, L.dh, 1, p->dh0, st))) return rc;
+  BwdBuffers b{};
+  b.q = p->q; b.k = p->k; b.v = p->v; b.do_ = p->do_; b.A = L.A; b.dA = L.dA; b.h = L.h; b.dh = L.dh;
+  b.dq = p->dq; b.dk = p->dk; b.dv = p->dv; b.grad_dtype = p->grad_dtype;
+  b.dg_stage = nullptr; b.dg_tile_stride = 0;
+  if (p->dg && kind == TOPS_GATE_PER_CHANNEL) b.dg_stage = p->dg;
+  if (p->dg && kind == TOPS_GATE_SCALAR) { b.dg_stage = L.dg_part; b.dg_tile_stride = L.dg_stride; }
+  if ((rc = generic::launch_bwd(pb, b, st))) return rc;
+  if (p->dg && kind == TOPS_GATE_SCALAR)
+    return generic::launch_sum_partials(L.dg_part, L.dg_stride, L.tilesK, p->dg, L.dg_stride, st);
+  return TOPS_OK;
+}
+
+// ---- recurrent --------------------------------------------------------------
+extern "C" int tops_b200_fused_recurrent_gla_fwd(const tops_recurrent_fwd_params* p, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->o) return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype) || !valid_dtype(p->o_dtype)) return TOPS_E_BAD_DTYPE;
+  if (p->cu_seqlens && (p->B != 1 || p->N < 1)) return TOPS_E_BAD_SHAPE;
+  return recurrent::fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" size_t tops_b200_fused_recurrent_gla_bwd_workspace_bytes(const tops_recurrent_bwd_params* p) {
+  if (!p) return 0;
+  return recurrent::bwd_workspace_bytes(*p);
+}
+
+extern "C" int tops_b200_fused_recurrent_gla_bwd(const tops_recurrent_bwd_params* p, void* workspace,
+                                                 size_t workspace_bytes, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->do_ || !p->dq || !p->dk || !p->dv) return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
+  if (p->gv && !p->o) return TOPS_E_NULL;
+  if (p->cu_seqlens && (p->B != 1 || p->N < 1)) return TOPS_E_BAD_SHAPE;
+  if (!workspace || workspace_bytes < recurrent::bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
+  return recurrent::bwd(*p, workspace, (cudaStream_t)stream);
+}

@@ -1,0 +1,134 @@
+"""ctypes binding of libtops_b200.so (the C ABI declared in include/tops_b200.h).
+
+There is no fallback: importing this module fails when the shared library has
+not been built, and every op raises when the library reports an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PATH = os.path.join(_HERE, "libtops_b200.so")
+if not os.path.exists(_PATH):
+    raise ImportError(
+        f"{_PATH} is missing: build it with `python pallas-kernel_b200/build.py` "
+        "(tops_b200 has no CPU or eager fallback)")
+lib = C.CDLL(_PATH)
+
+F32, BF16, F16 = 0, 1, 2
+GATE_NONE, GATE_PER_CHANNEL, GATE_SCALAR, GATE_GAMMA = 0, 1, 2, 3
+IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+_i32, _f32, _vp, _sz = C.c_int32, C.c_float, C.c_void_p, C.c_size_t
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    assert dt in _DT, f"unsupported dtype {dt} (fp32, bf16, fp16 only)"
+    return _DT[dt]
+
+
+class CumsumParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("D", _i32), ("chunk", _i32), ("dtype", _i32),
+                ("reverse", _i32), ("g", _vp), ("out", _vp), ("cu_seqlens", _vp), ("N", _i32)]
+
+
+class ChunkProblem(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("chunk", _i32),
+                ("dtype", _i32), ("gate_dtype", _i32), ("gate_kind", _i32), ("impl", _i32),
+                ("scale", _f32), ("cu_seqlens", _vp), ("cu_seqlens_host", _vp), ("N", _i32)]
+
+
+class FwdHParams(C.Structure):
+    _fields_ = [("pb", ChunkProblem), ("k", _vp), ("v", _vp), ("g_cumsum", _vp), ("h0", _vp), ("h", _vp),
+                ("h_dtype", _i32), ("ht", _vp)]
+
+
+class BwdDhParams(C.Structure):
+    _fields_ = [("pb", ChunkProblem), ("q", _vp), ("do_", _vp), ("g_cumsum", _vp), ("dht", _vp), ("dh", _vp),
+                ("dh0", _vp)]
+
+
+class ChunkFwdParams(C.Structure):
+    _fields_ = [("pb", ChunkProblem), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("h0", _vp), ("o", _vp),
+                ("ht", _vp), ("g_cumsum_out", _vp), ("A_out", _vp), ("h_out", _vp)]
+
+
+class ChunkBwdParams(C.Structure):
+    _fields_ = [("pb", ChunkProblem), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("h0", _vp), ("do_", _vp),
+                ("dht", _vp), ("dq", _vp), ("dk", _vp), ("grad_dtype", _i32), ("dv", _vp), ("dg", _vp),
+                ("dh0", _vp)]
+
+
+class RecurrentFwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("o_dtype", _i32), ("reverse", _i32), ("scale", _f32), ("q", _vp),
+                ("k", _vp), ("v", _vp), ("gk", _vp), ("gv", _vp), ("state_in", _vp), ("state_out", _vp),
+                ("o", _vp), ("cu_seqlens", _vp), ("N", _i32)]
+
+
+class RecurrentBwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("reverse", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp),
+                ("gk", _vp), ("gv", _vp), ("o", _vp), ("do_", _vp), ("h0", _vp), ("dht", _vp), ("dq", _vp),
+                ("dk", _vp), ("dv", _vp), ("dgk", _vp), ("dgv", _vp), ("dh0", _vp), ("cu_seqlens", _vp),
+                ("N", _i32)]
+
+
+lib.tops_b200_strerror.restype = C.c_char_p
+lib.tops_b200_strerror.argtypes = [C.c_int]
+lib.tops_b200_launch_count.restype = C.c_int64
+lib.tops_b200_launch_count.argtypes = []
+for _name, _ptype, _ws in [
+    ("tops_b200_chunk_local_cumsum", CumsumParams, False),
+    ("tops_b200_chunk_fwd_h", FwdHParams, False),
+    ("tops_b200_chunk_bwd_dh", BwdDhParams, False),
+    ("tops_b200_chunk_gla_fwd", ChunkFwdParams, True),
+    ("tops_b200_chunk_gla_bwd", ChunkBwdParams, True),
+    ("tops_b200_fused_recurrent_gla_fwd", RecurrentFwdParams, False),
+    ("tops_b200_fused_recurrent_gla_bwd", RecurrentBwdParams, True),
+]:
+    _f = getattr(lib, _name)
+    _f.restype = C.c_int
+    _f.argtypes = [C.POINTER(_ptype), _vp, _sz, _vp] if _ws else [C.POINTER(_ptype), _vp]
+for _name, _ptype in [
+    ("tops_b200_chunk_fwd_workspace_bytes", ChunkFwdParams),
+    ("tops_b200_chunk_bwd_workspace_bytes", ChunkBwdParams),
+    ("tops_b200_fused_recurrent_gla_bwd_workspace_bytes", RecurrentBwdParams),
+]:
+    _f = getattr(lib, _name)
+    _f.restype = _sz
+    _f.argtypes = [C.POINTER(_ptype)]
+
+
+class TopsError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise TopsError(f"{what}: {lib.tops_b200_strerror(rc).decode()} (code {rc})")
+
+
+def ptr(t) -> int | None:
+    """Device pointer of a tensor (None stays NULL)."""
+    if t is None:
+        return None
+    assert t.is_cuda, "tops_b200 ops take CUDA tensors; there is no CPU path"
+    assert t.is_contiguous(), "tensor must be contiguous"
+    return t.data_ptr()
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def launch_count() -> int:
+    return int(lib.tops_b200_launch_count())
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
