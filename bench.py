@@ -50,7 +50,8 @@ WORKLOADS = {
 # bytes every API tensor contributes once per (token, head) for fwd+bwd of gla_train:
 # fwd reads q,k,v,g (4 x 256) writes o (256); bwd reads q,k,v,g,do (5 x 256),
 # writes dq,dk,dg fp32 (3 x 512) and dv bf16 (256)
-GLA_TRAIN_BYTES_PER_TOKEN_HEAD = 4 * 256 + 256 + 5 * 256 + 3 * 512 + 256
+# plus the four fp32 states (h0, ht, dht, dh0: 4 x 64 KiB per (b, h)) spread over T=4096 tokens: 64 B
+GLA_TRAIN_BYTES_PER_TOKEN_HEAD = 4 * 256 + 256 + 5 * 256 + 3 * 512 + 256 + 64
 GLA_TRAIN_FLOP_PER_TOKEN_HEAD = 98304 + 245760
 
 
@@ -266,7 +267,7 @@ def run_b200(args):
                               "ms_per_launch": per_launch_ms, "peak_source": peak_kind,
                               "kernels_ms_per_step": {k: v[1] / args.steps for k, v in sorted(kernels.items())}}
     if rank == 0 and world == 1:
-        result["cpu_baseline"] = cpu_baseline(sample_B=2, passes=2)
+        result["cpu_baseline"] = cpu_baseline(sample_B=8, passes=4)
     if rank == 0:
         print(json.dumps(result), flush=True)
     if world > 1:

@@ -1,5 +1,4 @@
 """Op families: `gla` (per-channel gates), `simple_gla` (scalar gates),
-`common` (cumsum and the two state scans)."""
+`common` (cumsum and the two state scans).  Import the functions from the
+family modules, e.g. `from tops_b200.ops.gla import chunk_gla`."""
 from . import common, gla, simple_gla  # noqa: F401
-from .gla import chunk_gla, fused_chunk_gla, fused_recurrent_gla  # noqa: F401
-from .simple_gla import chunk_simple_gla, simple_gla  # noqa: F401
