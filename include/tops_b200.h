@@ -57,6 +57,13 @@ const char* tops_b200_strerror(int code);
 /* Number of kernels launched by this library since load (all entry points). */
 int64_t tops_b200_launch_count(void);
 
+/* Every wait inside the tcgen05 kernels (on a TMA or tensor-core completion
+ * barrier) is bounded; a wait that gives up records a small positive code in a
+ * device word and the kernel returns early.  This call copies that word to
+ * `*out` (0 = no wait has ever given up).  It synchronises with the device.
+ * No counterpart in the reference. */
+int tops_b200_device_error(int* out);
+
 /* Per-kernel device timing (no counterpart behind the reference's op API; its
  * benchmarks wrap timed loops in jax.profiler traces, `benchmarks/utils.py:71-83`).
  * While enabled, every kernel this library launches is bracketed by a CUDA event

@@ -82,6 +82,12 @@ lib.tops_b200_strerror.restype = C.c_char_p
 lib.tops_b200_strerror.argtypes = [C.c_int]
 lib.tops_b200_launch_count.restype = C.c_int64
 lib.tops_b200_launch_count.argtypes = []
+lib.tops_b200_device_error.restype = C.c_int
+lib.tops_b200_device_error.argtypes = [C.POINTER(C.c_int)]
+lib.tops_b200_profile_enable.restype = C.c_int
+lib.tops_b200_profile_enable.argtypes = [C.c_int]
+lib.tops_b200_profile_read.restype = C.c_int
+lib.tops_b200_profile_read.argtypes = [C.c_char_p, _sz]
 for _name, _ptype, _ws in [
     ("tops_b200_chunk_local_cumsum", CumsumParams, False),
     ("tops_b200_chunk_fwd_h", FwdHParams, False),
@@ -128,6 +134,13 @@ def stream_ptr(device) -> int:
 
 def launch_count() -> int:
     return int(lib.tops_b200_launch_count())
+
+
+def device_error() -> int:
+    """Code of the first bounded device-side wait that gave up (0 = none); synchronises."""
+    out = C.c_int(0)
+    check(lib.tops_b200_device_error(C.byref(out)), "device_error")
+    return out.value
 
 
 def workspace(nbytes: int, device) -> torch.Tensor:

@@ -1,0 +1,82 @@
+"""The tcgen05 / TMA kernels (bf16, K = V = 128, chunk 64) forced through the
+C ABI with impl = SM100, against the CPU oracle and against the generic
+kernels; the device error word must stay clear."""
+import pytest
+import torch
+
+from oracle import gla as O
+from tests.util import assert_close, rel_l2, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # B, T, H, h0
+    (1, 64, 1, False),
+    (1, 128, 2, True),
+    (2, 512, 3, True),
+    (1, 1024, 2, False),
+]
+
+
+def _run(x, B, T, H, impl, h0):
+    from tops_b200 import _lib as L
+    from tops_b200.ops._chunk import chunk_bwd_call, chunk_fwd_call
+    scale = 128 ** -0.5
+    o, ht, _, _, _ = chunk_fwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, scale, x.get("h0"), True, 64,
+                                    impl=impl)
+    dq, dk, dv, dg, dh0 = chunk_bwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, scale, x.get("h0"),
+                                         x["do"], x["dht"], 64, torch.float32, True, h0, impl=impl)
+    return dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+
+
+@pytest.mark.parametrize("B,T,H,h0", SHAPES)
+def test_sm100_matches_oracle_and_generic(B, T, H, h0):
+    from tops_b200 import _lib as L
+    from tops_b200.synth import make_inputs
+    x = make_inputs(31, B, T, H, 128, 128, dtype=torch.bfloat16, with_h0=h0, with_grads=True)
+    scale = 128 ** -0.5
+    o_ref, ht_ref = O.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale, x.get("h0"), True, chunk_size=64)
+    ref = O.chunk_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, scale, x.get("h0"), None, None, x["do"], x["dht"],
+                          chunk_size=64)
+    want = dict(o=o_ref, ht=ht_ref, dq=ref[0], dk=ref[1], dv=ref[2], dg=ref[3], dh0=ref[4])
+    c = to_cuda(x)
+    n0 = L.launch_count()
+    fast = _run(c, B, T, H, L.IMPL_SM100, h0)
+    torch.cuda.synchronize()
+    assert L.launch_count() - n0 == 5          # fwd: scan + output; bwd: two scans + chunk kernel
+    assert L.device_error() == 0
+    slow = _run(c, B, T, H, L.IMPL_GENERIC, h0)
+    report = {}
+    for name, r in want.items():
+        if r is None:
+            assert fast[name] is None
+            continue
+        report[name] = (rel_l2(fast[name], r), rel_l2(slow[name], r))
+    print(report)
+    for name, r in want.items():
+        if r is not None:
+            assert_close(name, fast[name], r, torch.bfloat16)
+
+
+def test_sm100_is_the_default_for_its_shape():
+    from tops_b200 import _lib as L
+    from tops_b200.ops.gla import chunk_gla
+    from tops_b200.synth import make_inputs
+    x = to_cuda(make_inputs(32, 1, 128, 1, 128, 128, dtype=torch.bfloat16))
+    L.lib.tops_b200_profile_enable(1)
+    chunk_gla(x["q"], x["k"], x["v"], x["g"], chunk_size=64)
+    L.lib.tops_b200_profile_enable(0)
+    import ctypes
+    buf = ctypes.create_string_buffer(4096)
+    L.lib.tops_b200_profile_read(buf, len(buf))
+    labels = [ln.split()[0] for ln in buf.value.decode().splitlines()]
+    assert sorted(labels) == ["sm100_fwd_h", "sm100_fwd_o"], labels
+
+
+def test_sm100_rejects_what_it_cannot_take():
+    from tops_b200 import _lib as L
+    from tops_b200.ops._chunk import chunk_fwd_call
+    from tops_b200.synth import make_inputs
+    x = to_cuda(make_inputs(33, 1, 100, 1, 128, 128, dtype=torch.bfloat16))      # T not a multiple of 64
+    with pytest.raises(L.TopsError):
+        chunk_fwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, 0.1, None, False, 64, impl=L.IMPL_SM100)
