@@ -160,7 +160,9 @@ def run_b200(args):
     from tops_b200.ops._chunk import chunk_bwd_call, chunk_fwd_call
     from tops_b200.synth import make_inputs
 
-    w = WORKLOADS["gla_train"]
+    w = dict(WORKLOADS["gla_train"])
+    if args.batch:
+        w["B"] = args.batch      # smaller batches are for profiler captures only
     dtype = getattr(torch, w["dtype"])
     scale = w["K"] ** -0.5
     host = make_inputs(w["seed"] + 1000 * rank, w["B"], w["T"], w["H"], w["K"], w["V"], dtype=dtype,
@@ -170,9 +172,11 @@ def run_b200(args):
     x = {n: pinned[n].to(dev) for n in names}
 
     def step(t):
-        o, ht, _, _, _ = chunk_fwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"], True, w["C"])
+        # the forward keeps its chunk-start states for the backward (what the differentiable op does)
+        o, ht, _, _, hs = chunk_fwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"], True, w["C"],
+                                         want_h=True)
         dq, dk, dv, dg, dh0 = chunk_bwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"],
-                                             t["do"], t["dht"], w["C"], torch.float32, True, True)
+                                             t["do"], t["dht"], w["C"], torch.float32, True, True, h_saved=hs)
         return o, ht, dq, dk, dv, dg, dh0
 
     def barrier():
@@ -211,6 +215,12 @@ def run_b200(args):
         label, count, total = line.split()
         kernels[label] = (int(count), float(total))
 
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "batch": w["B"], "ms_per_step": ms,
+                              "kernels_ms_per_launch": {k: v[1] / v[0] for k, v in sorted(kernels.items())}}), flush=True)
+        return
+
     # ---- end to end: host buffers in, host buffers out --------------------------------
     outs = step(x)
     out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
@@ -237,7 +247,7 @@ def run_b200(args):
         "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "chunk_gla fwd+bwd, B=8 per GPU, T=4096, H=16, K=V=128, chunk 64, h0+dht (BASELINE configs[1])",
+        "config": {"workload": f"chunk_gla fwd+bwd, B={w['B']} per GPU, T=4096, H=16, K=V=128, chunk 64, h0+dht (BASELINE configs[1])",
                    "global_batch": w["B"] * world, "seq_len": w["T"], "parallelism": f"batch x heads shard x{world}, no communication",
                    "l2": "inputs (671 MB) and outputs are larger than L2; no flush needed"},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -328,6 +338,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=0, help="override B (profiler captures on a smaller case)")
+    ap.add_argument("--kernel-only", action="store_true", help="device-resident timed steps only, short JSON")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:

@@ -184,6 +184,11 @@ typedef struct {
   void* dv;
   float* dg;
   float* dh0; /* NULL unless h0 given and wanted */
+  /* Optional: the chunk-start states `h_out` written by the forward call on
+   * the same inputs (input dtype, [B,NT,H,K,V]).  When given and usable the
+   * backward skips recomputing them; NULL recomputes (the reference always
+   * recomputes, `tops/cpu/ops/gla/chunk.py:551-561`). */
+  const void* h_saved;
 } tops_chunk_bwd_params;
 size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);
 int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,

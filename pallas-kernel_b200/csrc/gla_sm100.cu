@@ -20,6 +20,14 @@
 //   k_bwd_main     dA, dv, dq, dk, dg of one chunk from q, k, v, g, do, h_c, dh_c
 // with G the chunk-local cumulative gate and q~ = q exp(G - mid),
 // k~ = k exp(mid - G), mid = (G_0 + G_n) / 2 per channel.
+//
+// Thread layout (all kernels): 512 threads = 16 warps.  Thread (col, seg) with
+// col = (warp & 3) * 32 + lane and seg = warp >> 2 owns channel `col` for the
+// 16 time steps [16 seg, 16 seg + 16) of the chunk; the cumulative gate is a
+// two-level scan (16 steps in registers, 4 segment sums through shared memory).
+// A warp may only touch the 32 tensor-memory lanes (warp & 3) * 32 .. + 31, so
+// the same thread also owns accumulator row `col` and splits the accumulator
+// columns with the three other warps of its lane quarter by `seg`.
 #include <mutex>
 
 #include "gla_sm100.cuh"
@@ -29,14 +37,23 @@ namespace tops {
 namespace sm100 {
 
 __device__ int g_error;  // first bounded wait that gave up (0 = none)
+#ifdef TOPS_TIMING
+__device__ long long g_timing[16];
+#define TSTAMP(i) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { long long _n = clock64(); g_timing[i] += _n - _t; _t = _n; } } while (0)
+#define TSTART() long long _t = clock64()
+#else
+#define TSTAMP(i)
+#define TSTART()
+#endif
 
 namespace {
 
 constexpr int C = 64;    // chunk
 constexpr int D = 128;   // K = V
-constexpr int NTHREADS = 128;
-constexpr uint32_t SLAB64 = 64 * 128;    // bytes of a 64-row slab
-constexpr uint32_t TILE64 = 2 * SLAB64;  // 64 x 128 bf16 tile
+constexpr int NTHREADS = 512;
+constexpr int SEG = 16;  // time steps per thread
+constexpr uint32_t SLAB64 = 64 * 128;        // bytes of a 64-row slab
+constexpr uint32_t TILE64 = 2 * SLAB64;      // 64 x 128 bf16 tile
 constexpr uint32_t TILE128 = 2 * 128 * 128;  // 128 x 128 bf16 tile
 
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -48,10 +65,12 @@ __device__ __forceinline__ float ld_bf16(const uint8_t* tile, uint32_t off) {
 __device__ __forceinline__ void st_bf16(uint8_t* tile, uint32_t off, float x) {
   *reinterpret_cast<__nv_bfloat16*>(tile + off) = __float2bfloat16_rn(x);
 }
-// offset of (row i, this thread's column) in a 64-row tile; colbase / cchunk from col_prep
+// offset of (row i, this thread's column) in a 64-row tile
 struct ColAddr {
   uint32_t base, cchunk;
-  __device__ __forceinline__ uint32_t at(int i) const { return base + (uint32_t)i * 128u + (((cchunk ^ (uint32_t)i) & 7u) << 4); }
+  __device__ __forceinline__ uint32_t at(int i) const {
+    return base + (uint32_t)i * 128u + (((cchunk ^ (uint32_t)i) & 7u) << 4);
+  }
 };
 __device__ __forceinline__ ColAddr col_prep(int rows, int col) {
   return ColAddr{(uint32_t)((col >> 6) * rows * 128 + (col & 7) * 2), (uint32_t)((col & 63) >> 3)};
@@ -61,6 +80,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 __device__ __forceinline__ void fail(int code) { atomicCAS(&g_error, 0, code); }
+
+// Two-level inclusive scan of this thread's gate column.  gv[t] receives the
+// raw gate of row 16 seg + t; returns the sum over earlier segments (`prefix`)
+// and over the whole chunk (`gn`).  Contains one __syncthreads.
+__device__ __forceinline__ void gate_scan(const uint8_t* gs, const ColAddr& ca, int seg, int col,
+                                          float (*segsum)[D], float (&gv)[SEG], float& prefix, float& gn) {
+  // segsum has 5 rows: [0..3] segment sums, [4] the gate of row 0 (for the mid-point anchor)
+  float s = 0.f;
+#pragma unroll
+  for (int t = 0; t < SEG; ++t) {
+    gv[t] = ld_bf16(gs, ca.at(seg * SEG + t));
+    s += gv[t];
+  }
+  segsum[seg][col] = s;
+  if (seg == 0) segsum[4][col] = gv[0];
+  __syncthreads();
+  const float s0 = segsum[0][col], s1 = segsum[1][col], s2 = segsum[2][col], s3 = segsum[3][col];
+  prefix = (seg > 0 ? s0 : 0.f) + (seg > 1 ? s1 : 0.f) + (seg > 2 ? s2 : 0.f);
+  gn = s0 + s1 + s2 + s3;
+}
 
 // ===========================================================================
 // State scans
@@ -75,14 +114,17 @@ struct ScanParams {
 };
 
 template <bool BWD>
-__global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ ScanParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   constexpr uint32_t STAGE = 2 * TILE64 + SLAB64;  // x, g, y-half
   uint8_t* xg = smem + 2 * STAGE;                   // gated x, 64 x 128
   __shared__ uint64_t full[2], mma_bar;
   __shared__ uint32_t tmem_slot;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  __shared__ float segsum[5][D];
+  __shared__ volatile int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
   const int vh = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
 
@@ -90,6 +132,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     mbar_init(&full[0], 1); mbar_init(&full[1], 1); mbar_init(&mma_bar, 1);
     fence_barrier_init();
     tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
+    abort_flag = 0;
   }
   if (warp == 0) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
   tc_fence_before();
@@ -111,41 +154,44 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
   };
   if (tid == 0) { issue(0); if (NT > 1) issue(1); }
 
-  // fp32 state: row k = tid, columns vh*64 .. vh*64+63
-  float S[64];
+  // fp32 state: row k = col, columns vh*64 + 16 seg .. + 15
+  float S[SEG];
   {
-    const float* src = p.s0 ? p.s0 + ((size_t)bh * D + tid) * D + vh * 64 : nullptr;
+    const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + vh * 64 + seg * SEG : nullptr;
 #pragma unroll
-    for (int j = 0; j < 64; j += 4) {
+    for (int j = 0; j < SEG; j += 4) {
       float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
       S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
     }
   }
-  const ColAddr ca = col_prep(64, tid);
+  const ColAddr ca = col_prep(64, col);
   bool ok = true;
-  for (int step = 0; step < NT && ok; ++step) {
+  for (int step = 0; step < NT; ++step) {
     const int ci = BWD ? NT - 1 - step : step;
     const int s = step & 1;
     uint8_t* xs = smem + s * STAGE;
     uint8_t* gs = xs + TILE64;
     uint8_t* ys = xs + 2 * TILE64;
-    ok = __syncthreads_and(mbar_wait(&full[s], (step >> 1) & 1));
-    if (!ok) { fail(1); break; }
-    // gate the x operand; this thread owns channel `tid`
-    float gn = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) gn += ld_bf16(gs, ca.at(i));
-    float run = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) {
-      run += ld_bf16(gs, ca.at(i));
-      float x = ld_bf16(xs, ca.at(i));
-      float y = BWD ? x * p.scale * __expf(run) : x * __expf(gn - run);
+    TSTART();
+    if (!mbar_wait(&full[s], (step >> 1) & 1)) { abort_flag = 1; fail(1); }
+    TSTAMP(0);
+    float gv[SEG], prefix, gn;
+    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);   // __syncthreads inside
+    TSTAMP(1);
+    if (abort_flag) { ok = false; break; }
+    float run = prefix;
+#pragma unroll
+    for (int t = 0; t < SEG; ++t) {
+      const int i = seg * SEG + t;
+      run += gv[t];
+      const float x = ld_bf16(xs, ca.at(i));
+      const float y = BWD ? x * p.scale * __expf(run) : x * __expf(gn - run);
       st_bf16(xg, ca.at(i), y);
     }
     const float decay = __expf(gn);
     fence_async_smem();
     __syncthreads();
+    TSTAMP(2);
     if (tid == 0) {
       tc_fence_after();
       const uint32_t xa = smem_u32(xg), ya = smem_u32(ys);
@@ -156,37 +202,52 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     }
     // record the state this chunk starts from (bf16), while the tensor core works
     {
-      __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + tid) * D + vh * 64;
+      __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + col) * D + vh * 64 + seg * SEG;
 #pragma unroll
-      for (int j = 0; j < 64; j += 8) {
-        uint4 u;
-        u.x = pack_bf16(S[j], S[j + 1]); u.y = pack_bf16(S[j + 2], S[j + 3]);
-        u.z = pack_bf16(S[j + 4], S[j + 5]); u.w = pack_bf16(S[j + 6], S[j + 7]);
-        *reinterpret_cast<uint4*>(dst + j) = u;
-      }
+      for (int j = 0; j < SEG; j += 8)
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(S[j], S[j + 1]), pack_bf16(S[j + 2], S[j + 3]),
+                                                        pack_bf16(S[j + 4], S[j + 5]), pack_bf16(S[j + 6], S[j + 7]));
     }
-    ok = __syncthreads_and(mbar_wait(&mma_bar, step & 1));
-    if (!ok) { fail(2); break; }
+    TSTAMP(3);
+    if (!mbar_wait(&mma_bar, step & 1)) { abort_flag = 1; fail(2); }
+    TSTAMP(4);
     tc_fence_after();
+    {
+      float d[SEG];
+      tmem_ld16(tmem_addr(tm, (warp & 3) * 32, seg * SEG), d);
 #pragma unroll
-    for (int j = 0; j < 64; j += 32) {
-      float d[32];
-      tmem_ld32(tmem_addr(tm, warp * 32, j), d);
-#pragma unroll
-      for (int t = 0; t < 32; ++t) S[j + t] = fmaf(S[j + t], decay, d[t]);
+      for (int t = 0; t < SEG; ++t) S[t] = fmaf(S[t], decay, d[t]);
     }
     tc_fence_before();
     __syncthreads();
+    TSTAMP(5);
+    if (abort_flag) { ok = false; break; }
     if (tid == 0 && step + 2 < NT) issue(step + 2);
+    TSTAMP(6);
   }
   if (ok && p.s_final) {
-    float* dst = p.s_final + ((size_t)bh * D + tid) * D + vh * 64;
+    float* dst = p.s_final + ((size_t)bh * D + col) * D + vh * 64 + seg * SEG;
 #pragma unroll
-    for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    for (int j = 0; j < SEG; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 64);
+}
+
+// masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
+// 64 x 64 fp32 accumulator into a K-major 64 x 64 tile
+__device__ __forceinline__ void store_tril16(uint8_t* dst, int i, int j0, const float (&a)[16], float scale) {
+#pragma unroll
+  for (int c8 = 0; c8 < 16; c8 += 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 8; t += 2) {
+      const int j = j0 + c8 + t;
+      w[t >> 1] = pack_bf16(j <= i ? a[c8 + t] * scale : 0.f, j + 1 <= i ? a[c8 + t + 1] * scale : 0.f);
+    }
+    *reinterpret_cast<uint4*>(dst + slab_off(i, j0 + c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
 }
 
 // ===========================================================================
@@ -199,7 +260,7 @@ struct FwdOParams {
   float scale;
 };
 
-__global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdOParams p) {
+__global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ FwdOParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* qs = smem;                 // q -> q~ in place
@@ -209,7 +270,9 @@ __global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdO
   uint8_t* hs = vs + TILE64;          // h_c, 128 x 128; row k scaled in place by exp(mid_k) scale
   __shared__ uint64_t bar_load, bar_a, bar_o;
   __shared__ uint32_t tmem_slot;
+  __shared__ float segsum[5][D];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
   const int ci = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int row = b * p.T + ci * C;
 
@@ -217,9 +280,9 @@ __global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdO
     mbar_init(&bar_load, 1); mbar_init(&bar_a, 1); mbar_init(&bar_o, 1);
     fence_barrier_init();
     mbar_expect_tx(&bar_load, 4 * TILE64 + TILE128);
+    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
     tma_load_3d(qs, &p.mq, &bar_load, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_load, 64, h, row);
     tma_load_3d(ks, &p.mk, &bar_load, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_load, 64, h, row);
-    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
     tma_load_3d(vs, &p.mv, &bar_load, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &bar_load, 64, h, row);
     const int hrow = ((b * p.NT + ci) * p.H + h) * D;
     tma_load_2d(hs, &p.mh, &bar_load, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &bar_load, 64, hrow);
@@ -229,28 +292,30 @@ __global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdO
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
+  const uint32_t lane_base = (warp & 3) * 32;
   bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
   if (!ok) fail(3);
   if (ok) {
-    const ColAddr ca = col_prep(64, tid);
-    float g0 = ld_bf16(gs, ca.at(0)), gn = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) gn += ld_bf16(gs, ca.at(i));
+    const ColAddr ca = col_prep(64, col);
+    float gv[SEG], prefix, gn;
+    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);
+    const float g0 = segsum[4][col];
     const float mid = 0.5f * (g0 + gn);
-    const float qscale = __expf(mid) * p.scale;
-    float run = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) {
-      run += ld_bf16(gs, ca.at(i));
+    float run = prefix;
+#pragma unroll
+    for (int t = 0; t < SEG; ++t) {
+      const int i = seg * SEG + t;
+      run += gv[t];
       const float e = __expf(run - mid);
       const float q = ld_bf16(qs, ca.at(i)), k = ld_bf16(ks, ca.at(i));
       st_bf16(qs, ca.at(i), q * e);
       st_bf16(ks, ca.at(i), __fdividef(k, e));
     }
-    // q exp(G) scale = q~ (exp(mid) scale): fold the per-channel factor into row `tid` of h_c
-#pragma unroll 4
-    for (int c8 = 0; c8 < D; c8 += 8) {
-      uint4* ph = reinterpret_cast<uint4*>(hs + tile_off(128, tid, c8));
+    // q exp(G) scale = q~ (exp(mid) scale): fold the per-channel factor into row `col` of h_c
+    const float qscale = __expf(mid) * p.scale;
+#pragma unroll
+    for (int c8 = 0; c8 < 32; c8 += 8) {
+      uint4* ph = reinterpret_cast<uint4*>(hs + tile_off(128, col, seg * 32 + c8));
       uint4 a = *ph;
       __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&a);
 #pragma unroll
@@ -280,25 +345,11 @@ __global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdO
   }
   if (ok) {
     tc_fence_after();
-    // rows of an M = 64 accumulator sit in lanes 0..15 of each warp's 32-lane window
-    const int i = 16 * warp + lane;
-#pragma unroll
-    for (int j0 = 0; j0 < C; j0 += 32) {
-      float a[32];
-      tmem_ld32(tmem_addr(tm, warp * 32, j0), a);
-      if (lane < 16) {
-#pragma unroll
-        for (int c8 = 0; c8 < 32; c8 += 8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int t = 0; t < 8; t += 2) {
-            const int j = j0 + c8 + t;
-            w[t >> 1] = pack_bf16(j <= i ? a[c8 + t] * p.scale : 0.f, j + 1 <= i ? a[c8 + t + 1] * p.scale : 0.f);
-          }
-          *reinterpret_cast<uint4*>(gs + slab_off(i, j0 + c8)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-    }
+    // rows of an M = 64 accumulator sit in lanes 0..15 of each 32-lane quarter
+    const int i = 16 * (warp & 3) + lane;
+    float a[16];
+    tmem_ld16(tmem_addr(tm, lane_base, seg * 16), a);
+    if (lane < 16) store_tril16(gs, i, seg * 16, a, p.scale);
     fence_async_smem();
     tc_fence_before();
   }
@@ -317,18 +368,15 @@ __global__ void __launch_bounds__(NTHREADS) k_fwd_o(const __grid_constant__ FwdO
   }
   if (ok) {
     tc_fence_after();
-    const int i = 16 * warp + lane;
-    __nv_bfloat16* dst = p.o + ((size_t)(row + i) * p.H + h) * D;
+    const int i = 16 * (warp & 3) + lane;
+    __nv_bfloat16* dst = p.o + ((size_t)(row + i) * p.H + h) * D + seg * 32;
+    float a[32];
+    tmem_ld32(tmem_addr(tm, lane_base, 64 + seg * 32), a);
+    if (lane < 16) {
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      float a[32];
-      tmem_ld32(tmem_addr(tm, warp * 32, 64 + c0), a);
-      if (lane < 16) {
-#pragma unroll
-        for (int t = 0; t < 32; t += 8)
-          *reinterpret_cast<uint4*>(dst + c0 + t) = make_uint4(pack_bf16(a[t], a[t + 1]), pack_bf16(a[t + 2], a[t + 3]),
-                                                               pack_bf16(a[t + 4], a[t + 5]), pack_bf16(a[t + 6], a[t + 7]));
-      }
+      for (int t = 0; t < 32; t += 8)
+        *reinterpret_cast<uint4*>(dst + t) = make_uint4(pack_bf16(a[t], a[t + 1]), pack_bf16(a[t + 2], a[t + 3]),
+                                                        pack_bf16(a[t + 4], a[t + 5]), pack_bf16(a[t + 6], a[t + 7]));
     }
   }
   tc_fence_before();
@@ -350,86 +398,95 @@ struct BwdParams {
 __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  uint8_t* qs = smem;
-  uint8_t* ks = qs + TILE64;
-  uint8_t* gs = ks + TILE64;
+  uint8_t* qs = smem;                 // q -> q exp(G - mid) in place
+  uint8_t* ks = qs + TILE64;          // k -> k exp(mid - G) in place
+  uint8_t* gs = ks + TILE64;          // g -> k exp(G_n - G) in place
   uint8_t* vs = gs + TILE64;
   uint8_t* dos = vs + TILE64;
   uint8_t* hs = dos + TILE64;         // h_c   128 x 128
   uint8_t* dhs = hs + TILE128;        // dh_c  128 x 128
-  uint8_t* qt = dhs + TILE128;        // q exp(G - mid)      (later: fp32 dg staging, with kt)
-  uint8_t* kt = qt + TILE64;          // k exp(mid - G)
-  uint8_t* kg = kt + TILE64;          // k exp(G_n - G)
-  uint8_t* Ps = kg + TILE64;          // tril(A) scale, bf16 64 x 64
+  uint8_t* Ps = dhs + TILE128;        // tril(A) scale, bf16 64 x 64
   uint8_t* dAs = Ps + SLAB64;         // tril(dA) scale, bf16 64 x 64
-  __shared__ uint64_t bar_load, bar1, bar2, bar3;
+  __shared__ uint64_t bar_load, bar1, bar3;
   __shared__ uint32_t tmem_slot;
+  __shared__ float segsum[5][D];      // gate segment sums (+ row-0 gate); later suffix-sum partials of dg
+  __shared__ float part[2][4][D];     // [0]: sum_v h dh partials; [1]: sum_i dk_inter k partials
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
   const int ci = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int row = b * p.T + ci * C;
 
   if (tid == 0) {
-    mbar_init(&bar_load, 1); mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_init(&bar3, 1);
+    mbar_init(&bar_load, 1); mbar_init(&bar1, 1); mbar_init(&bar3, 1);
     fence_barrier_init();
     mbar_expect_tx(&bar_load, 5 * TILE64 + 2 * TILE128);
+    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
     tma_load_3d(qs, &p.mq, &bar_load, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_load, 64, h, row);
     tma_load_3d(ks, &p.mk, &bar_load, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_load, 64, h, row);
-    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
-    tma_load_3d(vs, &p.mv, &bar_load, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &bar_load, 64, h, row);
-    tma_load_3d(dos, &p.mdo, &bar_load, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &bar_load, 64, h, row);
     const int hrow = ((b * p.NT + ci) * p.H + h) * D;
     tma_load_2d(hs, &p.mh, &bar_load, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &bar_load, 64, hrow);
     tma_load_2d(dhs, &p.mdh, &bar_load, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &bar_load, 64, hrow);
+    tma_load_3d(vs, &p.mv, &bar_load, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &bar_load, 64, h, row);
+    tma_load_3d(dos, &p.mdo, &bar_load, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &bar_load, 64, h, row);
   }
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
+  const uint32_t lane_base = (warp & 3) * 32;
   // tensor-memory columns
   constexpr uint32_t cA = 0, cdA = 64, cdq2 = 128, cdk2 = 192, cdv = 256, cdq1 = 320, cdk1 = 384;
 
-  const ColAddr ca = col_prep(64, tid);
-  float mid = 0.f, gn = 0.f, hdh = 0.f;
+  // values of this thread's 16 (time, channel) elements, kept for the epilogue
+  uint32_t qk[SEG];   // packed bf16 (q, k)
+  float gv[SEG];
+  float mid = 0.f, gn = 0.f, gend = 0.f;
   bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
   if (!ok) fail(6);
   if (ok) {
-    const float g0 = ld_bf16(gs, ca.at(0));
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) gn += ld_bf16(gs, ca.at(i));
+    const ColAddr ca = col_prep(64, col);
+    float prefix;
+    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);
+    const float g0 = segsum[4][col];
     mid = 0.5f * (g0 + gn);
     const float tail = __expf(gn - mid);
-    float run = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < C; ++i) {
-      run += ld_bf16(gs, ca.at(i));
+    float run = prefix;
+#pragma unroll
+    for (int t = 0; t < SEG; ++t) {
+      const int i = seg * SEG + t;
+      run += gv[t];
       const float e = __expf(run - mid);
       const float q = ld_bf16(qs, ca.at(i)), k = ld_bf16(ks, ca.at(i));
+      qk[t] = pack_bf16(q, k);
       const float kn = __fdividef(k, e);
-      st_bf16(qt, ca.at(i), q * e);
-      st_bf16(kt, ca.at(i), kn);
-      st_bf16(kg, ca.at(i), kn * tail);
+      st_bf16(qs, ca.at(i), q * e);
+      st_bf16(ks, ca.at(i), kn);
+      st_bf16(gs, ca.at(i), kn * tail);
     }
-    // sum_v h[k][v] dh[k][v] for k = tid
-#pragma unroll 4
-    for (int c8 = 0; c8 < D; c8 += 8) {
-      const uint32_t off = tile_off(128, tid, c8);
+    gend = run;
+    // partial of sum_v h[k][v] dh[k][v] for k = col over v in [32 seg, 32 seg + 32)
+    float hd = 0.f;
+#pragma unroll
+    for (int c8 = 0; c8 < 32; c8 += 8) {
+      const uint32_t off = tile_off(128, col, seg * 32 + c8);
       const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
       const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
       const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
-        hdh = fmaf(fa.x, fd.x, hdh);
-        hdh = fmaf(fa.y, fd.y, hdh);
+        hd = fmaf(fa.x, fd.x, hd);
+        hd = fmaf(fa.y, fd.y, hd);
       }
     }
+    part[0][seg][col] = hd;
     fence_async_smem();
   }
   __syncthreads();
   if (ok && tid == 0) {
     tc_fence_after();
-    const uint32_t qta = smem_u32(qt), kta = smem_u32(kt), kga = smem_u32(kg), va = smem_u32(vs), doa = smem_u32(dos),
+    const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), kga = smem_u32(gs), va = smem_u32(vs), doa = smem_u32(dos),
                    ha = smem_u32(hs), dha = smem_u32(dhs);
 #pragma unroll
     for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
@@ -447,7 +504,6 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
 #pragma unroll
     for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh^T kg^T
       umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kga, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
-    umma_commit(&bar2);
   }
   if (ok) {
     ok = __syncthreads_and(mbar_wait(&bar1, 0));
@@ -455,35 +511,19 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   }
   if (ok) {
     tc_fence_after();
-    const int i = 16 * warp + lane;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      uint8_t* dst = which ? dAs : Ps;
-#pragma unroll
-      for (int j0 = 0; j0 < C; j0 += 32) {
-        float a[32];
-        tmem_ld32(tmem_addr(tm, warp * 32, (which ? cdA : cA) + j0), a);
-        if (lane < 16) {
-#pragma unroll
-          for (int c8 = 0; c8 < 32; c8 += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int t = 0; t < 8; t += 2) {
-              const int j = j0 + c8 + t;
-              w[t >> 1] = pack_bf16(j <= i ? a[c8 + t] * p.scale : 0.f, j + 1 <= i ? a[c8 + t + 1] * p.scale : 0.f);
-            }
-            *reinterpret_cast<uint4*>(dst + slab_off(i, j0 + c8)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
-    }
+    const int i = 16 * (warp & 3) + lane;
+    float a[16];
+    tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
+    if (lane < 16) store_tril16(Ps, i, seg * 16, a, p.scale);
+    tmem_ld16(tmem_addr(tm, lane_base, cdA + seg * 16), a);
+    if (lane < 16) store_tril16(dAs, i, seg * 16, a, p.scale);
     fence_async_smem();
     tc_fence_before();
   }
   __syncthreads();
   if (ok && tid == 0) {
     tc_fence_after();
-    const uint32_t qta = smem_u32(qt), kta = smem_u32(kt), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
+    const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
 #pragma unroll
     for (int k0 = 0; k0 < C; k0 += 16)   // dq_intra^T[k][i] = sum_j k~[j][k] dA[i][j]
       umma_bf16(tm + cdq1, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
@@ -499,55 +539,57 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     ok = __syncthreads_and(mbar_wait(&bar3, 0));
     if (!ok) fail(8);
   }
+  float dgl[SEG];
+  const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
+  const size_t ostride = (size_t)p.H * D;
   if (ok) {
     tc_fence_after();
-    // dv: this thread owns value channel `tid`
+    // dv: this thread owns value channel `col`, time steps of its segment
     {
-      __nv_bfloat16* dst = p.dv + ((size_t)row * p.H + h) * D + tid;
+      float a[16];
+      tmem_ld16(tmem_addr(tm, lane_base, cdv + seg * 16), a);
 #pragma unroll
-      for (int j0 = 0; j0 < C; j0 += 32) {
-        float a[32];
-        tmem_ld32(tmem_addr(tm, warp * 32, cdv + j0), a);
-#pragma unroll
-        for (int t = 0; t < 32; ++t) dst[(size_t)(j0 + t) * p.H * D] = __float2bfloat16_rn(a[t]);
-      }
+      for (int t = 0; t < 16; ++t) p.dv[obase + t * ostride] = __float2bfloat16_rn(a[t]);
     }
-    // dq, dk, dg: this thread owns key channel `tid`; walk time backwards so the
-    // suffix sum of the gate gradient stays in a register
-    float* stage = reinterpret_cast<float*>(qt);  // [64][128] fp32 over qt + kt (both consumed)
+    // dq, dk and the local suffix sums of the gate gradient, walking time backwards
     const float c1 = p.scale * __expf(mid), c2 = __expf(gn - mid);
-    float grun = gn, run = 0.f, tail = 0.f;
-    const size_t obase = ((size_t)row * p.H + h) * D + tid;
-    const size_t ostride = (size_t)p.H * D;
-#pragma unroll 1
-    for (int i0 = C - 16; i0 >= 0; i0 -= 16) {
-      float dq1[16], dq2[16], dk1[16], dk2[16];
-      tmem_ld16(tmem_addr(tm, warp * 32, cdq1 + i0), dq1);
-      tmem_ld16(tmem_addr(tm, warp * 32, cdq2 + i0), dq2);
-      tmem_ld16(tmem_addr(tm, warp * 32, cdk1 + i0), dk1);
-      tmem_ld16(tmem_addr(tm, warp * 32, cdk2 + i0), dk2);
+    float grun = gend, run = 0.f, tail = 0.f;
 #pragma unroll
-      for (int t = 15; t >= 0; --t) {
-        const int i = i0 + t;
+    for (int half = 1; half >= 0; --half) {
+      float dq1[8], dq2[8], dk1[8], dk2[8];
+      const uint32_t c0 = seg * 16 + half * 8;
+      tmem_ld8(tmem_addr(tm, lane_base, cdq1 + c0), dq1);
+      tmem_ld8(tmem_addr(tm, lane_base, cdq2 + c0), dq2);
+      tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
+      tmem_ld8(tmem_addr(tm, lane_base, cdk2 + c0), dk2);
+#pragma unroll
+      for (int u = 7; u >= 0; --u) {
+        const int t = half * 8 + u;
         const float e = __expf(grun - mid);
         const float r = __fdividef(1.f, e);
-        const float dq = e * fmaf(c1, dq2[t], dq1[t]);
-        const float dkin = r * c2 * dk2[t];
-        const float dk = fmaf(r, dk1[t], dkin);
-        p.dq[obase + i * ostride] = dq;
-        p.dk[obase + i * ostride] = dk;
-        const float q = ld_bf16(qs, ca.at(i)), k = ld_bf16(ks, ca.at(i));
-        run += q * dq - k * dk;
-        tail = fmaf(dkin, k, tail);
-        stage[i * D + tid] = run;
-        grun -= ld_bf16(gs, ca.at(i));
+        const float dq = e * fmaf(c1, dq2[u], dq1[u]);
+        const float dkin = r * c2 * dk2[u];
+        const float dk = fmaf(r, dk1[u], dkin);
+        p.dq[obase + t * ostride] = dq;
+        p.dk[obase + t * ostride] = dk;
+        const float2 qkf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qk[t]));
+        run += qkf.x * dq - qkf.y * dk;
+        tail = fmaf(dkin, qkf.y, tail);
+        dgl[t] = run;
+        grun -= gv[t];
       }
     }
-    if (p.dg) {
-      const float cst = tail + __expf(gn) * hdh;
-#pragma unroll 8
-      for (int i = 0; i < C; ++i) p.dg[obase + i * ostride] = stage[i * D + tid] + cst;
-    }
+    segsum[seg][col] = run;
+    part[1][seg][col] = tail;
+  }
+  __syncthreads();
+  if (ok && p.dg) {
+    const float later = (seg < 1 ? segsum[1][col] : 0.f) + (seg < 2 ? segsum[2][col] : 0.f) + (seg < 3 ? segsum[3][col] : 0.f);
+    const float hdh = part[0][0][col] + part[0][1][col] + part[0][2][col] + part[0][3][col];
+    const float tails = part[1][0][col] + part[1][1][col] + part[1][2][col] + part[1][3][col];
+    const float cst = later + tails + __expf(gn) * hdh;
+#pragma unroll
+    for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
   }
   tc_fence_before();
   __syncthreads();
@@ -613,7 +655,7 @@ bool device_is_sm100() {
 
 constexpr size_t SCAN_SMEM = 2 * (2 * TILE64 + SLAB64) + TILE64 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + 1024;
-constexpr size_t BWD_SMEM = 8 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 1024;
+constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 1024;
 
 template <class F>
 int opt_in_smem(F f, size_t bytes) {
@@ -682,7 +724,9 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
   return post_launch();
 }
 
-size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p) { return 2 * state_bytes(p.pb) + 256; }
+size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p) {
+  return (p.h_saved ? 1 : 2) * state_bytes(p.pb) + 256;
+}
 
 int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st) {
   const tops_chunk_problem& pb = p.pb;
@@ -690,10 +734,16 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.do_) ||
       !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(ws))
     return TOPS_E_ALIGN;
-  char* h = reinterpret_cast<char*>(ws);
-  char* dh = h + state_bytes(pb);
-  int rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, h, nullptr, st);
-  if (rc) return rc;
+  const char* h = reinterpret_cast<const char*>(p.h_saved);
+  char* dh = reinterpret_cast<char*>(ws);
+  int rc = TOPS_OK;
+  if (!h) {
+    if (!aligned16(p.h_saved)) return TOPS_E_ALIGN;
+    char* hw = reinterpret_cast<char*>(ws);
+    dh = hw + state_bytes(pb);
+    if ((rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, hw, nullptr, st))) return rc;
+    h = hw;
+  }
   if ((rc = run_scan(true, pb, p.q, p.g, p.do_, p.dht, dh, p.dh0, st))) return rc;
   BwdParams bp;
   const int BT = pb.B * pb.T, NT = pb.T / C;
@@ -710,6 +760,15 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   k_bwd_main<<<dim3(NT, pb.B * pb.H), NTHREADS, BWD_SMEM, st>>>(bp);
   return post_launch();
 }
+
+#ifdef TOPS_TIMING
+extern "C" int tops_b200_debug_timing(long long* out, int n, int reset) {
+  long long z[16] = {0};
+  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(long long) * (n < 16 ? n : 16)) != cudaSuccess) return TOPS_E_CUDA;
+  if (reset) cudaMemcpyToSymbol(g_timing, z, sizeof z);
+  return TOPS_OK;
+}
+#endif
 
 int device_error(int* out) {
   int v = 0;

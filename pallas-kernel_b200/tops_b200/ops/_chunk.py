@@ -45,8 +45,9 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
 
 
 def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dtype, want_dg, want_dh0,
-                   cu_seqlens=None, impl=L.IMPL_AUTO):
-    """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0)."""
+                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None):
+    """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0).  `h_saved`
+    is the `h` returned by chunk_fwd_call(want_h=True) on the same inputs."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     dev = q.device
@@ -76,6 +77,9 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
                                               L.ptr(dht))
     p.dq, p.dk, p.dv, p.dg, p.dh0 = L.ptr(dq), L.ptr(dk), L.ptr(dv), L.ptr(dg), L.ptr(dh0)
     p.grad_dtype = L.dtype_code(grad_dtype)
+    if h_saved is not None:
+        assert h_saved.dtype == q.dtype and h_saved.shape[-3:] == (H, K, V)
+        p.h_saved = L.ptr(h_saved)
     ws = L.workspace(L.lib.tops_b200_chunk_bwd_workspace_bytes(C.byref(p)), dev)
     L.check(L.lib.tops_b200_chunk_gla_bwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)),
             "chunk_gla_bwd")

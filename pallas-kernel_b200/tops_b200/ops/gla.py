@@ -70,20 +70,20 @@ def chunk_gla_bwd(q, k, v, g, g_cumsum, scale, initial_state, h, A, do, dht, chu
 class _ChunkGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, initial_state, scale, output_final_state, cu, chunk_size):
-        o, ht, _, _, _ = chunk_fwd_call(q, k, v, g, L.GATE_PER_CHANNEL if g is not None else L.GATE_NONE,
-                                        scale, initial_state, output_final_state, chunk_size, cu)
-        ctx.save_for_backward(q, k, v, g, initial_state)
+        # the chunk-start states are kept for the backward (one bf16 [B,NT,H,K,V] tensor)
+        keep = any(t is not None and t.requires_grad for t in (q, k, v, g, initial_state))
+        o, ht, _, _, hs = chunk_fwd_call(q, k, v, g, L.GATE_PER_CHANNEL if g is not None else L.GATE_NONE,
+                                         scale, initial_state, output_final_state, chunk_size, cu, want_h=keep)
+        ctx.save_for_backward(q, k, v, g, initial_state, hs)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
-        if ht is None:
-            ctx.mark_non_differentiable()
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, h0 = ctx.saved_tensors
+        q, k, v, g, h0, hs = ctx.saved_tensors
         kind = L.GATE_PER_CHANNEL if g is not None else L.GATE_NONE
         dq, dk, dv, dg, dh0 = chunk_bwd_call(q, k, v, g, kind, ctx.scale, h0, do.to(q.dtype), dht, ctx.chunk,
-                                             torch.float32, g is not None, h0 is not None, ctx.cu)
+                                             torch.float32, g is not None, h0 is not None, ctx.cu, h_saved=hs)
         # cotangents take the primal's dtype at this boundary
         return (dq.to(q.dtype), dk.to(k.dtype), dv, None if g is None else dg.to(g.dtype),
                 None if h0 is None else dh0.to(h0.dtype), None, None, None, None)
