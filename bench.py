@@ -174,7 +174,7 @@ def run_b200(args):
     def step(t):
         # the forward keeps its chunk-start states for the backward (what the differentiable op does)
         o, ht, _, _, hs = chunk_fwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"], True, w["C"],
-                                         want_h=True)
+                                         want_saved=True)
         dq, dk, dv, dg, dh0 = chunk_bwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"],
                                              t["do"], t["dht"], w["C"], torch.float32, True, True, h_saved=hs)
         return o, ht, dq, dk, dv, dg, dh0

@@ -158,7 +158,15 @@ typedef struct {
   float* g_cumsum_out;
   float* A_out;
   void* h_out;
+  /* Optional scratch kept for the backward call of the same problem:
+   * B*NT*H*K*V elements of the input dtype.  Its content is private to the
+   * kernel family that ran (the tcgen05 kernels store pre-scaled bf16 states);
+   * hand it to tops_b200_chunk_gla_bwd as `h_saved` only when
+   * tops_b200_chunk_selected_impl reports TOPS_IMPL_SM100 for the problem. */
+  void* saved_out;
 } tops_chunk_fwd_params;
+/* Which kernel family TOPS_IMPL_AUTO resolves to for this problem on the current device. */
+int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb);
 size_t tops_b200_chunk_fwd_workspace_bytes(const tops_chunk_fwd_params* p);
 int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* workspace, size_t workspace_bytes,
                             void* stream);
@@ -184,10 +192,10 @@ typedef struct {
   void* dv;
   float* dg;
   float* dh0; /* NULL unless h0 given and wanted */
-  /* Optional: the chunk-start states `h_out` written by the forward call on
-   * the same inputs (input dtype, [B,NT,H,K,V]).  When given and usable the
-   * backward skips recomputing them; NULL recomputes (the reference always
-   * recomputes, `tops/cpu/ops/gla/chunk.py:551-561`). */
+  /* Optional: the `saved_out` scratch written by the forward call on the same
+   * inputs (tcgen05 path only).  When given the backward skips recomputing the
+   * chunk-start states; NULL recomputes (the reference always recomputes,
+   * `tops/cpu/ops/gla/chunk.py:551-561`). */
   const void* h_saved;
 } tops_chunk_bwd_params;
 size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);

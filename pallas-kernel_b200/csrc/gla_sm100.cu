@@ -39,11 +39,15 @@ namespace sm100 {
 __device__ int g_error;  // first bounded wait that gave up (0 = none)
 #ifdef TOPS_TIMING
 __device__ long long g_timing[16];
-#define TSTAMP(i) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { long long _n = clock64(); g_timing[i] += _n - _t; _t = _n; } } while (0)
-#define TSTART() long long _t = clock64()
+#define TDECL() long long _acc[16] = {0}; long long _t = 0
+#define TSTAMP(i) do { long long _n = clock64(); _acc[i] += _n - _t; _t = _n; } while (0)
+#define TSTART() _t = clock64()
+#define TFLUSH() do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { for (int _i = 0; _i < 16; ++_i) g_timing[_i] += _acc[_i]; } } while (0)
 #else
+#define TDECL()
 #define TSTAMP(i)
 #define TSTART()
+#define TFLUSH()
 #endif
 
 namespace {
@@ -113,46 +117,120 @@ struct ScanParams {
   float scale;
 };
 
+// Constant 64 x 64 patterns, stored as K-major bf16 tiles, that turn the gate
+// tile g [time j][channel] into exponents with one tensor-core product:
+//   TRI_INCL  L[i][j] = (j <= i)                 -> G_i           (inclusive cumulative gate)
+//   TRI_REV   U[i][j] = (j > i), row 63 all ones  -> G_n - G_i for i < 63 (the exponent of row 63 is 0 and is
+//             not needed from the product), and G_n in row 63
+//   TRI_MID   L - 1/2 [j == 0] - 1/2             -> G_i - (G_0 + G_n) / 2
+// All entries (0, 1, +-1/2) are exact in bf16 and the products accumulate in fp32.
+enum { TRI_INCL = 0, TRI_REV = 1, TRI_MID = 2 };
+__device__ __forceinline__ float tri_value(int kind, int i, int j) {
+  if (kind == TRI_INCL) return j <= i ? 1.f : 0.f;
+  if (kind == TRI_REV) return (i == 63 || j > i) ? 1.f : 0.f;
+  return j == 0 ? 0.f : (j <= i ? 0.5f : -0.5f);
+}
+__device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind) {
+  for (int idx = threadIdx.x; idx < rows * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8, i = r & 63;
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) w[t] = pack_bf16(tri_value(kind, i, c8 + 2 * t), tri_value(kind, i, c8 + 2 * t + 1));
+    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+// 16 x 64 tile: row 0 sums the gates (G_n), row 1 gives the mid-point (G_0 + G_n) / 2
+__device__ __forceinline__ void build_w_tile(uint8_t* tile) {
+  for (int idx = threadIdx.x; idx < 16 * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int j = c8 + 2 * t;
+      const float a = r == 0 ? 1.f : (r == 1 ? (j == 0 ? 1.f : 0.5f) : 0.f);
+      const float b = r == 0 ? 1.f : (r == 1 ? 0.5f : 0.f);
+      w[t] = pack_bf16(a, b);
+    }
+    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+// multiply 8 packed bf16 by 8 fp32 factors
+__device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
+  __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);
+  uint4 y;
+  uint32_t* py = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = __bfloat1622float2(px[t]);
+    py[t] = pack_bf16(v.x * f[2 * t], v.y * f[2 * t + 1]);
+  }
+  return y;
+}
+
 template <bool BWD>
 __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ ScanParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   constexpr uint32_t STAGE = 2 * TILE64 + SLAB64;  // x, g, y-half
   uint8_t* xg = smem + 2 * STAGE;                   // gated x, 64 x 128
-  __shared__ uint64_t full[2], mma_bar;
+  uint8_t* mt = xg + TILE64;                        // exponent pattern, 64 x 64
+  __shared__ uint64_t full[2], ebar, sbar;
+  __shared__ float gn_s[D], e0_s[D];   // row 63 (G_n) and row 0 of the exponent tile, per channel
   __shared__ uint32_t tmem_slot;
-  __shared__ float segsum[5][D];
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
+  const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
   const int vh = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
+  constexpr uint32_t cE = 0, cS = 128;   // tensor-memory columns
 
   if (tid == 0) {
-    mbar_init(&full[0], 1); mbar_init(&full[1], 1); mbar_init(&mma_bar, 1);
+    mbar_init(&full[0], 2); mbar_init(&full[1], 2); mbar_init(&ebar, 1); mbar_init(&sbar, 1);
     fence_barrier_init();
     tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
     abort_flag = 0;
   }
-  if (warp == 0) { tmem_alloc(&tmem_slot, 64); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  build_tri_tile(mt, 64, BWD ? TRI_INCL : TRI_REV);
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
+  const uint32_t lane_base = q4 * 32;
 
-  auto issue = [&](int step) {
+  auto issue_xg = [&](int step) {
     const int ci = BWD ? NT - 1 - step : step;
-    const int s = step & 1;
-    uint8_t* st = smem + s * STAGE;
+    uint8_t* st = smem + (step & 1) * STAGE;
     const int row = b * p.T + ci * C;
-    mbar_expect_tx(&full[s], STAGE);
-    tma_load_3d(st, &p.mx, &full[s], 0, h, row);
-    tma_load_3d(st + SLAB64, &p.mx, &full[s], 64, h, row);
-    tma_load_3d(st + TILE64, &p.mg, &full[s], 0, h, row);
-    tma_load_3d(st + TILE64 + SLAB64, &p.mg, &full[s], 64, h, row);
-    tma_load_3d(st + 2 * TILE64, &p.my, &full[s], vh * 64, h, row);
+    mbar_expect_tx(&full[step & 1], 2 * TILE64);
+    tma_load_3d(st + TILE64, &p.mg, &full[step & 1], 0, h, row);
+    tma_load_3d(st + TILE64 + SLAB64, &p.mg, &full[step & 1], 64, h, row);
+    tma_load_3d(st, &p.mx, &full[step & 1], 0, h, row);
+    tma_load_3d(st + SLAB64, &p.mx, &full[step & 1], 64, h, row);
   };
-  if (tid == 0) { issue(0); if (NT > 1) issue(1); }
+  auto issue_y = [&](int step) {
+    const int ci = BWD ? NT - 1 - step : step;
+    uint8_t* st = smem + (step & 1) * STAGE;
+    mbar_expect_tx(&full[step & 1], SLAB64);
+    tma_load_3d(st + 2 * TILE64, &p.my, &full[step & 1], vh * 64, h, b * p.T + ci * C);
+  };
+  // exponents E = pattern . g (M = 64) of one stage; row 63 of E is the chunk total G_n
+  auto issue_gate_mma = [&](int step) {
+    const uint32_t ga = smem_u32(smem + (step & 1) * STAGE + TILE64), ma = smem_u32(mt);
+#pragma unroll
+    for (int j0 = 0; j0 < C; j0 += 16)
+      umma_bf16(tm + cE, desc_kmajor(ma, 64, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(64, 128, 0, 1), j0 > 0);
+    umma_commit(&ebar);
+  };
+  if (tid == 0) {
+    issue_xg(0); issue_y(0);
+    if (NT > 1) { issue_xg(1); issue_y(1); }
+    if (!mbar_wait(&full[0], 0)) { abort_flag = 1; fail(1); }
+    tc_fence_after();
+    issue_gate_mma(0);
+  }
+  __syncwarp();
 
   // fp32 state: row k = col, columns vh*64 + 16 seg .. + 15
   float S[SEG];
@@ -164,57 +242,101 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ Sc
       S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
     }
   }
-  const ColAddr ca = col_prep(64, col);
   bool ok = true;
+  TDECL();
   for (int step = 0; step < NT; ++step) {
     const int ci = BWD ? NT - 1 - step : step;
     const int s = step & 1;
     uint8_t* xs = smem + s * STAGE;
-    uint8_t* gs = xs + TILE64;
     uint8_t* ys = xs + 2 * TILE64;
     TSTART();
     if (!mbar_wait(&full[s], (step >> 1) & 1)) { abort_flag = 1; fail(1); }
+    if (!mbar_wait(&ebar, step & 1)) { abort_flag = 1; fail(2); }
+    tc_fence_after();
     TSTAMP(0);
-    float gv[SEG], prefix, gn;
-    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);   // __syncthreads inside
+    {
+      // rows of the M = 64 exponent tile sit in lanes 0..15 of each 32-lane quarter
+      float e[32];
+      tmem_ld32(tmem_addr(tm, lane_base, cE + seg * 32), e);
+      TSTAMP(8);
+      if (lane < 16) {
+        const int i = 16 * q4 + lane;
+        if (i == 63) {   // this row carries G_n: the log-decay of the state rows
+#pragma unroll
+          for (int t = 0; t < 32; ++t) gn_s[seg * 32 + t] = e[t];
+          if (!BWD) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) e[t] = 0.f;
+          }
+        }
+        if (!BWD && i == 0) {   // G_n - G_0, for the mid-point the stored states are scaled by
+#pragma unroll
+          for (int t = 0; t < 32; ++t) e0_s[seg * 32 + t] = e[t];
+        }
+#pragma unroll
+        for (int t = 0; t < 32; ++t) e[t] = fast_exp(e[t]);
+        if (BWD) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) e[t] *= p.scale;
+        }
+        const uint32_t rowoff = (uint32_t)(seg >> 1) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = rowoff + (((uint32_t)((seg & 1) * 4 + u) ^ (uint32_t)i) & 7u) * 16u;
+          *reinterpret_cast<uint4*>(xg + off) = scale8(*reinterpret_cast<const uint4*>(xs + off), e + 8 * u);
+        }
+      }
+    }
+    TSTAMP(9);
+    fence_async_smem();
+    TSTAMP(10);
+    tc_fence_before();
+    __syncthreads();
     TSTAMP(1);
     if (abort_flag) { ok = false; break; }
-    float run = prefix;
-#pragma unroll
-    for (int t = 0; t < SEG; ++t) {
-      const int i = seg * SEG + t;
-      run += gv[t];
-      const float x = ld_bf16(xs, ca.at(i));
-      const float y = BWD ? x * p.scale * __expf(run) : x * __expf(gn - run);
-      st_bf16(xg, ca.at(i), y);
-    }
-    const float decay = __expf(gn);
-    fence_async_smem();
-    __syncthreads();
-    TSTAMP(2);
+    const float gnv = gn_s[col];
+    const float decay = fast_exp(gnv);
+    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2:
+    // the form in which the output and backward kernels consume them (q exp(G) scale = q~ exp(mid) scale)
+    const float hscale = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[col]) * p.scale;
+    // three threads drive the asynchronous units side by side
     if (tid == 0) {
       tc_fence_after();
+      TSTAMP(11);
       const uint32_t xa = smem_u32(xg), ya = smem_u32(ys);
 #pragma unroll
       for (int k0 = 0; k0 < C; k0 += 16)
-        umma_bf16(tm, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
-      umma_commit(&mma_bar);
+        umma_bf16(tm + cS, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
+      TSTAMP(12);
+      umma_commit(&sbar);
+      TSTAMP(13);
+    } else if (tid == 32) {
+      if (step + 1 < NT) {
+        if (!mbar_wait(&full[(step + 1) & 1], ((step + 1) >> 1) & 1)) { abort_flag = 1; fail(1); }
+        tc_fence_after();
+        issue_gate_mma(step + 1);
+      }
+    } else if (tid == 64) {
+      if (step + 2 < NT) issue_xg(step + 2);
     }
+    __syncwarp();   // the other lanes of an issuing warp must not spin on a barrier the issuer still has to feed
+    TSTAMP(2);
     // record the state this chunk starts from (bf16), while the tensor core works
     {
       __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + col) * D + vh * 64 + seg * SEG;
 #pragma unroll
       for (int j = 0; j < SEG; j += 8)
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16(S[j], S[j + 1]), pack_bf16(S[j + 2], S[j + 3]),
-                                                        pack_bf16(S[j + 4], S[j + 5]), pack_bf16(S[j + 6], S[j + 7]));
+        *reinterpret_cast<uint4*>(dst + j) =
+            make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
+                       pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
     }
     TSTAMP(3);
-    if (!mbar_wait(&mma_bar, step & 1)) { abort_flag = 1; fail(2); }
+    if (!mbar_wait(&sbar, step & 1)) { abort_flag = 1; fail(2); }
     TSTAMP(4);
     tc_fence_after();
     {
       float d[SEG];
-      tmem_ld16(tmem_addr(tm, (warp & 3) * 32, seg * SEG), d);
+      tmem_ld16(tmem_addr(tm, lane_base, cS + seg * SEG), d);
 #pragma unroll
       for (int t = 0; t < SEG; ++t) S[t] = fmaf(S[t], decay, d[t]);
     }
@@ -222,7 +344,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ Sc
     __syncthreads();
     TSTAMP(5);
     if (abort_flag) { ok = false; break; }
-    if (tid == 0 && step + 2 < NT) issue(step + 2);
+    if (tid == 96 && step + 2 < NT) issue_y(step + 2);
+    __syncwarp();
     TSTAMP(6);
   }
   if (ok && p.s_final) {
@@ -230,9 +353,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ Sc
 #pragma unroll
     for (int j = 0; j < SEG; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
   }
+  TFLUSH();
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tm, 64);
+  if (warp == 0) tmem_dealloc(tm, 256);
 }
 
 // masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
@@ -267,17 +391,18 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   uint8_t* ks = qs + TILE64;          // k -> k~ in place
   uint8_t* gs = ks + TILE64;          // g; later the bf16 intra matrix (first 8 KB)
   uint8_t* vs = gs + TILE64;
-  uint8_t* hs = vs + TILE64;          // h_c, 128 x 128; row k scaled in place by exp(mid_k) scale
-  __shared__ uint64_t bar_load, bar_a, bar_o;
+  uint8_t* hs = vs + TILE64;          // h_c exp(mid) scale, 128 x 128 (scaled by the scan kernel)
+  uint8_t* mt = hs + TILE128;         // TRI_MID pattern, 64 x 64
+  __shared__ uint64_t bar_load, bar_e, bar_a, bar_o;
   __shared__ uint32_t tmem_slot;
-  __shared__ float segsum[5][D];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
+  const int q4 = warp & 3, seg = warp >> 2;
   const int ci = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int row = b * p.T + ci * C;
+  constexpr uint32_t cO = 0, cE = 0, cA = 128;   // E is consumed before O is produced
 
   if (tid == 0) {
-    mbar_init(&bar_load, 1); mbar_init(&bar_a, 1); mbar_init(&bar_o, 1);
+    mbar_init(&bar_load, 1); mbar_init(&bar_e, 1); mbar_init(&bar_a, 1); mbar_init(&bar_o, 1);
     fence_barrier_init();
     mbar_expect_tx(&bar_load, 4 * TILE64 + TILE128);
     tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
@@ -287,68 +412,72 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
     const int hrow = ((b * p.NT + ci) * p.H + h) * D;
     tma_load_2d(hs, &p.mh, &bar_load, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &bar_load, 64, hrow);
   }
+  __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  build_tri_tile(mt, 64, TRI_MID);
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
-  const uint32_t lane_base = (warp & 3) * 32;
+  const uint32_t lane_base = q4 * 32;
   bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
   if (!ok) fail(3);
+  if (ok && tid == 0) {
+    tc_fence_after();
+    const uint32_t ga = smem_u32(gs), ma = smem_u32(mt);
+#pragma unroll
+    for (int j0 = 0; j0 < C; j0 += 16)   // E = G - mid, [time][channel]
+      umma_bf16(tm + cE, desc_kmajor(ma, 64, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(64, 128, 0, 1), j0 > 0);
+    umma_commit(&bar_e);
+  }
+  __syncwarp();
   if (ok) {
-    const ColAddr ca = col_prep(64, col);
-    float gv[SEG], prefix, gn;
-    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);
-    const float g0 = segsum[4][col];
-    const float mid = 0.5f * (g0 + gn);
-    float run = prefix;
+    ok = __syncthreads_and(mbar_wait(&bar_e, 0));
+    if (!ok) fail(9);
+  }
+  if (ok) {
+    tc_fence_after();
+    float e[32];
+    tmem_ld32(tmem_addr(tm, lane_base, cE + seg * 32), e);
+    if (lane < 16) {   // rows of an M = 64 accumulator sit in lanes 0..15 of each 32-lane quarter
+      const int i = 16 * q4 + lane;
+      const uint32_t rowoff = (uint32_t)(seg >> 1) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
-    for (int t = 0; t < SEG; ++t) {
-      const int i = seg * SEG + t;
-      run += gv[t];
-      const float e = __expf(run - mid);
-      const float q = ld_bf16(qs, ca.at(i)), k = ld_bf16(ks, ca.at(i));
-      st_bf16(qs, ca.at(i), q * e);
-      st_bf16(ks, ca.at(i), __fdividef(k, e));
-    }
-    // q exp(G) scale = q~ (exp(mid) scale): fold the per-channel factor into row `col` of h_c
-    const float qscale = __expf(mid) * p.scale;
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t off = rowoff + (((uint32_t)((seg & 1) * 4 + u) ^ (uint32_t)i) & 7u) * 16u;
+        float f[8], r[8];
 #pragma unroll
-    for (int c8 = 0; c8 < 32; c8 += 8) {
-      uint4* ph = reinterpret_cast<uint4*>(hs + tile_off(128, col, seg * 32 + c8));
-      uint4 a = *ph;
-      __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&a);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        float2 f = __bfloat1622float2(pa[t]);
-        pa[t] = __floats2bfloat162_rn(f.x * qscale, f.y * qscale);
+        for (int t = 0; t < 8; ++t) { f[t] = fast_exp(e[8 * u + t]); r[t] = fast_exp(-e[8 * u + t]); }
+        *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), f);
+        *reinterpret_cast<uint4*>(ks + off) = scale8(*reinterpret_cast<const uint4*>(ks + off), r);
       }
-      *ph = a;
     }
     fence_async_smem();
+    tc_fence_before();
   }
   __syncthreads();
   if (ok && tid == 0) {
     tc_fence_after();
     const uint32_t qa = smem_u32(qs), ka = smem_u32(ks), ha = smem_u32(hs);
 #pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // A = q~ k~^T  -> columns [0,64)
-      umma_bf16(tm, desc_kmajor(qa, 64, 0, k0), desc_kmajor(ka, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+    for (int k0 = 0; k0 < D; k0 += 16)   // A = q~ k~^T
+      umma_bf16(tm + cA, desc_kmajor(qa, 64, 0, k0), desc_kmajor(ka, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
     umma_commit(&bar_a);
 #pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // o = q~ h'  -> columns [64,192)
-      umma_bf16(tm + 64, desc_kmajor(qa, 64, 0, k0), desc_mnmajor(ha, 128, k0, 0), umma_idesc(64, 128, 0, 1), k0 > 0);
+    for (int k0 = 0; k0 < D; k0 += 16)   // o = q~ h'
+      umma_bf16(tm + cO, desc_kmajor(qa, 64, 0, k0), desc_mnmajor(ha, 128, k0, 0), umma_idesc(64, 128, 0, 1), k0 > 0);
   }
+  __syncwarp();
   if (ok) {
     ok = __syncthreads_and(mbar_wait(&bar_a, 0));
     if (!ok) fail(4);
   }
   if (ok) {
     tc_fence_after();
-    // rows of an M = 64 accumulator sit in lanes 0..15 of each 32-lane quarter
-    const int i = 16 * (warp & 3) + lane;
+    const int i = 16 * q4 + lane;
     float a[16];
-    tmem_ld16(tmem_addr(tm, lane_base, seg * 16), a);
+    tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
     if (lane < 16) store_tril16(gs, i, seg * 16, a, p.scale);
     fence_async_smem();
     tc_fence_before();
@@ -359,19 +488,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
     const uint32_t pa = smem_u32(gs), va = smem_u32(vs);
 #pragma unroll
     for (int k0 = 0; k0 < C; k0 += 16)   // o += A v
-      umma_bf16(tm + 64, desc_kmajor(pa, 64, 0, k0), desc_mnmajor(va, 64, k0, 0), umma_idesc(64, 128, 0, 1), 1);
+      umma_bf16(tm + cO, desc_kmajor(pa, 64, 0, k0), desc_mnmajor(va, 64, k0, 0), umma_idesc(64, 128, 0, 1), 1);
     umma_commit(&bar_o);
   }
+  __syncwarp();
   if (ok) {
     ok = __syncthreads_and(mbar_wait(&bar_o, 0));
     if (!ok) fail(5);
   }
   if (ok) {
     tc_fence_after();
-    const int i = 16 * (warp & 3) + lane;
+    const int i = 16 * q4 + lane;
     __nv_bfloat16* dst = p.o + ((size_t)(row + i) * p.H + h) * D + seg * 32;
     float a[32];
-    tmem_ld32(tmem_addr(tm, lane_base, 64 + seg * 32), a);
+    tmem_ld32(tmem_addr(tm, lane_base, cO + seg * 32), a);
     if (lane < 16) {
 #pragma unroll
       for (int t = 0; t < 32; t += 8)
@@ -442,7 +572,10 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   uint32_t qk[SEG];   // packed bf16 (q, k)
   float gv[SEG];
   float mid = 0.f, gn = 0.f, gend = 0.f;
+  TDECL();
+  TSTART();
   bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
+  TSTAMP(8);
   if (!ok) fail(6);
   if (ok) {
     const ColAddr ca = col_prep(64, col);
@@ -484,6 +617,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     fence_async_smem();
   }
   __syncthreads();
+  TSTAMP(9);
   if (ok && tid == 0) {
     tc_fence_after();
     const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), kga = smem_u32(gs), va = smem_u32(vs), doa = smem_u32(dos),
@@ -505,10 +639,13 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh^T kg^T
       umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kga, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
   }
+  __syncwarp();
+  TSTAMP(10);
   if (ok) {
     ok = __syncthreads_and(mbar_wait(&bar1, 0));
     if (!ok) fail(7);
   }
+  TSTAMP(11);
   if (ok) {
     tc_fence_after();
     const int i = 16 * (warp & 3) + lane;
@@ -521,6 +658,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     tc_fence_before();
   }
   __syncthreads();
+  TSTAMP(12);
   if (ok && tid == 0) {
     tc_fence_after();
     const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
@@ -535,10 +673,12 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
     umma_commit(&bar3);
   }
+  __syncwarp();
   if (ok) {
     ok = __syncthreads_and(mbar_wait(&bar3, 0));
     if (!ok) fail(8);
   }
+  TSTAMP(13);
   float dgl[SEG];
   const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
   const size_t ostride = (size_t)p.H * D;
@@ -552,7 +692,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       for (int t = 0; t < 16; ++t) p.dv[obase + t * ostride] = __float2bfloat16_rn(a[t]);
     }
     // dq, dk and the local suffix sums of the gate gradient, walking time backwards
-    const float c1 = p.scale * __expf(mid), c2 = __expf(gn - mid);
+    const float c2 = __expf(gn - mid);   // (the stored states already carry exp(mid) scale)
     float grun = gend, run = 0.f, tail = 0.f;
 #pragma unroll
     for (int half = 1; half >= 0; --half) {
@@ -567,7 +707,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
         const int t = half * 8 + u;
         const float e = __expf(grun - mid);
         const float r = __fdividef(1.f, e);
-        const float dq = e * fmaf(c1, dq2[u], dq1[u]);
+        const float dq = e * (dq2[u] + dq1[u]);
         const float dkin = r * c2 * dk2[u];
         const float dk = fmaf(r, dk1[u], dkin);
         p.dq[obase + t * ostride] = dq;
@@ -583,16 +723,19 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     part[1][seg][col] = tail;
   }
   __syncthreads();
+  TSTAMP(14);
   if (ok && p.dg) {
     const float later = (seg < 1 ? segsum[1][col] : 0.f) + (seg < 2 ? segsum[2][col] : 0.f) + (seg < 3 ? segsum[3][col] : 0.f);
     const float hdh = part[0][0][col] + part[0][1][col] + part[0][2][col] + part[0][3][col];
     const float tails = part[1][0][col] + part[1][1][col] + part[1][2][col] + part[1][3][col];
-    const float cst = later + tails + __expf(gn) * hdh;
+    const float cst = later + tails + __expf(gn - mid) / p.scale * hdh;
 #pragma unroll
     for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
   }
   tc_fence_before();
   __syncthreads();
+  TSTAMP(15);
+  TFLUSH();
   if (warp == 0) tmem_dealloc(tm, 512);
 }
 
@@ -653,8 +796,8 @@ bool device_is_sm100() {
   return cached == 1;
 }
 
-constexpr size_t SCAN_SMEM = 2 * (2 * TILE64 + SLAB64) + TILE64 + 1024;
-constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + 1024;
+constexpr size_t SCAN_SMEM = 2 * (2 * TILE64 + SLAB64) + TILE64 + SLAB64 + 1024;
+constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
 constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 1024;
 
 template <class F>
@@ -692,6 +835,7 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* 
 bool supported(const tops_chunk_problem& pb) {
   if (pb.dtype != TOPS_BF16 || pb.gate_dtype != TOPS_BF16 || pb.gate_kind != TOPS_GATE_PER_CHANNEL) return false;
   if (pb.K != D || pb.V != D || pb.chunk != C || pb.T % C != 0 || pb.cu_seqlens) return false;
+  if (!(pb.scale > 0.f) || !(pb.scale < 1e30f)) return false;   // states are stored multiplied by scale
   if ((size_t)pb.B * pb.T >= (1u << 31)) return false;
   return device_is_sm100() && encode_fn() != nullptr;
 }
@@ -700,15 +844,15 @@ static size_t state_bytes(const tops_chunk_problem& pb) {
   return align_up((size_t)pb.B * (pb.T / C) * pb.H * D * D * 2);
 }
 
-size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p) { return (p.h_out ? 0 : state_bytes(p.pb)) + 256; }
+size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p) { return (p.saved_out ? 0 : state_bytes(p.pb)) + 256; }
 
 int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st) {
   const tops_chunk_problem& pb = p.pb;
-  if (p.g_cumsum_out || p.A_out) return TOPS_E_UNSUPPORTED;
+  if (p.g_cumsum_out || p.A_out || p.h_out) return TOPS_E_UNSUPPORTED;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.o) ||
       !aligned16(p.h0) || !aligned16(p.ht) || !aligned16(ws))
     return TOPS_E_ALIGN;
-  void* h = p.h_out ? p.h_out : ws;
+  void* h = p.saved_out ? p.saved_out : ws;
   int rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, h, p.ht, st);
   if (rc) return rc;
   FwdOParams fp;

@@ -135,6 +135,11 @@ extern "C" const char* tops_b200_strerror(int code) {
 
 extern "C" int64_t tops_b200_launch_count(void) { return g_launches.load(); }
 
+extern "C" int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb) {
+  if (!pb || check_problem(*pb)) return TOPS_IMPL_GENERIC;
+  return use_sm100(*pb) ? TOPS_IMPL_SM100 : TOPS_IMPL_GENERIC;
+}
+
 extern "C" int tops_b200_device_error(int* out) {
   if (!out) return TOPS_E_NULL;
   return sm100::device_error(out);
@@ -231,7 +236,7 @@ static size_t fwd_layout(const tops_chunk_fwd_params* p, void* ws, cudaStream_t 
 
 extern "C" size_t tops_b200_chunk_fwd_workspace_bytes(const tops_chunk_fwd_params* p) {
   if (!p || check_problem(p->pb)) return 0;
-  if (use_sm100(p->pb) && !p->g_cumsum_out && !p->A_out) return sm100::fwd_workspace_bytes(*p);
+  if (use_sm100(p->pb) && !p->g_cumsum_out && !p->A_out && !p->h_out) return sm100::fwd_workspace_bytes(*p);
   Problem pb;
   return fwd_layout(p, nullptr, nullptr, false, &pb, nullptr, nullptr, nullptr) + 256;
 }
@@ -245,7 +250,7 @@ extern "C" int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* wor
   if (p->pb.impl == TOPS_IMPL_SM100 && !sm100::supported(p->pb)) return TOPS_E_UNSUPPORTED;
   if (!workspace || workspace_bytes < tops_b200_chunk_fwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_sm100(p->pb) && !p->g_cumsum_out && !p->A_out) return sm100::chunk_fwd(*p, workspace, workspace_bytes, st);
+  if (use_sm100(p->pb) && !p->g_cumsum_out && !p->A_out && !p->h_out) return sm100::chunk_fwd(*p, workspace, workspace_bytes, st);
 
   Problem pb;
   float* gcum = nullptr;

@@ -54,7 +54,7 @@ class BwdDhParams(C.Structure):
 
 class ChunkFwdParams(C.Structure):
     _fields_ = [("pb", ChunkProblem), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("h0", _vp), ("o", _vp),
-                ("ht", _vp), ("g_cumsum_out", _vp), ("A_out", _vp), ("h_out", _vp)]
+                ("ht", _vp), ("g_cumsum_out", _vp), ("A_out", _vp), ("h_out", _vp), ("saved_out", _vp)]
 
 
 class ChunkBwdParams(C.Structure):
@@ -82,6 +82,8 @@ lib.tops_b200_strerror.restype = C.c_char_p
 lib.tops_b200_strerror.argtypes = [C.c_int]
 lib.tops_b200_launch_count.restype = C.c_int64
 lib.tops_b200_launch_count.argtypes = []
+lib.tops_b200_chunk_selected_impl.restype = C.c_int
+lib.tops_b200_chunk_selected_impl.argtypes = [C.POINTER(ChunkProblem)]
 lib.tops_b200_device_error.restype = C.c_int
 lib.tops_b200_device_error.argtypes = [C.POINTER(C.c_int)]
 lib.tops_b200_profile_enable.restype = C.c_int

@@ -11,9 +11,11 @@ from .common import make_problem, total_chunks
 
 
 def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqlens=None,
-                   want_gcum=False, want_A=False, want_h=False, impl=L.IMPL_AUTO):
+                   want_gcum=False, want_A=False, want_h=False, impl=L.IMPL_AUTO, want_saved=False):
     """Run tops_b200_chunk_gla_fwd.  Returns (o, ht, g_cumsum, A, h); the last
-    three are None unless asked for."""
+    three are None unless asked for.  With `want_saved` the fifth value is
+    instead the opaque scratch the tcgen05 forward keeps for its backward
+    (None when another kernel family runs): pass it to chunk_bwd_call as `h_saved`."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     dev = q.device
@@ -38,6 +40,10 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
                         cu_seqlens, keep)
     p.q, p.k, p.v, p.g, p.h0, p.o, p.ht = L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(gate), L.ptr(h0), L.ptr(o), L.ptr(ht)
     p.g_cumsum_out, p.A_out, p.h_out = L.ptr(gcum), L.ptr(A), L.ptr(hs)
+    if want_saved and not (want_gcum or want_A or want_h) \
+            and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100:
+        hs = torch.empty(B, nch // B, H, K, V, dtype=k.dtype, device=dev)
+        p.saved_out = L.ptr(hs)
     ws = L.workspace(L.lib.tops_b200_chunk_fwd_workspace_bytes(C.byref(p)), dev)
     L.check(L.lib.tops_b200_chunk_gla_fwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)),
             "chunk_gla_fwd")

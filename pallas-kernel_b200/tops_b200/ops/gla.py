@@ -70,10 +70,10 @@ def chunk_gla_bwd(q, k, v, g, g_cumsum, scale, initial_state, h, A, do, dht, chu
 class _ChunkGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, initial_state, scale, output_final_state, cu, chunk_size):
-        # the chunk-start states are kept for the backward (one bf16 [B,NT,H,K,V] tensor)
+        # the tcgen05 forward keeps its chunk-start states for the backward (one bf16 [B,NT,H,K,V] tensor)
         keep = any(t is not None and t.requires_grad for t in (q, k, v, g, initial_state))
         o, ht, _, _, hs = chunk_fwd_call(q, k, v, g, L.GATE_PER_CHANNEL if g is not None else L.GATE_NONE,
-                                         scale, initial_state, output_final_state, chunk_size, cu, want_h=keep)
+                                         scale, initial_state, output_final_state, chunk_size, cu, want_saved=keep)
         ctx.save_for_backward(q, k, v, g, initial_state, hs)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
         return o, ht
