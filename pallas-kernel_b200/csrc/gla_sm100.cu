@@ -120,14 +120,16 @@ struct ScanParams {
 // Constant 64 x 64 patterns, stored as K-major bf16 tiles, that turn the gate
 // tile g [time j][channel] into exponents with one tensor-core product:
 //   TRI_INCL  L[i][j] = (j <= i)                 -> G_i           (inclusive cumulative gate)
-//   TRI_REV   U[i][j] = (j > i), row 63 all ones  -> G_n - G_i for i < 63 (the exponent of row 63 is 0 and is
-//             not needed from the product), and G_n in row 63
+//   TRI_REV   U[i][j] = (j > i)                  -> G_n - G_i
+//   TRI_REVN  TRI_REV with row 63 all ones       -> G_n - G_i for i < 63 and G_n itself in row 63 (whose own
+//             exponent, 0, needs no product)
 //   TRI_MID   L - 1/2 [j == 0] - 1/2             -> G_i - (G_0 + G_n) / 2
 // All entries (0, 1, +-1/2) are exact in bf16 and the products accumulate in fp32.
-enum { TRI_INCL = 0, TRI_REV = 1, TRI_MID = 2 };
+enum { TRI_INCL = 0, TRI_REV = 1, TRI_MID = 2, TRI_REVN = 3 };
 __device__ __forceinline__ float tri_value(int kind, int i, int j) {
   if (kind == TRI_INCL) return j <= i ? 1.f : 0.f;
-  if (kind == TRI_REV) return (i == 63 || j > i) ? 1.f : 0.f;
+  if (kind == TRI_REV) return j > i ? 1.f : 0.f;
+  if (kind == TRI_REVN) return (i == 63 || j > i) ? 1.f : 0.f;
   return j == 0 ? 0.f : (j <= i ? 0.5f : -0.5f);
 }
 __device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind) {
@@ -191,7 +193,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ Sc
     abort_flag = 0;
   }
   if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
-  build_tri_tile(mt, 64, BWD ? TRI_INCL : TRI_REV);
+  build_tri_tile(mt, 64, BWD ? TRI_INCL : TRI_REVN);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -515,13 +517,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
 }
 
 // ===========================================================================
-// Backward of one chunk
+// Backward of the chunks (persistent: each block walks chunks blockIdx.x,
+// blockIdx.x + gridDim.x, ... and fetches the next chunk's tiles while the
+// tensor core and the epilogue of the current one are still busy)
 // ===========================================================================
 struct BwdParams {
   CUtensorMap mq, mk, mg, mv, mdo, mh, mdh;
   float *dq, *dk, *dg;   // [B,T,H,K] fp32 (dg may be null)
   __nv_bfloat16* dv;     // [B,T,H,V]
-  int T, H, NT;
+  int T, H, NT, total;   // total = B * H * NT chunks
   float scale;
 };
 
@@ -533,157 +537,219 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   uint8_t* gs = ks + TILE64;          // g -> k exp(G_n - G) in place
   uint8_t* vs = gs + TILE64;
   uint8_t* dos = vs + TILE64;
-  uint8_t* hs = dos + TILE64;         // h_c   128 x 128
-  uint8_t* dhs = hs + TILE128;        // dh_c  128 x 128
+  uint8_t* hs = dos + TILE64;         // h_c exp(mid) scale, 128 x 128
+  uint8_t* dhs = hs + TILE128;        // dh_c, 128 x 128
   uint8_t* Ps = dhs + TILE128;        // tril(A) scale, bf16 64 x 64
   uint8_t* dAs = Ps + SLAB64;         // tril(dA) scale, bf16 64 x 64
-  __shared__ uint64_t bar_load, bar1, bar3;
+  uint8_t* mtm = dAs + SLAB64;        // TRI_MID pattern, rows repeated to 128
+  uint8_t* mtr = mtm + 2 * SLAB64;    // TRI_REV pattern, rows repeated to 128
+  __shared__ uint64_t loadA, loadB, bar_e, bar1, bar2, bar3;
   __shared__ uint32_t tmem_slot;
-  __shared__ float segsum[5][D];      // gate segment sums (+ row-0 gate); later suffix-sum partials of dg
-  __shared__ float part[2][4][D];     // [0]: sum_v h dh partials; [1]: sum_i dk_inter k partials
+  __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums   (double-buffered per iteration)
+  __shared__ float part[2][2][4][D];  // [.][0]: sum_v h dh partials; [.][1]: sum_i dk_inter k partials
+  __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int col = (warp & 3) * 32 + lane, seg = warp >> 2;
-  const int ci = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int row = b * p.T + ci * C;
+  const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
+  // tensor-memory columns; the exponent tiles are consumed before the accumulators that share their columns
+  constexpr uint32_t cEm = 0, cEr = 128, cET = 448;
+  constexpr uint32_t cdq2 = 0, cdk2 = 64, cdv = 128, cdq1 = 192, cA = 256, cdA = 320, cdk1 = 384;
+
+  auto chunk_rows = [&](int cid, int& h, int& row, int& hrow) {
+    const int ci = cid % p.NT, bh = cid / p.NT, b = bh / p.H;
+    h = bh % p.H;
+    row = b * p.T + ci * C;
+    hrow = ((b * p.NT + ci) * p.H + h) * D;
+  };
+  auto issue_A = [&](int cid) {   // tiles whose buffers are free once the first batch of products is done
+    int h, row, hrow;
+    chunk_rows(cid, h, row, hrow);
+    mbar_expect_tx(&loadA, 2 * TILE128 + 2 * TILE64);
+    tma_load_3d(gs, &p.mg, &loadA, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &loadA, 64, h, row);
+    tma_load_2d(hs, &p.mh, &loadA, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &loadA, 64, hrow);
+    tma_load_2d(dhs, &p.mdh, &loadA, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &loadA, 64, hrow);
+    tma_load_3d(vs, &p.mv, &loadA, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &loadA, 64, h, row);
+  };
+  auto issue_B = [&](int cid) {   // tiles still read by the second batch
+    int h, row, hrow;
+    chunk_rows(cid, h, row, hrow);
+    mbar_expect_tx(&loadB, 3 * TILE64);
+    tma_load_3d(qs, &p.mq, &loadB, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &loadB, 64, h, row);
+    tma_load_3d(ks, &p.mk, &loadB, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &loadB, 64, h, row);
+    tma_load_3d(dos, &p.mdo, &loadB, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &loadB, 64, h, row);
+  };
 
   if (tid == 0) {
-    mbar_init(&bar_load, 1); mbar_init(&bar1, 1); mbar_init(&bar3, 1);
+    mbar_init(&loadA, 1); mbar_init(&loadB, 1); mbar_init(&bar_e, 1);
+    mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_init(&bar3, 1);
     fence_barrier_init();
-    mbar_expect_tx(&bar_load, 5 * TILE64 + 2 * TILE128);
-    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
-    tma_load_3d(qs, &p.mq, &bar_load, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_load, 64, h, row);
-    tma_load_3d(ks, &p.mk, &bar_load, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_load, 64, h, row);
-    const int hrow = ((b * p.NT + ci) * p.H + h) * D;
-    tma_load_2d(hs, &p.mh, &bar_load, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &bar_load, 64, hrow);
-    tma_load_2d(dhs, &p.mdh, &bar_load, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &bar_load, 64, hrow);
-    tma_load_3d(vs, &p.mv, &bar_load, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &bar_load, 64, h, row);
-    tma_load_3d(dos, &p.mdo, &bar_load, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &bar_load, 64, h, row);
+    abort_flag = 0;
+    issue_A(blockIdx.x);
+    issue_B(blockIdx.x);
   }
+  __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  build_tri_tile(mtm, 128, TRI_MID);
+  build_tri_tile(mtr, 128, TRI_REV);
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
-  const uint32_t lane_base = (warp & 3) * 32;
-  // tensor-memory columns
-  constexpr uint32_t cA = 0, cdA = 64, cdq2 = 128, cdk2 = 192, cdv = 256, cdq1 = 320, cdk1 = 384;
-
-  // values of this thread's 16 (time, channel) elements, kept for the epilogue
-  uint32_t qk[SEG];   // packed bf16 (q, k)
-  float gv[SEG];
-  float mid = 0.f, gn = 0.f, gend = 0.f;
+  const uint32_t lane_base = q4 * 32;
+  const ColAddr ca = col_prep(64, col);
+  bool ok = true;
   TDECL();
-  TSTART();
-  bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
-  TSTAMP(8);
-  if (!ok) fail(6);
-  if (ok) {
-    const ColAddr ca = col_prep(64, col);
-    float prefix;
-    gate_scan(gs, ca, seg, col, segsum, gv, prefix, gn);
-    const float g0 = segsum[4][col];
-    mid = 0.5f * (g0 + gn);
-    const float tail = __expf(gn - mid);
-    float run = prefix;
+
+  for (int cid = blockIdx.x, it = 0; cid < p.total; cid += gridDim.x, ++it) {
+    const uint32_t ph = it & 1;
+    const int nxt = cid + gridDim.x;
+    int h, row, hrow;
+    chunk_rows(cid, h, row, hrow);
+    TSTART();
+    if (!mbar_wait(&loadA, ph) || !mbar_wait(&loadB, ph)) { abort_flag = 1; fail(6); }
+    TSTAMP(8);
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm), mra = smem_u32(mtr);
 #pragma unroll
-    for (int t = 0; t < SEG; ++t) {
-      const int i = seg * SEG + t;
-      run += gv[t];
-      const float e = __expf(run - mid);
-      const float q = ld_bf16(qs, ca.at(i)), k = ld_bf16(ks, ca.at(i));
-      qk[t] = pack_bf16(q, k);
-      const float kn = __fdividef(k, e);
-      st_bf16(qs, ca.at(i), q * e);
-      st_bf16(ks, ca.at(i), kn);
-      st_bf16(gs, ca.at(i), kn * tail);
+      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
+        umma_bf16(tm + cEm, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // G_n - G, [time (repeated)][channel]
+        umma_bf16(tm + cEr, desc_kmajor(mra, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
+        umma_bf16(tm + cET, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0), umma_idesc(128, 64, 1, 0), j0 > 0);
+      umma_commit(&bar_e);
     }
-    gend = run;
-    // partial of sum_v h[k][v] dh[k][v] for k = col over v in [32 seg, 32 seg + 32)
-    float hd = 0.f;
+    __syncwarp();
+    // partial of sum_v h'[k][v] dh[k][v] for k = col over v in [32 seg, 32 seg + 32), while the tensor core works
+    {
+      float hd = 0.f;
 #pragma unroll
-    for (int c8 = 0; c8 < 32; c8 += 8) {
-      const uint32_t off = tile_off(128, col, seg * 32 + c8);
-      const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
-      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-      const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
+      for (int c8 = 0; c8 < 32; c8 += 8) {
+        const uint32_t off = tile_off(128, col, seg * 32 + c8);
+        const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
-        hd = fmaf(fa.x, fd.x, hd);
-        hd = fmaf(fa.y, fd.y, hd);
+        for (int t = 0; t < 4; ++t) {
+          const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
+          hd = fmaf(fa.x, fd.x, hd);
+          hd = fmaf(fa.y, fd.y, hd);
+        }
+      }
+      part[ph][0][seg][col] = hd;
+    }
+    if (!mbar_wait(&bar_e, ph)) { abort_flag = 1; fail(9); }
+    tc_fence_after();
+    TSTAMP(9);
+    {
+      // gate q, k: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
+      const int i = (q4 * 32 + lane) & 63;
+      const int cg = (q4 >> 1) * 4 + seg;
+      float em[16], er[16];
+      tmem_ld16(tmem_addr(tm, lane_base, cEm + cg * 16), em);
+      tmem_ld16(tmem_addr(tm, lane_base, cEr + cg * 16), er);
+      const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+        float f[8], r[8], w[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          f[t] = fast_exp(em[8 * u + t]);
+          r[t] = fast_exp(-em[8 * u + t]);
+          w[t] = fast_exp(er[8 * u + t]);
+        }
+        const uint4 kv = *reinterpret_cast<const uint4*>(ks + off);
+        *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), f);
+        *reinterpret_cast<uint4*>(ks + off) = scale8(kv, r);
+        *reinterpret_cast<uint4*>(gs + off) = scale8(kv, w);
       }
     }
-    part[0][seg][col] = hd;
-    fence_async_smem();
-  }
-  __syncthreads();
-  TSTAMP(9);
-  if (ok && tid == 0) {
-    tc_fence_after();
-    const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), kga = smem_u32(gs), va = smem_u32(vs), doa = smem_u32(dos),
-                   ha = smem_u32(hs), dha = smem_u32(dhs);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
-      umma_bf16(tm + cA, desc_kmajor(qta, 64, 0, k0), desc_kmajor(kta, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dA[i][j] = do v^T
-      umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
-    umma_commit(&bar1);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h do^T
-      umma_bf16(tm + cdq2, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dk_inter^T[k][j] = dh v^T
-      umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh^T kg^T
-      umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kga, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
-  }
-  __syncwarp();
-  TSTAMP(10);
-  if (ok) {
-    ok = __syncthreads_and(mbar_wait(&bar1, 0));
-    if (!ok) fail(7);
-  }
-  TSTAMP(11);
-  if (ok) {
-    tc_fence_after();
-    const int i = 16 * (warp & 3) + lane;
-    float a[16];
-    tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
-    if (lane < 16) store_tril16(Ps, i, seg * 16, a, p.scale);
-    tmem_ld16(tmem_addr(tm, lane_base, cdA + seg * 16), a);
-    if (lane < 16) store_tril16(dAs, i, seg * 16, a, p.scale);
     fence_async_smem();
     tc_fence_before();
-  }
-  __syncthreads();
-  TSTAMP(12);
-  if (ok && tid == 0) {
+    __syncthreads();
+    TSTAMP(10);
+    if (abort_flag) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), kga = smem_u32(gs), va = smem_u32(vs), doa = smem_u32(dos),
+                     ha = smem_u32(hs), dha = smem_u32(dhs);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
+        umma_bf16(tm + cA, desc_kmajor(qta, 64, 0, k0), desc_kmajor(kta, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dA[i][j] = do v^T
+        umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+      umma_commit(&bar1);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
+        umma_bf16(tm + cdq2, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dk_inter^T[k][j] = dh v^T
+        umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh^T kg^T
+        umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kga, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
+      umma_commit(&bar2);
+    }
+    __syncwarp();
+    if (!mbar_wait(&bar1, ph)) { abort_flag = 1; fail(7); }
     tc_fence_after();
-    const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
+    TSTAMP(11);
+    {
+      const int i = 16 * q4 + lane;   // rows of the M = 64 accumulators sit in lanes 0..15 of each quarter
+      float a[16];
+      tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
+      if (lane < 16) store_tril16(Ps, i, seg * 16, a, p.scale);
+      tmem_ld16(tmem_addr(tm, lane_base, cdA + seg * 16), a);
+      if (lane < 16) store_tril16(dAs, i, seg * 16, a, p.scale);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    TSTAMP(12);
+    if (abort_flag) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
 #pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dq_intra^T[k][i] = sum_j k~[j][k] dA[i][j]
-      umma_bf16(tm + cdq1, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
+      for (int k0 = 0; k0 < C; k0 += 16)   // dq_intra^T[k][i] = sum_j k~[j][k] dA[i][j]
+        umma_bf16(tm + cdq1, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
 #pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
-      umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
+      for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
+        umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
 #pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] += sum_i do[i][v] A[i][j]
-      umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
-    umma_commit(&bar3);
-  }
-  __syncwarp();
-  if (ok) {
-    ok = __syncthreads_and(mbar_wait(&bar3, 0));
-    if (!ok) fail(8);
-  }
-  TSTAMP(13);
-  float dgl[SEG];
-  const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
-  const size_t ostride = (size_t)p.H * D;
-  if (ok) {
+      for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] += sum_i do[i][v] A[i][j]
+        umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
+      umma_commit(&bar3);
+    } else if (tid == 64) {
+      // h, dh, v and the gated-k tile are dead once the first batch is complete: fetch the next chunk's
+      if (!mbar_wait(&bar2, ph)) { abort_flag = 1; fail(10); }
+      if (nxt < p.total) issue_A(nxt);
+    }
+    __syncwarp();
+    // this thread's 16 (time, channel) elements of q~ and k~, kept for the gate gradient
+    uint32_t qk[SEG];
+#pragma unroll
+    for (int t = 0; t < SEG; ++t) {
+      const uint32_t off = ca.at(seg * SEG + t);
+      qk[t] = (uint32_t)*reinterpret_cast<const uint16_t*>(qs + off) |
+              ((uint32_t)*reinterpret_cast<const uint16_t*>(ks + off) << 16);
+    }
+    if (!mbar_wait(&bar3, ph)) { abort_flag = 1; fail(8); }
     tc_fence_after();
+    __syncthreads();   // every thread holds its q~, k~ values and all products are complete
+    TSTAMP(13);
+    if (abort_flag) { ok = false; break; }
+    if (tid == 96 && nxt < p.total) issue_B(nxt);
+    __syncwarp();
+
+    float dgl[SEG];
+    const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
+    const size_t ostride = (size_t)p.H * D;
     // dv: this thread owns value channel `col`, time steps of its segment
     {
       float a[16];
@@ -692,12 +758,13 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       for (int t = 0; t < 16; ++t) p.dv[obase + t * ostride] = __float2bfloat16_rn(a[t]);
     }
     // dq, dk and the local suffix sums of the gate gradient, walking time backwards
-    const float c2 = __expf(gn - mid);   // (the stored states already carry exp(mid) scale)
-    float grun = gend, run = 0.f, tail = 0.f;
+    const float c2 = fast_exp(tmem_ld1(tmem_addr(tm, lane_base, cET + 63)));   // exp(G_n - mid)
+    float run = 0.f, tail = 0.f;
 #pragma unroll
     for (int half = 1; half >= 0; --half) {
-      float dq1[8], dq2[8], dk1[8], dk2[8];
+      float dq1[8], dq2[8], dk1[8], dk2[8], et[8];
       const uint32_t c0 = seg * 16 + half * 8;
+      tmem_ld8(tmem_addr(tm, lane_base, cET + c0), et);
       tmem_ld8(tmem_addr(tm, lane_base, cdq1 + c0), dq1);
       tmem_ld8(tmem_addr(tm, lane_base, cdq2 + c0), dq2);
       tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
@@ -705,37 +772,39 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
 #pragma unroll
       for (int u = 7; u >= 0; --u) {
         const int t = half * 8 + u;
-        const float e = __expf(grun - mid);
-        const float r = __fdividef(1.f, e);
-        const float dq = e * (dq2[u] + dq1[u]);
-        const float dkin = r * c2 * dk2[u];
-        const float dk = fmaf(r, dk1[u], dkin);
-        p.dq[obase + t * ostride] = dq;
-        p.dk[obase + t * ostride] = dk;
-        const float2 qkf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qk[t]));
-        run += qkf.x * dq - qkf.y * dk;
-        tail = fmaf(dkin, qkf.y, tail);
+        const float e = fast_exp(et[u]), r = fast_exp(-et[u]);
+        const float dqs = dq1[u] + dq2[u];              // dq exp(mid - G)
+        const float dki = c2 * dk2[u];                  // dk_inter exp(G - mid)
+        const float dks = dk1[u] + dki;                 // dk exp(G - mid)
+        p.dq[obase + t * ostride] = e * dqs;
+        p.dk[obase + t * ostride] = r * dks;
+        const float qt = __uint_as_float(qk[t] << 16), kt = __uint_as_float(qk[t] & 0xffff0000u);
+        run += qt * dqs - kt * dks;                     // q dq - k dk
+        tail = fmaf(dki, kt, tail);                     // dk_inter k
         dgl[t] = run;
-        grun -= gv[t];
       }
     }
-    segsum[seg][col] = run;
-    part[1][seg][col] = tail;
-  }
-  __syncthreads();
-  TSTAMP(14);
-  if (ok && p.dg) {
-    const float later = (seg < 1 ? segsum[1][col] : 0.f) + (seg < 2 ? segsum[2][col] : 0.f) + (seg < 3 ? segsum[3][col] : 0.f);
-    const float hdh = part[0][0][col] + part[0][1][col] + part[0][2][col] + part[0][3][col];
-    const float tails = part[1][0][col] + part[1][1][col] + part[1][2][col] + part[1][3][col];
-    const float cst = later + tails + __expf(gn - mid) / p.scale * hdh;
+    sufsum[ph][seg][col] = run;
+    part[ph][1][seg][col] = tail;
+    tc_fence_before();
+    __syncthreads();   // also: every tensor-memory read of this chunk is done before the next products overwrite it
+    TSTAMP(14);
+    if (p.dg) {
+      const float later = (seg < 1 ? sufsum[ph][1][col] : 0.f) + (seg < 2 ? sufsum[ph][2][col] : 0.f) +
+                          (seg < 3 ? sufsum[ph][3][col] : 0.f);
+      const float hdh = part[ph][0][0][col] + part[ph][0][1][col] + part[ph][0][2][col] + part[ph][0][3][col];
+      const float tails = part[ph][1][0][col] + part[ph][1][1][col] + part[ph][1][2][col] + part[ph][1][3][col];
+      // exp(G_n) sum_v h dh with h = h' / (exp(mid) scale)
+      const float cst = later + tails + c2 / p.scale * hdh;
 #pragma unroll
-    for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
+      for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
+    }
+    TSTAMP(15);
   }
+  TFLUSH();
+  (void)ok;
   tc_fence_before();
   __syncthreads();
-  TSTAMP(15);
-  TFLUSH();
   if (warp == 0) tmem_dealloc(tm, 512);
 }
 
@@ -782,6 +851,16 @@ int state_map(CUtensorMap* m, const void* ptr, size_t rows) {
   return r == CUDA_SUCCESS ? TOPS_OK : TOPS_E_CUDA;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 148;
+  }
+  return n;
+}
+
 bool device_is_sm100() {
   static int cached = -1;
   if (cached < 0) {
@@ -798,7 +877,7 @@ bool device_is_sm100() {
 
 constexpr size_t SCAN_SMEM = 2 * (2 * TILE64 + SLAB64) + TILE64 + SLAB64 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
-constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 1024;
+constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 4 * SLAB64 + 1024;
 
 template <class F>
 int opt_in_smem(F f, size_t bytes) {
@@ -899,9 +978,11 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
     return rc;
   bp.dq = reinterpret_cast<float*>(p.dq); bp.dk = reinterpret_cast<float*>(p.dk); bp.dg = p.dg;
   bp.dv = reinterpret_cast<__nv_bfloat16*>(p.dv); bp.T = pb.T; bp.H = pb.H; bp.NT = NT; bp.scale = pb.scale;
+  bp.total = NT * pb.B * pb.H;
   if ((rc = opt_in_smem(k_bwd_main, BWD_SMEM))) return rc;
+  const int grid = bp.total < sm_count() ? bp.total : sm_count();
   KernelScope ks("sm100_bwd_main", st);
-  k_bwd_main<<<dim3(NT, pb.B * pb.H), NTHREADS, BWD_SMEM, st>>>(bp);
+  k_bwd_main<<<grid, NTHREADS, BWD_SMEM, st>>>(bp);
   return post_launch();
 }
 
