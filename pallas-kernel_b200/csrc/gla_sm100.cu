@@ -623,6 +623,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       umma_commit(&bar_e);
     }
     __syncwarp();
+    TSTAMP(0);
     // partial of sum_v h'[k][v] dh[k][v] for k = col over v in [32 seg, 32 seg + 32), while the tensor core works
     {
       float hd = 0.f;
@@ -641,6 +642,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       }
       part[ph][0][seg][col] = hd;
     }
+    TSTAMP(1);
     if (!mbar_wait(&bar_e, ph)) { abort_flag = 1; fail(9); }
     tc_fence_after();
     TSTAMP(9);
@@ -696,6 +698,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       umma_commit(&bar2);
     }
     __syncwarp();
+    TSTAMP(2);
     if (!mbar_wait(&bar1, ph)) { abort_flag = 1; fail(7); }
     tc_fence_after();
     TSTAMP(11);
@@ -739,7 +742,9 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       qk[t] = (uint32_t)*reinterpret_cast<const uint16_t*>(qs + off) |
               ((uint32_t)*reinterpret_cast<const uint16_t*>(ks + off) << 16);
     }
+    TSTAMP(3);
     if (!mbar_wait(&bar3, ph)) { abort_flag = 1; fail(8); }
+    TSTAMP(4);
     tc_fence_after();
     __syncthreads();   // every thread holds its q~, k~ values and all products are complete
     TSTAMP(13);
