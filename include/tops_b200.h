@@ -37,7 +37,8 @@ enum {
   TOPS_E_WORKSPACE = -4,   /* workspace missing or too small */
   TOPS_E_CUDA = -5,        /* a CUDA runtime / driver call failed */
   TOPS_E_UNSUPPORTED = -6, /* valid request that no kernel covers */
-  TOPS_E_ALIGN = -7        /* a pointer is not 16-byte aligned */
+  TOPS_E_ALIGN = -7,       /* a pointer is not 16-byte aligned */
+  TOPS_E_STATIC_LIMIT = -8 /* the problem needs more scratch than the built-in static buffer holds */
 };
 
 enum { TOPS_F32 = 0, TOPS_BF16 = 1, TOPS_F16 = 2 };
@@ -170,6 +171,35 @@ int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb);
 size_t tops_b200_chunk_fwd_workspace_bytes(const tops_chunk_fwd_params* p);
 int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* workspace, size_t workspace_bytes,
                             void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_gla_fwd without a caller-provided workspace.  This entry point has no
+ * counterpart in the reference.
+ *
+ * Some hosts of this library cannot give it scratch memory: a runtime that
+ * owns the whole device heap and hands a custom call only its operand and
+ * result buffers (no scratch allocator, no way to call cudaMalloc on its
+ * behalf), or a serving process whose memory pool is carved up at start-up.
+ * For them this variant runs exactly the forward pass of
+ * tops_b200_chunk_gla_fwd (same params, same kernels, same results) with its
+ * scratch (cumulative gates, chunk-start states) in a device array that is
+ * part of the library image: TOPS_STATIC_SCRATCH_BYTES on every GPU that
+ * loads the library, held until the process exits.  Nothing is allocated or
+ * freed, here or in anything it calls.
+ *
+ *  - Problems whose scratch need (tops_b200_chunk_fwd_workspace_bytes) exceeds
+ *    TOPS_STATIC_SCRATCH_BYTES are refused with TOPS_E_STATIC_LIMIT; nothing
+ *    is launched.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the last
+ *    call left there.  The forward pass overwrites every element it later
+ *    reads, so nothing has to be cleared; but two calls whose kernels overlap
+ *    on the GPU (different streams, or different host threads) race on it.
+ *    Serialise them.
+ * ------------------------------------------------------------------------ */
+#define TOPS_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int tops_b200_chunk_gla_fwd_static(const tops_chunk_fwd_params* p, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * chunk_gla_bwd / chunk_simple_gla_bwd — replace

@@ -129,6 +129,7 @@ extern "C" const char* tops_b200_strerror(int code) {
     case TOPS_E_CUDA: return "CUDA call failed";
     case TOPS_E_UNSUPPORTED: return "no kernel covers this request";
     case TOPS_E_ALIGN: return "pointer is not 16-byte aligned";
+    case TOPS_E_STATIC_LIMIT: return "problem needs more scratch than the built-in static buffer holds";
     default: return "unknown error";
   }
 }
@@ -267,6 +268,46 @@ extern "C" int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* wor
   if ((rc = generic::launch_scan(pb, false, p->k, p->v, p->h0, h, 0, p->ht, st))) return rc;
   int round_A = p->pb.gate_kind == TOPS_GATE_PER_CHANNEL || p->pb.gate_kind == TOPS_GATE_NONE;
   return generic::launch_fwd_o(pb, p->q, p->k, p->v, h, 0, p->o, p->A_out, round_A, st);
+}
+
+// ---- forward on the library's own scratch ---------------------------------------
+// Scratch for callers that can neither allocate device memory nor pass a
+// workspace.  In host code this name is only a handle for the runtime: the
+// device address has to be looked up with cudaGetSymbolAddress, per device.
+static __device__ __align__(256) unsigned char g_static_scratch[TOPS_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device (looked up once per device).
+int static_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TOPS_E_CUDA;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return TOPS_E_CUDA;
+    }
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return TOPS_OK;
+}
+}  // namespace
+
+extern "C" int tops_b200_chunk_gla_fwd_static(const tops_chunk_fwd_params* p, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->o) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  const size_t need = tops_b200_chunk_fwd_workspace_bytes(p);
+  if (need == 0 || need > TOPS_STATIC_SCRATCH_BYTES) return TOPS_E_STATIC_LIMIT;
+  void* scratch = nullptr;
+  if ((rc = static_scratch(&scratch))) return rc;
+  return tops_b200_chunk_gla_fwd(p, scratch, TOPS_STATIC_SCRATCH_BYTES, stream);
 }
 
 // ---- backward ---------------------------------------------------------------

@@ -102,6 +102,10 @@ for _name, _ptype, _ws in [
     _f = getattr(lib, _name)
     _f.restype = C.c_int
     _f.argtypes = [C.POINTER(_ptype), _vp, _sz, _vp] if _ws else [C.POINTER(_ptype), _vp]
+lib.tops_b200_chunk_gla_fwd_static.restype = C.c_int
+lib.tops_b200_chunk_gla_fwd_static.argtypes = [C.POINTER(ChunkFwdParams), _vp]
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
+E_STATIC_LIMIT = -8
 for _name, _ptype in [
     ("tops_b200_chunk_fwd_workspace_bytes", ChunkFwdParams),
     ("tops_b200_chunk_bwd_workspace_bytes", ChunkBwdParams),
