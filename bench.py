@@ -271,7 +271,7 @@ def run_b200(args):
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get(top)
+            traffic = json.load(open(tpath)).get(top) if w["B"] == 8 else None
         result["roofline"] = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                               "frac": None if achieved is None else achieved / hbm_peak, "traffic": traffic,
                               "ms_per_launch": per_launch_ms, "peak_source": peak_kind,
