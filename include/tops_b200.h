@@ -281,6 +281,46 @@ size_t tops_b200_fused_recurrent_gla_bwd_workspace_bytes(const tops_recurrent_bw
 int tops_b200_fused_recurrent_gla_bwd(const tops_recurrent_bwd_params* p, void* workspace,
                                       size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * KDA (gated delta rule) forward — replaces the forward of `chunk_kda`
+ * (`tops/ops/kda/chunk.py:193-216`, oracle `tops/cpu/ops/kda/naive.py:121-313`)
+ * and `fused_recurrent_kda` (`tops/ops/kda/fused_recurrent.py:19-105`,
+ * `tops/cpu/ops/kda/naive.py:10-118`):
+ *   S' = S exp(g_t); e = v_t - k_t^T S'; S = S' + beta_t k_t (x) e; o_t = scale q_t^T S.
+ * g is the natural-log decay [B,T,H,K]; beta [B,T,H] in the dtype of q.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V;
+  int32_t dtype;      /* q, k, v, beta, o */
+  int32_t gate_dtype; /* g */
+  float scale;
+  const void *q, *k, *v, *g, *beta;
+  const float* h0; /* [B,H,K,V] or NULL */
+  void* o;
+  float* ht;       /* [B,H,K,V] or NULL */
+} tops_kda_fwd_params;
+int tops_b200_kda_fwd(const tops_kda_fwd_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * KDA backward — replaces `chunk_kda_bwd` (`tops/cpu/ops/kda/chunk_bwd.py:525-668`)
+ * and the explicit recurrent backward (`tops/cpu/ops/kda/fused_recurrent.py:212-418`):
+ * dq, dk, dv, dbeta in the input dtype, dg in the gate dtype (with respect to
+ * the natural-log gate), dh0 fp32 (NULL to skip).  K, V <= 128.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V;
+  int32_t dtype, gate_dtype;
+  float scale;
+  const void *q, *k, *v, *g, *beta;
+  const float* h0;
+  const void* do_;
+  const float* dht; /* NULL: zero */
+  void *dq, *dk, *dv, *dg, *dbeta;
+  float* dh0;
+} tops_kda_bwd_params;
+size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p);
+int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,6 +10,7 @@
 #include "common.cuh"
 #include "gla_generic.cuh"
 #include "gla_sm100.cuh"
+#include "kda.cuh"
 #include "recurrent.cuh"
 
 namespace tops {
@@ -406,4 +407,26 @@ extern "C" int tops_b200_fused_recurrent_gla_bwd(const tops_recurrent_bwd_params
   if (p->cu_seqlens && (p->B != 1 || p->N < 1)) return TOPS_E_BAD_SHAPE;
   if (!workspace || workspace_bytes < recurrent::bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
   return recurrent::bwd(*p, workspace, (cudaStream_t)stream);
+}
+
+// ---- KDA ----------------------------------------------------------------------
+extern "C" int tops_b200_kda_fwd(const tops_kda_fwd_params* p, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->g || !p->beta || !p->o) return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1 || p->K > 256) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
+  return kda::fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p) {
+  return p ? kda::bwd_workspace_bytes(*p) : 0;
+}
+
+extern "C" int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->g || !p->beta || !p->do_ || !p->dq || !p->dk || !p->dv || !p->dg ||
+      !p->dbeta)
+    return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1 || p->K > 128 || p->V > 128) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
+  if (!workspace || workspace_bytes < kda::bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
+  return kda::bwd(*p, workspace, (cudaStream_t)stream);
 }

@@ -78,6 +78,19 @@ class RecurrentBwdParams(C.Structure):
                 ("N", _i32)]
 
 
+class KdaFwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp),
+                ("beta", _vp), ("h0", _vp), ("o", _vp), ("ht", _vp)]
+
+
+class KdaBwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp),
+                ("beta", _vp), ("h0", _vp), ("do_", _vp), ("dht", _vp), ("dq", _vp), ("dk", _vp), ("dv", _vp),
+                ("dg", _vp), ("dbeta", _vp), ("dh0", _vp)]
+
+
 lib.tops_b200_strerror.restype = C.c_char_p
 lib.tops_b200_strerror.argtypes = [C.c_int]
 lib.tops_b200_launch_count.restype = C.c_int64
@@ -98,6 +111,8 @@ for _name, _ptype, _ws in [
     ("tops_b200_chunk_gla_bwd", ChunkBwdParams, True),
     ("tops_b200_fused_recurrent_gla_fwd", RecurrentFwdParams, False),
     ("tops_b200_fused_recurrent_gla_bwd", RecurrentBwdParams, True),
+    ("tops_b200_kda_fwd", KdaFwdParams, False),
+    ("tops_b200_kda_bwd", KdaBwdParams, True),
 ]:
     _f = getattr(lib, _name)
     _f.restype = C.c_int
@@ -110,6 +125,7 @@ for _name, _ptype in [
     ("tops_b200_chunk_fwd_workspace_bytes", ChunkFwdParams),
     ("tops_b200_chunk_bwd_workspace_bytes", ChunkBwdParams),
     ("tops_b200_fused_recurrent_gla_bwd_workspace_bytes", RecurrentBwdParams),
+    ("tops_b200_kda_bwd_workspace_bytes", KdaBwdParams),
 ]:
     _f = getattr(lib, _name)
     _f.restype = _sz
