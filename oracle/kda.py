@@ -70,16 +70,12 @@ def naive_chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_fin
     beta = beta.to(acc).permute(0, 2, 1).reshape(B, H, NT, C)
     q = q * scale
     G = g.cumsum(3)
-    # A0[c,i] = sum_k k_c exp(G_c - G_i) k_i
-    A = torch.zeros(B, H, NT, C, C, dtype=acc)
-    for i in range(C):
-        A[..., i] = torch.einsum("bhnck,bhnk->bhnc", k * torch.exp(G - G[..., i:i + 1, :]), k[..., i, :])
-    A = A * beta[..., None]
-    upper = torch.triu(torch.ones(C, C, dtype=torch.bool))
-    A = torch.where(upper, torch.zeros((), dtype=acc), -A)
-    for i in range(1, C):
-        A[..., i, :i] = A[..., i, :i] + torch.einsum("bhnm,bhnmj->bhnj", A[..., i, :], A[..., :, :i])
-    A = (A + torch.eye(C, dtype=acc)) * beta[..., None, :]
+    # A0[c,i] = beta_c sum_k k_c k_i exp(G_c - G_i), strictly below the diagonal
+    A0 = (k[..., :, None, :] * k[..., None, :, :] * torch.exp(G[..., :, None, :] - G[..., None, :, :])).sum(-1)
+    A0 = torch.tril(A0 * beta[..., None], -1)
+    # (I + A0)^-1 diag(beta): what the reference's row-by-row forward substitution produces (:237-243)
+    eye = torch.eye(C, dtype=acc).expand(A0.shape)
+    A = torch.linalg.solve_triangular(eye + A0, eye, upper=False) * beta[..., None, :]
     w = A @ (torch.exp(G) * k)
     u = A @ v
     S = torch.zeros(B, H, K, V, dtype=acc)
