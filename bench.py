@@ -289,6 +289,11 @@ def cpu_baseline(sample_B, passes, warm=1):
     batch slice of the workload, all host threads."""
     from oracle import gla as G
     from tops_b200.synth import make_inputs
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host core
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except Exception:
+        torch.set_num_threads(os.cpu_count() or 1)
     w = WORKLOADS["gla_train"]
     x = make_inputs(w["seed"], sample_B, w["T"], w["H"], w["K"], w["V"], dtype=getattr(torch, w["dtype"]),
                     with_h0=True, with_grads=True)
