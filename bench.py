@@ -2,7 +2,7 @@
 """Benchmark of the chunked GLA hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload gla_train|decode|simple_gla_long]
+                    [--workload gla_train|decode|simple_gla_long|kda]
 
 One "step" is one forward + backward pass of `chunk_gla` over one synthetic
 batch of the headline configuration (bf16, B=8, T=4096, H=16, K=V=128,
@@ -337,6 +337,69 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_extra(args):
+    """Secondary workloads (BASELINE configs[2..4]) on one GPU: device-resident timing, one JSON line."""
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    from tops_b200 import _lib as L
+    from tops_b200.synth import make_inputs
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    hbm_peak, _, peak_kind = measured_peaks()
+    n0 = L.launch_count()
+    if args.workload == "decode":
+        from tops_b200.ops.gla import fused_recurrent_gla_decode_
+        B, H, K, V = 128, 32, 128, 128
+        x = {k: v.cuda() for k, v in make_inputs(3, B, 1, H, K, V, dtype=torch.bfloat16, with_h0=True).items()}
+        state = x["h0"].clone()
+        ms = timed(lambda: fused_recurrent_gla_decode_(x["q"], x["k"], x["v"], x["g"], state), max(args.steps, 200), 20)
+        nbytes = 2 * B * H * K * V * 4
+        out = {"metric": "fused_recurrent_gla decode GB/s (state read+write)", "value": nbytes / (ms * 1e-3) / 1e9,
+               "unit": "GB/s", "ms_per_step": ms, "config": {"workload": "decode B=128 H=32 K=V=128, 1 token per call, fp32 state in place"},
+               "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                            "frac": nbytes / (ms * 1e-3) / 1e9 / hbm_peak, "peak_source": peak_kind}}
+    elif args.workload == "simple_gla_long":
+        from tops_b200.ops.simple_gla import chunk_simple_gla_bwd, chunk_simple_gla_fwd
+        B, T, H, K, V = 1, args.seq or 65536, 32, 128, 128
+        x = {k: v.cuda() for k, v in make_inputs(4, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True,
+                                                   with_grads=True).items()}
+        sc = K ** -0.5
+
+        def step():
+            chunk_simple_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, sc, x["h0"], True, 64)
+            chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"], x["dht"], sc, 64)
+        ms = timed(step, args.steps, 2)
+        out = {"metric": "simple_gla chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+               "config": {"workload": f"simple_gla B=1 T={T} H=32 K=V=128 chunk 64 bf16 (bf16 gate), one GPU"}}
+    else:
+        from tops_b200.ops.kda import kda_bwd, kda_fwd
+        B, T, H, K, V = 4, args.seq or 8192, 32, 128, 128
+        x = {k: v.cuda() for k, v in make_inputs(5, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_grads=True,
+                                                   with_beta=True, l2norm_qk=True).items()}
+        sc = K ** -0.5
+
+        def step():
+            kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], sc, x["h0"], True)
+            kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], sc, x["h0"], x["dht"])
+        ms = timed(step, min(args.steps, 3), 1)
+        out = {"metric": "KDA fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+               "config": {"workload": f"KDA B=4 T={T} H=32 K=V=128 bf16, one GPU (token-serial kernels)"}}
+    out["gpu_launches"] = L.launch_count() - n0
+    out["n_gpus"] = 1
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -345,6 +408,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=0, help="override B (profiler captures on a smaller case)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timed steps only, short JSON")
+    ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda"],
+                    help="gla_train is the headline metric; the others are secondary one-GPU measurements")
+    ap.add_argument("--seq", type=int, default=0, help="override T of a secondary workload")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
@@ -352,7 +418,9 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
                os.path.abspath(__file__), *sys.argv[1:]]
         sys.exit(subprocess.call(cmd))
-    if args.impl == "reference":
+    if args.workload != "gla_train":
+        run_extra(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

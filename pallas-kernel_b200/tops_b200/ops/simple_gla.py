@@ -51,12 +51,27 @@ def _cu(cu_seqlens):
     return None if cu_seqlens is None else [int(x) for x in cu_seqlens]
 
 
+def _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
+    """True when the tcgen05 GLA kernels can serve this scalar-gate problem: a scalar
+    gate is a per-channel gate with the same value on all 128 channels, so the bf16
+    gate is replicated over K and the per-channel gate gradient summed over K."""
+    return (g is not None and g_gamma is None and cu_seqlens is None and chunk_size == 64
+            and q.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
+            and q.shape[-1] == 128 and v.shape[-1] == 128 and q.shape[1] % 64 == 0)
+
+
+def _expand_gate(g, K):
+    return g.unsqueeze(-1).expand(*g.shape, K).contiguous()
+
+
 def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
                          cu_seqlens=None):
     """Forward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:53-129`).
     Returns (o in v.dtype, ht fp32 or None)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
+    if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
+        gate, kind = _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL
     o, ht, _, _, _ = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
                                     _cu(cu_seqlens))
     return o, ht
@@ -68,6 +83,11 @@ def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chu
     None, dh0 fp32 or None)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
+    if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
+        dq, dk, dv, dgk, dh0 = chunk_bwd_call(q, k, v, _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale,
+                                              initial_state, do, dht, chunk_size, torch.float32, True,
+                                              initial_state is not None)
+        return dq.to(q.dtype), dk.to(k.dtype), dv, dgk.sum(-1), dh0
     return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
                           g is not None, initial_state is not None, _cu(cu_seqlens))
 
@@ -75,9 +95,7 @@ def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chu
 class _ChunkSimpleGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, g_gamma, initial_state, scale, output_final_state, cu, chunk_size):
-        gate, kind = _gate(g, g_gamma)
-        o, ht, _, _, _ = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state,
-                                        chunk_size, cu)
+        o, ht = chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu)
         ctx.save_for_backward(q, k, v, g, g_gamma, initial_state)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
         return o, ht
@@ -85,9 +103,8 @@ class _ChunkSimpleGLA(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dht):
         q, k, v, g, g_gamma, h0 = ctx.saved_tensors
-        gate, kind = _gate(g, g_gamma)
-        dq, dk, dv, dg, dh0 = chunk_bwd_call(q, k, v, gate, kind, ctx.scale, h0, do.to(q.dtype), dht, ctx.chunk,
-                                             q.dtype, g is not None, h0 is not None, ctx.cu)
+        dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(q, k, v, g, g_gamma, h0, do.to(q.dtype), dht, ctx.scale, ctx.chunk,
+                                                   ctx.cu)
         # a constant decay gets a zero cotangent, as in the reference (tops/ops/simple_gla/chunk.py:764)
         dgamma = None if g_gamma is None else torch.zeros_like(g_gamma)
         return (dq, dk, dv, None if g is None else dg.to(g.dtype), dgamma,

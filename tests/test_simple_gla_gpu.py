@@ -99,3 +99,31 @@ def test_chunk_simple_gla_varlen():
                                chunk_size=C, cu_seqlens=cu)
     for name, a, b in zip(("dq", "dk", "dv", "dg", "dh0"), got, ref):
         assert_close(name, a, b, torch.float32)
+
+
+def test_scalar_gate_on_tensor_core_kernels():
+    """bf16 scalar gates with K = V = 128, chunk 64 run on the tcgen05 GLA kernels
+    (gate replicated over the channels, gate gradient summed over them)."""
+    from tops_b200 import _lib as L
+    from tops_b200.ops.simple_gla import chunk_simple_gla, chunk_simple_gla_bwd
+    from tops_b200.synth import make_inputs
+    B, T, H, K, V, C = 1, 512, 2, 128, 128, 64
+    x = make_inputs(24, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
+    assert x["g"].dtype == torch.bfloat16
+    scale = K ** -0.5
+    o_ref, ht_ref = O.chunk_simple_gla(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True, chunk_size=C)
+    ref = O.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"], x["dht"], scale, chunk_size=C)
+    c = to_cuda(x)
+    L.lib.tops_b200_profile_enable(1)
+    o, ht = chunk_simple_gla(c["q"], c["k"], c["v"], c["g"], None, scale, c["h0"], True, chunk_size=C)
+    got = chunk_simple_gla_bwd(c["q"], c["k"], c["v"], c["g"], None, c["h0"], c["do"], c["dht"], scale, chunk_size=C)
+    L.lib.tops_b200_profile_enable(0)
+    import ctypes
+    buf = ctypes.create_string_buffer(4096)
+    L.lib.tops_b200_profile_read(buf, len(buf))
+    assert all(ln.startswith("sm100_") for ln in buf.value.decode().splitlines()), buf.value
+    assert_close("o", o, o_ref, torch.bfloat16)
+    assert_close("ht", ht, ht_ref, torch.bfloat16)
+    assert got[0].dtype == torch.bfloat16 and got[3].shape == (B, T, H)
+    for name, a, b in zip(("dq", "dk", "dv", "dg", "dh0"), got, ref):
+        assert_close(name, a, b, torch.bfloat16)
