@@ -26,6 +26,7 @@ CASES = {
     "gla_bf16": dict(op="gla", seed=102, B=1, T=128, H=2, K=64, V=64, C=64, dtype="bfloat16", h0=True),
     "simple_gla_fp32": dict(op="simple_gla", seed=103, B=2, T=50, H=2, K=32, V=32, C=16, dtype="float32", h0=True),
     "recurrent_fp32": dict(op="recurrent", seed=104, B=2, T=24, H=2, K=32, V=16, dtype="float32", h0=True),
+    "kda_fp32": dict(op="kda", seed=105, B=1, T=40, H=2, K=32, V=32, dtype="float32", h0=True),
 }
 
 
@@ -34,7 +35,7 @@ def case_inputs(c):
     dtype = getattr(torch, c["dtype"])
     gate = "scalar" if c["op"] == "simple_gla" else "per_channel"
     return make_inputs(c["seed"], c["B"], c["T"], c["H"], c["K"], c["V"], dtype=dtype, gate=gate,
-                       with_h0=c["h0"], with_grads=True,
+                       with_h0=c["h0"], with_grads=True, with_beta=c["op"] == "kda", l2norm_qk=c["op"] == "kda",
                        gate_dtype=torch.float32 if gate == "scalar" else None)
 
 
@@ -58,6 +59,12 @@ def run_case(c):
         dq, dk, dv, dgk, _, dh0 = G.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], None, None, x["do"], x["dht"],
                                                         scale, x.get("h0"))
         return dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dh0=dh0)
+    if c["op"] == "kda":
+        from oracle import kda as K
+        o, ht = K.naive_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x.get("h0"), True)
+        dq, dk, dv, dg, db, dh0 = K.fused_recurrent_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale,
+                                                            x.get("h0"), x["dht"])
+        return dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db, dh0=dh0)
     raise ValueError(c["op"])
 
 

@@ -31,6 +31,11 @@ def test_kernels_match_golden(name):
         dq, dk, dv, dg, dh0 = simple_gla.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"],
                                                               x["dht"], scale, chunk_size=c["C"])
         got = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+    elif c["op"] == "kda":
+        from tops_b200.ops import kda
+        o, ht = kda.kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+        dq, dk, dv, dg, db, dh0 = kda.kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
+        got = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db, dh0=dh0)
     else:
         o, ht = gla.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True)
         dq, dk, dv, dgk, _, dh0 = gla.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], None, None, x["do"],
