@@ -169,31 +169,62 @@ __device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
   return y;
 }
 
+// One block per (batch, head); the whole K x V state lives in registers
+// (thread (q4, lane, seg): row k = 32 q4 + lane, columns 32 seg .. 32 seg + 31).
+// Software pipeline over the chunks p (in scan order):
+//   iteration p:  store h'_p;  gate x(p+1) in place (exponents E(p+1) from tensor memory);
+//                 __syncthreads;  [thread 0] state product of chunk p+1 -> accumulator (p+1)&1,
+//                 [thread 32] exponent product of chunk p+2;  wait for the state product of chunk p;
+//                 state <- state * exp(G_n(p)) + D(p);  [thread 64] TMA for chunk p+3.
+// so the tensor-core latency of one chunk hides behind the gating of the next, and there is one
+// block-wide barrier per chunk.  x/y tiles: 3 stages, g tiles: 2 stages.
 template <bool BWD>
-__global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ ScanParams p) {
+__global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  constexpr uint32_t STAGE = 2 * TILE64 + SLAB64;  // x, g, y-half
-  uint8_t* xg = smem + 2 * STAGE;                   // gated x, 64 x 128
-  uint8_t* mt = xg + TILE64;                        // exponent pattern, 64 x 64
-  __shared__ uint64_t full[2], ebar, sbar;
-  __shared__ float gn_s[D], e0_s[D];   // row 63 (G_n) and row 0 of the exponent tile, per channel
+  uint8_t* xs = smem;                       // 3 x (64 x 128): x, gated in place
+  uint8_t* ys = xs + 3 * TILE64;            // 3 x (64 x 128): y
+  uint8_t* gs = ys + 3 * TILE64;            // 2 x (64 x 128): g
+  uint8_t* mt = gs + 2 * TILE64;            // exponent pattern, rows repeated to 128
+  __shared__ uint64_t fullg[2], fullxy[3], ebar, sbar[2];
   __shared__ uint32_t tmem_slot;
+  __shared__ float gn_s[2][D], e0_s[2][D];  // row 63 (G_n) and row 0 of the exponent tile, per channel
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
-  const int vh = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
-  constexpr uint32_t cE = 0, cS = 128;   // tensor-memory columns
+  constexpr uint32_t cE = 0, cS = 128;      // tensor-memory columns: exponents, two state-product accumulators
 
+  auto chunk_row = [&](int pp) { return b * p.T + (BWD ? NT - 1 - pp : pp) * C; };
+  auto issue_g = [&](int pp) {
+    uint8_t* dst = gs + (pp & 1) * TILE64;
+    mbar_expect_tx(&fullg[pp & 1], TILE64);
+    tma_load_3d(dst, &p.mg, &fullg[pp & 1], 0, h, chunk_row(pp));
+    tma_load_3d(dst + SLAB64, &p.mg, &fullg[pp & 1], 64, h, chunk_row(pp));
+  };
+  auto issue_xy = [&](int pp) {
+    const int st = pp % 3;
+    mbar_expect_tx(&fullxy[st], 2 * TILE64);
+    tma_load_3d(xs + st * TILE64, &p.mx, &fullxy[st], 0, h, chunk_row(pp));
+    tma_load_3d(xs + st * TILE64 + SLAB64, &p.mx, &fullxy[st], 64, h, chunk_row(pp));
+    tma_load_3d(ys + st * TILE64, &p.my, &fullxy[st], 0, h, chunk_row(pp));
+    tma_load_3d(ys + st * TILE64 + SLAB64, &p.my, &fullxy[st], 64, h, chunk_row(pp));
+  };
   if (tid == 0) {
-    mbar_init(&full[0], 2); mbar_init(&full[1], 2); mbar_init(&ebar, 1); mbar_init(&sbar, 1);
+    mbar_init(&fullg[0], 1); mbar_init(&fullg[1], 1);
+    mbar_init(&fullxy[0], 1); mbar_init(&fullxy[1], 1); mbar_init(&fullxy[2], 1);
+    mbar_init(&ebar, 1); mbar_init(&sbar[0], 1); mbar_init(&sbar[1], 1);
     fence_barrier_init();
     tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
     abort_flag = 0;
+    issue_g(0); issue_xy(0);
+    if (NT > 1) { issue_g(1); issue_xy(1); }
+    if (NT > 2) issue_xy(2);
   }
-  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
-  build_tri_tile(mt, 64, BWD ? TRI_INCL : TRI_REVN);
+  __syncwarp();
+  if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  build_tri_tile(mt, 128, BWD ? TRI_INCL : TRI_REVN);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -201,164 +232,157 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_scan(const __grid_constant__ Sc
   const uint32_t tm = tmem_slot;
   const uint32_t lane_base = q4 * 32;
 
-  auto issue_xg = [&](int step) {
-    const int ci = BWD ? NT - 1 - step : step;
-    uint8_t* st = smem + (step & 1) * STAGE;
-    const int row = b * p.T + ci * C;
-    mbar_expect_tx(&full[step & 1], 2 * TILE64);
-    tma_load_3d(st + TILE64, &p.mg, &full[step & 1], 0, h, row);
-    tma_load_3d(st + TILE64 + SLAB64, &p.mg, &full[step & 1], 64, h, row);
-    tma_load_3d(st, &p.mx, &full[step & 1], 0, h, row);
-    tma_load_3d(st + SLAB64, &p.mx, &full[step & 1], 64, h, row);
-  };
-  auto issue_y = [&](int step) {
-    const int ci = BWD ? NT - 1 - step : step;
-    uint8_t* st = smem + (step & 1) * STAGE;
-    mbar_expect_tx(&full[step & 1], SLAB64);
-    tma_load_3d(st + 2 * TILE64, &p.my, &full[step & 1], vh * 64, h, b * p.T + ci * C);
-  };
-  // exponents E = pattern . g (M = 64) of one stage; row 63 of E is the chunk total G_n
-  auto issue_gate_mma = [&](int step) {
-    const uint32_t ga = smem_u32(smem + (step & 1) * STAGE + TILE64), ma = smem_u32(mt);
+  // exponents E = pattern . g of chunk pp: [time (repeated to 128 lanes)][channel]; row 63 is G_n
+  auto issue_gate_mma = [&](int pp) {
+    const uint32_t ga = smem_u32(gs + (pp & 1) * TILE64), ma = smem_u32(mt);
 #pragma unroll
     for (int j0 = 0; j0 < C; j0 += 16)
-      umma_bf16(tm + cE, desc_kmajor(ma, 64, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(64, 128, 0, 1), j0 > 0);
+      umma_bf16(tm + cE, desc_kmajor(ma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
     umma_commit(&ebar);
   };
-  if (tid == 0) {
-    issue_xg(0); issue_y(0);
-    if (NT > 1) { issue_xg(1); issue_y(1); }
-    if (!mbar_wait(&full[0], 0)) { abort_flag = 1; fail(1); }
-    tc_fence_after();
-    issue_gate_mma(0);
-  }
-  __syncwarp();
-
-  // fp32 state: row k = col, columns vh*64 + 16 seg .. + 15
-  float S[SEG];
-  {
-    const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + vh * 64 + seg * SEG : nullptr;
+  auto issue_state_mma = [&](int pp) {
+    const uint32_t xa = smem_u32(xs + (pp % 3) * TILE64), ya = smem_u32(ys + (pp % 3) * TILE64);
 #pragma unroll
-    for (int j = 0; j < SEG; j += 4) {
+    for (int k0 = 0; k0 < C; k0 += 16)
+      umma_bf16(tm + cS + (pp & 1) * 128, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0),
+                umma_idesc(128, 128, 1, 1), k0 > 0);
+    umma_commit(&sbar[pp & 1]);
+  };
+  // gate x of chunk pp in place and publish G_n (and G_n - G_0) of its channels
+  auto gate_chunk = [&](int pp) {
+    if (!mbar_wait(&ebar, pp & 1) || !mbar_wait(&fullxy[pp % 3], (pp / 3) & 1)) { abort_flag = 1; fail(1); }
+    tc_fence_after();
+    const int i = (q4 * 32 + lane) & 63;          // time row of this thread
+    const int cg = (q4 >> 1) * 4 + seg;           // its 16 channels
+    float e[16];
+    tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), e);
+    if (i == 63) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) gn_s[pp & 1][cg * 16 + t] = e[t];
+      if (!BWD) {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) e[t] = 0.f;   // row 63 of TRI_REVN carries G_n, its own exponent is 0
+      }
+    }
+    if (!BWD && i == 0) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) e0_s[pp & 1][cg * 16 + t] = e[t];
+    }
+#pragma unroll
+    for (int t = 0; t < 16; ++t) e[t] = BWD ? fast_exp(e[t]) * p.scale : fast_exp(e[t]);
+    uint8_t* xt = xs + (pp % 3) * TILE64;
+    const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+      *reinterpret_cast<uint4*>(xt + off) = scale8(*reinterpret_cast<const uint4*>(xt + off), e + 8 * u);
+    }
+    fence_async_smem();
+    tc_fence_before();
+  };
+
+  // fp32 state: row k = col, columns 32 seg .. + 31
+  float S[32];
+  {
+    const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
       float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
       S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
     }
   }
-  bool ok = true;
-  TDECL();
-  for (int step = 0; step < NT; ++step) {
-    const int ci = BWD ? NT - 1 - step : step;
-    const int s = step & 1;
-    uint8_t* xs = smem + s * STAGE;
-    uint8_t* ys = xs + 2 * TILE64;
-    TSTART();
-    if (!mbar_wait(&full[s], (step >> 1) & 1)) { abort_flag = 1; fail(1); }
-    if (!mbar_wait(&ebar, step & 1)) { abort_flag = 1; fail(2); }
+  // prologue: exponents and gating of chunk 0, its state product, exponents of chunk 1
+  if (tid == 0) {
+    if (!mbar_wait(&fullg[0], 0)) { abort_flag = 1; fail(1); }
     tc_fence_after();
-    TSTAMP(0);
-    {
-      // rows of the M = 64 exponent tile sit in lanes 0..15 of each 32-lane quarter
-      float e[32];
-      tmem_ld32(tmem_addr(tm, lane_base, cE + seg * 32), e);
-      TSTAMP(8);
-      if (lane < 16) {
-        const int i = 16 * q4 + lane;
-        if (i == 63) {   // this row carries G_n: the log-decay of the state rows
-#pragma unroll
-          for (int t = 0; t < 32; ++t) gn_s[seg * 32 + t] = e[t];
-          if (!BWD) {
-#pragma unroll
-            for (int t = 0; t < 32; ++t) e[t] = 0.f;
-          }
-        }
-        if (!BWD && i == 0) {   // G_n - G_0, for the mid-point the stored states are scaled by
-#pragma unroll
-          for (int t = 0; t < 32; ++t) e0_s[seg * 32 + t] = e[t];
-        }
-#pragma unroll
-        for (int t = 0; t < 32; ++t) e[t] = fast_exp(e[t]);
-        if (BWD) {
-#pragma unroll
-          for (int t = 0; t < 32; ++t) e[t] *= p.scale;
-        }
-        const uint32_t rowoff = (uint32_t)(seg >> 1) * SLAB64 + (uint32_t)i * 128u;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t off = rowoff + (((uint32_t)((seg & 1) * 4 + u) ^ (uint32_t)i) & 7u) * 16u;
-          *reinterpret_cast<uint4*>(xg + off) = scale8(*reinterpret_cast<const uint4*>(xs + off), e + 8 * u);
-        }
-      }
-    }
-    TSTAMP(9);
-    fence_async_smem();
-    TSTAMP(10);
-    tc_fence_before();
-    __syncthreads();
-    TSTAMP(1);
-    if (abort_flag) { ok = false; break; }
-    const float gnv = gn_s[col];
-    const float decay = fast_exp(gnv);
-    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2:
-    // the form in which the output and backward kernels consume them (q exp(G) scale = q~ exp(mid) scale)
-    const float hscale = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[col]) * p.scale;
-    // three threads drive the asynchronous units side by side
+    issue_gate_mma(0);
+  }
+  __syncwarp();
+  gate_chunk(0);
+  __syncthreads();
+  bool ok = !abort_flag;
+  float decay = 1.f, hscale = 1.f;
+  if (ok) {
+    const float gnv = gn_s[0][col];
+    decay = fast_exp(gnv);
+    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2
+    hscale = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[0][col]) * p.scale;
     if (tid == 0) {
       tc_fence_after();
-      TSTAMP(11);
-      const uint32_t xa = smem_u32(xg), ya = smem_u32(ys);
-#pragma unroll
-      for (int k0 = 0; k0 < C; k0 += 16)
-        umma_bf16(tm + cS, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
-      TSTAMP(12);
-      umma_commit(&sbar);
-      TSTAMP(13);
-    } else if (tid == 32) {
-      if (step + 1 < NT) {
-        if (!mbar_wait(&full[(step + 1) & 1], ((step + 1) >> 1) & 1)) { abort_flag = 1; fail(1); }
-        tc_fence_after();
-        issue_gate_mma(step + 1);
-      }
-    } else if (tid == 64) {
-      if (step + 2 < NT) issue_xg(step + 2);
+      issue_state_mma(0);
+    } else if (tid == 32 && NT > 1) {
+      if (!mbar_wait(&fullg[1], 0)) { abort_flag = 1; fail(1); }
+      tc_fence_after();
+      issue_gate_mma(1);
+    } else if (tid == 64 && NT > 2) {
+      issue_g(2);
     }
-    __syncwarp();   // the other lanes of an issuing warp must not spin on a barrier the issuer still has to feed
-    TSTAMP(2);
-    // record the state this chunk starts from (bf16), while the tensor core works
+    __syncwarp();
+  }
+  TDECL();
+  for (int pp = 0; ok && pp < NT; ++pp) {
+    const int ci = BWD ? NT - 1 - pp : pp;
+    TSTART();
+    // the state this chunk starts from (bf16), in the form its consumers use
     {
-      __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + col) * D + vh * 64 + seg * SEG;
+      __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + col) * D + seg * 32;
 #pragma unroll
-      for (int j = 0; j < SEG; j += 8)
+      for (int j = 0; j < 32; j += 8)
         *reinterpret_cast<uint4*>(dst + j) =
             make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
                        pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
     }
+    TSTAMP(0);
+    if (pp + 1 < NT) gate_chunk(pp + 1);
+    TSTAMP(1);
+    __syncthreads();
+    TSTAMP(2);
+    if (abort_flag) { ok = false; break; }
+    float decay_n = 1.f, hscale_n = 1.f;
+    if (pp + 1 < NT) {
+      const float gnv = gn_s[(pp + 1) & 1][col];
+      decay_n = fast_exp(gnv);
+      hscale_n = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[(pp + 1) & 1][col]) * p.scale;
+      if (tid == 0) {
+        tc_fence_after();
+        issue_state_mma(pp + 1);
+      } else if (tid == 32 && pp + 2 < NT) {
+        if (!mbar_wait(&fullg[(pp + 2) & 1], ((pp + 2) >> 1) & 1)) { abort_flag = 1; fail(1); }
+        tc_fence_after();
+        issue_gate_mma(pp + 2);
+      }
+      __syncwarp();
+    }
     TSTAMP(3);
-    if (!mbar_wait(&sbar, step & 1)) { abort_flag = 1; fail(2); }
-    TSTAMP(4);
+    if (!mbar_wait(&sbar[pp & 1], (pp >> 1) & 1)) { abort_flag = 1; fail(2); }
     tc_fence_after();
+    TSTAMP(4);
     {
-      float d[SEG];
-      tmem_ld16(tmem_addr(tm, lane_base, cS + seg * SEG), d);
+      float d[32];
+      tmem_ld32(tmem_addr(tm, lane_base, cS + (pp & 1) * 128 + seg * 32), d);
 #pragma unroll
-      for (int t = 0; t < SEG; ++t) S[t] = fmaf(S[t], decay, d[t]);
+      for (int t = 0; t < 32; ++t) S[t] = fmaf(S[t], decay, d[t]);
     }
     tc_fence_before();
-    __syncthreads();
     TSTAMP(5);
-    if (abort_flag) { ok = false; break; }
-    if (tid == 96 && step + 2 < NT) issue_y(step + 2);
+    // the x/y stage of chunk pp and the g stage of chunk pp+1 are free now
+    if (tid == 64) {
+      if (pp + 3 < NT) { issue_xy(pp + 3); issue_g(pp + 3); }
+    }
     __syncwarp();
     TSTAMP(6);
-  }
-  if (ok && p.s_final) {
-    float* dst = p.s_final + ((size_t)bh * D + col) * D + vh * 64 + seg * SEG;
-#pragma unroll
-    for (int j = 0; j < SEG; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    decay = decay_n;
+    hscale = hscale_n;
   }
   TFLUSH();
+  if (ok && p.s_final) {
+    float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+  }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tm, 256);
+  if (warp == 0) tmem_dealloc(tm, 512);
 }
 
 // masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
@@ -880,7 +904,7 @@ bool device_is_sm100() {
   return cached == 1;
 }
 
-constexpr size_t SCAN_SMEM = 2 * (2 * TILE64 + SLAB64) + TILE64 + SLAB64 + 1024;
+constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
 constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 4 * SLAB64 + 1024;
 
@@ -901,7 +925,7 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* 
     return rc;
   sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final;
   sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C; sp.scale = pb.scale;
-  dim3 grid(2, pb.B * pb.H);
+  dim3 grid(pb.B * pb.H);
   if (bwd) {
     if ((rc = opt_in_smem(k_scan<true>, SCAN_SMEM))) return rc;
     KernelScope ks("sm100_bwd_dh", st);
