@@ -110,6 +110,7 @@ __device__ __forceinline__ void gate_scan(const uint8_t* gs, const ColAddr& ca, 
 // ===========================================================================
 struct ScanParams {
   CUtensorMap mx, mg, my;  // x: k (fwd) / q (bwd); y: v / do
+  CUtensorMap mst;         // the states tensor as [B*NT*H*128, 128] (TMA stores)
   const float* s0;         // h0 / dht  [B,H,K,V] or null
   __nv_bfloat16* states;   // h / dh    [B,NT,H,K,V]
   float* s_final;          // ht / dh0  or null
@@ -186,6 +187,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
   uint8_t* ys = xs + 3 * TILE64;            // 3 x (64 x 128): y
   uint8_t* gs = ys + 3 * TILE64;            // 2 x (64 x 128): g
   uint8_t* mt = gs + 2 * TILE64;            // exponent pattern, rows repeated to 128
+  uint8_t* hst = mt + 2 * SLAB64;           // 2 x (128 x 128) bf16: chunk-start states on their way to HBM
   __shared__ uint64_t fullg[2], fullxy[3], ebar, sbar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ float gn_s[2][D], e0_s[2][D];  // row 63 (G_n) and row 0 of the exponent tile, per channel
@@ -323,21 +325,31 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
   for (int pp = 0; ok && pp < NT; ++pp) {
     const int ci = BWD ? NT - 1 - pp : pp;
     TSTART();
-    // the state this chunk starts from (bf16), in the form its consumers use
+    // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
+    // memory in the tile format of the states tensor map and written out by a TMA store
     {
-      __nv_bfloat16* dst = p.states + ((((size_t)b * NT + ci) * p.H + h) * D + col) * D + seg * 32;
+      uint8_t* tile = hst + (pp & 1) * TILE128;
 #pragma unroll
       for (int j = 0; j < 32; j += 8)
-        *reinterpret_cast<uint4*>(dst + j) =
+        *reinterpret_cast<uint4*>(tile + tile_off(128, col, seg * 32 + j)) =
             make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
                        pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
+      fence_async_smem();
     }
     TSTAMP(0);
     if (pp + 1 < NT) gate_chunk(pp + 1);
+    if (tid == 96) tma_store_wait_read();   // the store of chunk pp-1 has drained its staging tile
+    __syncwarp();
     TSTAMP(1);
     __syncthreads();
     TSTAMP(2);
     if (abort_flag) { ok = false; break; }
+    if (tid == 96) {
+      const int hrow = ((b * NT + ci) * p.H + h) * D;
+      tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
+      tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
+      tma_store_commit();
+    }
     float decay_n = 1.f, hscale_n = 1.f;
     if (pp + 1 < NT) {
       const float gnv = gn_s[(pp + 1) & 1][col];
@@ -375,6 +387,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     hscale = hscale_n;
   }
   TFLUSH();
+  if (tid == 96) tma_store_wait_all();
   if (ok && p.s_final) {
     float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
 #pragma unroll
@@ -904,7 +917,7 @@ bool device_is_sm100() {
   return cached == 1;
 }
 
-constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 1024;
+constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 2 * TILE128 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
 constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 4 * SLAB64 + 1024;
 
@@ -921,7 +934,8 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* 
   ScanParams sp;
   const int BT = pb.B * pb.T;
   int rc;
-  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.mg, g, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H)))
+  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.mg, g, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H)) ||
+      (rc = state_map(&sp.mst, states, (size_t)pb.B * (pb.T / C) * pb.H * D)))
     return rc;
   sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final;
   sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C; sp.scale = pb.scale;
