@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
         for (int t = 0; t < 16; ++t) e[t] = 0.f;   // row 63 of TRI_REVN carries G_n, its own exponent is 0
       }
     }
-    if (!BWD && i == 0) {
+    if (i == 0) {   // forward: G_n - G_0; reverse: G_0
 #pragma unroll
       for (int t = 0; t < 16; ++t) e0_s[pp & 1][cg * 16 + t] = e[t];
     }
@@ -307,8 +307,9 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
   if (ok) {
     const float gnv = gn_s[0][col];
     decay = fast_exp(gnv);
-    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2
-    hscale = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[0][col]) * p.scale;
+    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2;
+    // reverse states as dh * exp(G_n - mid) = dh * exp((G_n - G_0) / 2)
+    hscale = BWD ? fast_exp(0.5f * (gnv - e0_s[0][col])) : fast_exp(gnv - 0.5f * e0_s[0][col]) * p.scale;
     if (tid == 0) {
       tc_fence_after();
       issue_state_mma(0);
@@ -354,7 +355,8 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     if (pp + 1 < NT) {
       const float gnv = gn_s[(pp + 1) & 1][col];
       decay_n = fast_exp(gnv);
-      hscale_n = BWD ? 1.f : fast_exp(gnv - 0.5f * e0_s[(pp + 1) & 1][col]) * p.scale;
+      hscale_n = BWD ? fast_exp(0.5f * (gnv - e0_s[(pp + 1) & 1][col]))
+                     : fast_exp(gnv - 0.5f * e0_s[(pp + 1) & 1][col]) * p.scale;
       if (tid == 0) {
         tc_fence_after();
         issue_state_mma(pp + 1);
@@ -571,15 +573,14 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   uint8_t* smem = align1024(smem_raw);
   uint8_t* qs = smem;                 // q -> q exp(G - mid) in place
   uint8_t* ks = qs + TILE64;          // k -> k exp(mid - G) in place
-  uint8_t* gs = ks + TILE64;          // g -> k exp(G_n - G) in place
+  uint8_t* gs = ks + TILE64;          // g
   uint8_t* vs = gs + TILE64;
   uint8_t* dos = vs + TILE64;
   uint8_t* hs = dos + TILE64;         // h_c exp(mid) scale, 128 x 128
-  uint8_t* dhs = hs + TILE128;        // dh_c, 128 x 128
+  uint8_t* dhs = hs + TILE128;        // dh_c exp(G_n - mid), 128 x 128
   uint8_t* Ps = dhs + TILE128;        // tril(A) scale, bf16 64 x 64
   uint8_t* dAs = Ps + SLAB64;         // tril(dA) scale, bf16 64 x 64
   uint8_t* mtm = dAs + SLAB64;        // TRI_MID pattern, rows repeated to 128
-  uint8_t* mtr = mtm + 2 * SLAB64;    // TRI_REV pattern, rows repeated to 128
   __shared__ uint64_t loadA, loadB, bar_e, bar1, bar2, bar3;
   __shared__ uint32_t tmem_slot;
   __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums   (double-buffered per iteration)
@@ -588,8 +589,8 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
   // tensor-memory columns; the exponent tiles are consumed before the accumulators that share their columns
-  constexpr uint32_t cEm = 0, cEr = 128, cET = 448;
-  constexpr uint32_t cdq2 = 0, cdk2 = 64, cdv = 128, cdq1 = 192, cA = 256, cdA = 320, cdk1 = 384;
+  constexpr uint32_t cEm = 0, cET = 384;
+  constexpr uint32_t cdq = 0, cdk2 = 64, cdv = 128, cdk1 = 192, cA = 256, cdA = 320;
 
   auto chunk_rows = [&](int cid, int& h, int& row, int& hrow) {
     const int ci = cid % p.NT, bh = cid / p.NT, b = bh / p.H;
@@ -626,7 +627,6 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
   build_tri_tile(mtm, 128, TRI_MID);
-  build_tri_tile(mtr, 128, TRI_REV);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -647,13 +647,10 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     TSTAMP(8);
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm), mra = smem_u32(mtr);
+      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm);
 #pragma unroll
       for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
         umma_bf16(tm + cEm, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
-#pragma unroll
-      for (int j0 = 0; j0 < C; j0 += 16)   // G_n - G, [time (repeated)][channel]
-        umma_bf16(tm + cEr, desc_kmajor(mra, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
 #pragma unroll
       for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
         umma_bf16(tm + cET, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0), umma_idesc(128, 64, 1, 0), j0 > 0);
@@ -661,7 +658,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     }
     __syncwarp();
     TSTAMP(0);
-    // partial of sum_v h'[k][v] dh[k][v] for k = col over v in [32 seg, 32 seg + 32), while the tensor core works
+    // partial of sum_v h'[k][v] dh'[k][v] for k = col over v in [32 seg, 32 seg + 32), while the tensor core works
     {
       float hd = 0.f;
 #pragma unroll
@@ -687,24 +684,20 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       // gate q, k: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
       const int i = (q4 * 32 + lane) & 63;
       const int cg = (q4 >> 1) * 4 + seg;
-      float em[16], er[16];
+      float em[16];
       tmem_ld16(tmem_addr(tm, lane_base, cEm + cg * 16), em);
-      tmem_ld16(tmem_addr(tm, lane_base, cEr + cg * 16), er);
       const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
-        float f[8], r[8], w[8];
+        float f[8], r[8];
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
           f[t] = fast_exp(em[8 * u + t]);
           r[t] = fast_exp(-em[8 * u + t]);
-          w[t] = fast_exp(er[8 * u + t]);
         }
-        const uint4 kv = *reinterpret_cast<const uint4*>(ks + off);
         *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), f);
-        *reinterpret_cast<uint4*>(ks + off) = scale8(kv, r);
-        *reinterpret_cast<uint4*>(gs + off) = scale8(kv, w);
+        *reinterpret_cast<uint4*>(ks + off) = scale8(*reinterpret_cast<const uint4*>(ks + off), r);
       }
     }
     fence_async_smem();
@@ -714,7 +707,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
     if (abort_flag) { ok = false; break; }
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), kga = smem_u32(gs), va = smem_u32(vs), doa = smem_u32(dos),
+      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), va = smem_u32(vs), doa = smem_u32(dos),
                      ha = smem_u32(hs), dha = smem_u32(dhs);
 #pragma unroll
       for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
@@ -725,13 +718,13 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       umma_commit(&bar1);
 #pragma unroll
       for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
-        umma_bf16(tm + cdq2, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+        umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
 #pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // dk_inter^T[k][j] = dh v^T
+      for (int k0 = 0; k0 < D; k0 += 16)   // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
         umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
 #pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh^T kg^T
-        umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kga, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
+      for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh'^T k~^T
+        umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
       umma_commit(&bar2);
     }
     __syncwarp();
@@ -756,8 +749,8 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       tc_fence_after();
       const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
 #pragma unroll
-      for (int k0 = 0; k0 < C; k0 += 16)   // dq_intra^T[k][i] = sum_j k~[j][k] dA[i][j]
-        umma_bf16(tm + cdq1, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
+      for (int k0 = 0; k0 < C; k0 += 16)   // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
+        umma_bf16(tm + cdq, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
 #pragma unroll
       for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
         umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
@@ -766,7 +759,7 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
         umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
       umma_commit(&bar3);
     } else if (tid == 64) {
-      // h, dh, v and the gated-k tile are dead once the first batch is complete: fetch the next chunk's
+      // g, h, dh and v are dead once the first batch is complete: fetch the next chunk's
       if (!mbar_wait(&bar2, ph)) { abort_flag = 1; fail(10); }
       if (nxt < p.total) issue_A(nxt);
     }
@@ -800,23 +793,21 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
       for (int t = 0; t < 16; ++t) p.dv[obase + t * ostride] = __float2bfloat16_rn(a[t]);
     }
     // dq, dk and the local suffix sums of the gate gradient, walking time backwards
-    const float c2 = fast_exp(tmem_ld1(tmem_addr(tm, lane_base, cET + 63)));   // exp(G_n - mid)
     float run = 0.f, tail = 0.f;
 #pragma unroll
     for (int half = 1; half >= 0; --half) {
-      float dq1[8], dq2[8], dk1[8], dk2[8], et[8];
+      float dq[8], dk1[8], dk2[8], et[8];
       const uint32_t c0 = seg * 16 + half * 8;
       tmem_ld8(tmem_addr(tm, lane_base, cET + c0), et);
-      tmem_ld8(tmem_addr(tm, lane_base, cdq1 + c0), dq1);
-      tmem_ld8(tmem_addr(tm, lane_base, cdq2 + c0), dq2);
+      tmem_ld8(tmem_addr(tm, lane_base, cdq + c0), dq);
       tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
       tmem_ld8(tmem_addr(tm, lane_base, cdk2 + c0), dk2);
 #pragma unroll
       for (int u = 7; u >= 0; --u) {
         const int t = half * 8 + u;
         const float e = fast_exp(et[u]), r = fast_exp(-et[u]);
-        const float dqs = dq1[u] + dq2[u];              // dq exp(mid - G)
-        const float dki = c2 * dk2[u];                  // dk_inter exp(G - mid)
+        const float dqs = dq[u];                        // dq exp(mid - G)
+        const float dki = dk2[u];                       // dk_inter exp(G - mid)
         const float dks = dk1[u] + dki;                 // dk exp(G - mid)
         p.dq[obase + t * ostride] = e * dqs;
         p.dk[obase + t * ostride] = r * dks;
@@ -836,8 +827,8 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
                           (seg < 3 ? sufsum[ph][3][col] : 0.f);
       const float hdh = part[ph][0][0][col] + part[ph][0][1][col] + part[ph][0][2][col] + part[ph][0][3][col];
       const float tails = part[ph][1][0][col] + part[ph][1][1][col] + part[ph][1][2][col] + part[ph][1][3][col];
-      // exp(G_n) sum_v h dh with h = h' / (exp(mid) scale)
-      const float cst = later + tails + c2 / p.scale * hdh;
+      // exp(G_n) sum_v h dh with h = h' / (exp(mid) scale) and dh = dh' / exp(G_n - mid)
+      const float cst = later + tails + hdh / p.scale;
 #pragma unroll
       for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
     }
@@ -919,7 +910,7 @@ bool device_is_sm100() {
 
 constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 2 * TILE128 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
-constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 4 * SLAB64 + 1024;
+constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
 
 template <class F>
 int opt_in_smem(F f, size_t bytes) {
