@@ -47,11 +47,15 @@ WORKLOADS = {
     # BASELINE.json configs[2]: one decode token per call, state updated in place
     "decode": dict(B=128, T=1, H=32, K=128, V=128, dtype="bfloat16", seed=3),
 }
-# bytes every API tensor contributes once per (token, head) for fwd+bwd of gla_train:
-# fwd reads q,k,v,g (4 x 256) writes o (256); bwd reads q,k,v,g,do (5 x 256),
-# writes dq,dk,dg fp32 (3 x 512) and dv bf16 (256)
-# plus the four fp32 states (h0, ht, dht, dh0: 4 x 64 KiB per (b, h)) spread over T=4096 tokens: 64 B
-GLA_TRAIN_BYTES_PER_TOKEN_HEAD = 4 * 256 + 256 + 5 * 256 + 3 * 512 + 256 + 64
+
+def gla_train_bytes_per_token_head(grad_bytes):
+    """Bytes every API tensor contributes once per (token, head) for fwd+bwd of gla_train:
+    fwd reads q,k,v,g (4 x 256) writes o (256); bwd reads q,k,v,g,do (5 x 256), writes dq,dk,dg
+    (3 x 128 x grad_bytes) and dv bf16 (256), plus the four fp32 states (h0, ht, dht, dh0:
+    4 x 64 KiB per (b, h)) spread over T=4096 tokens: 64 B."""
+    return 4 * 256 + 256 + 5 * 256 + 3 * 128 * grad_bytes + 256 + 64
+
+
 GLA_TRAIN_FLOP_PER_TOKEN_HEAD = 98304 + 245760
 
 
@@ -122,7 +126,7 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-def kernel_bytes(label, w):
+def kernel_bytes(label, w, grad_bytes=4):
     """Algorithmic bytes one launch of a kernel must move for the gla_train
     workload: every operand it needs read once, every result written once."""
     tok = w["B"] * w["T"] * w["H"]
@@ -143,7 +147,7 @@ def kernel_bytes(label, w):
         "sm100_fwd_h": tok * (K + V + K) * in2 + state * in2 + 2 * bhkv * 4,
         "sm100_fwd_o": tok * (3 * K + 2 * V) * in2 + state * in2,
         "sm100_bwd_dh": tok * (K + V + K) * in2 + state * in2 + 2 * bhkv * 4,
-        "sm100_bwd_main": tok * (3 * K + 2 * V) * in2 + 2 * state * in2 + 3 * tok * K * 4 + tok * V * in2,
+        "sm100_bwd_main": tok * (3 * K + 2 * V) * in2 + 2 * state * in2 + 3 * tok * K * grad_bytes + tok * V * in2,
     }
     return t.get(label)
 
@@ -171,12 +175,19 @@ def run_b200(args):
     pinned = {n: host[n].pin_memory() for n in names}
     x = {n: pinned[n].to(dev) for n in names}
 
+    # "primal": dq, dk, dg come back in the dtypes of q, k, g (bf16), as the differentiable op returns
+    # them and as the reference's accelerator kernel writes them; "fp32": as the reference's CPU
+    # orchestrator returns them
+    primal = args.grads == "primal"
+    grad_bytes = 2 if primal else 4
+
     def step(t):
         # the forward keeps its chunk-start states for the backward (what the differentiable op does)
         o, ht, _, _, hs = chunk_fwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"], True, w["C"],
                                          want_saved=True)
         dq, dk, dv, dg, dh0 = chunk_bwd_call(t["q"], t["k"], t["v"], t["g"], L.GATE_PER_CHANNEL, scale, t["h0"],
-                                             t["do"], t["dht"], w["C"], torch.float32, True, True, h_saved=hs)
+                                             t["do"], t["dht"], w["C"], torch.float32, True, True, h_saved=hs,
+                                             primal_dtypes=primal)
         return o, ht, dq, dk, dv, dg, dh0
 
     def barrier():
@@ -248,6 +259,7 @@ def run_b200(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"chunk_gla fwd+bwd, B={w['B']} per GPU, T=4096, H=16, K=V=128, chunk 64, h0+dht (BASELINE configs[1])",
+                   "grads": "dq, dk, dg in bf16 (the primal dtypes)" if primal else "dq, dk, dg in fp32",
                    "global_batch": w["B"] * world, "seq_len": w["T"], "parallelism": f"batch x heads shard x{world}, no communication",
                    "l2": "inputs (671 MB) and outputs are larger than L2; no flush needed"},
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -257,6 +269,7 @@ def run_b200(args):
     }
     # whole-step view against both roofs
     th = w["B"] * w["T"] * w["H"]
+    GLA_TRAIN_BYTES_PER_TOKEN_HEAD = gla_train_bytes_per_token_head(grad_bytes)
     result["step_roofline"] = {
         "hbm_frac": th * GLA_TRAIN_BYTES_PER_TOKEN_HEAD / (ms * 1e-3) / (hbm_peak * 1e9),
         "tensor_frac": th * GLA_TRAIN_FLOP_PER_TOKEN_HEAD / (ms * 1e-3) / (tf_peak * 1e12),
@@ -266,7 +279,7 @@ def run_b200(args):
         top = max(kernels, key=lambda k: kernels[k][1])
         count, total = kernels[top]
         per_launch_ms = total / count
-        nbytes = kernel_bytes(top, w)
+        nbytes = kernel_bytes(top, w, grad_bytes)
         achieved = None if nbytes is None else nbytes / (per_launch_ms * 1e-3) / 1e9
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -406,6 +419,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--grads", default="primal", choices=["primal", "fp32"],
+                    help="dtype of dq, dk, dg in the timed step: the primal dtypes (bf16) or fp32")
     ap.add_argument("--batch", type=int, default=0, help="override B (profiler captures on a smaller case)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timed steps only, short JSON")
     ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda"],

@@ -207,8 +207,13 @@ int tops_b200_chunk_gla_fwd_static(const tops_chunk_fwd_params* p, void* stream)
  * `tops/cpu/ops/simple_gla/chunk.py:668-788`: recompute cumsum, states and
  * the intra matrix, reverse-scan dh, then dq, dk, dv, dg (and dh0 when h0 is
  * given).  Output dtypes: `grad_dtype` for dq/dk (TOPS_F32 for GLA as in the
- * reference, the input dtype for simple_gla), dv in the input dtype, dg fp32
- * (`[B,T,H,K]` per-channel, `[B,T,H]` scalar; NULL for GAMMA/NONE).
+ * reference's CPU path, the input dtype for simple_gla), dv in the input
+ * dtype, dg in `dg_dtype` (`[B,T,H,K]` per-channel, `[B,T,H]` scalar; NULL
+ * for GAMMA/NONE).  `dg_dtype` is TOPS_F32 (the default, what
+ * `tops/cpu/ops/gla/chunk.py:637-638` returns) or, on the tcgen05 path with
+ * `grad_dtype == TOPS_BF16`, TOPS_BF16: the reference's accelerator kernel
+ * writes dq, dk and dg in the dtypes of q, k and g
+ * (`tops/ops/gla/chunk.py:1551-1554`).
  * ------------------------------------------------------------------------ */
 typedef struct {
   tops_chunk_problem pb;
@@ -220,13 +225,14 @@ typedef struct {
   void *dq, *dk;
   int32_t grad_dtype;
   void* dv;
-  float* dg;
+  void* dg;
   float* dh0; /* NULL unless h0 given and wanted */
   /* Optional: the `saved_out` scratch written by the forward call on the same
    * inputs (tcgen05 path only).  When given the backward skips recomputing the
    * chunk-start states; NULL recomputes (the reference always recomputes,
    * `tops/cpu/ops/gla/chunk.py:551-561`). */
   const void* h_saved;
+  int32_t dg_dtype; /* TOPS_F32 (0) or TOPS_BF16, see above */
 } tops_chunk_bwd_params;
 size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);
 int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,

@@ -8,26 +8,28 @@
 // Data layout.  Activations stay in the caller's [B,T,H,D] layout; a chunk of
 // one head is a 64 x 128 tile whose rows are H*D elements apart, fetched as two
 // 64 x 64 TMA boxes (SWIZZLE_128B) straight into the tile format UMMA
-// descriptors read (sm100_prims.cuh).  Chunk-start states h_c and their
-// gradients dh_c are kept as bf16 [B,NT,H,K,V] scratch in HBM: they are only
-// ever used as bf16 tensor-core operands; the running state itself is fp32 in
-// registers of the scan kernels.
+// descriptors read (sm100_prims.cuh).  Chunk-start states and their gradients
+// are kept as bf16 [B,NT,H,K,V] scratch in HBM, pre-multiplied by the
+// per-channel factors their consumers need (h' = h exp(mid) scale,
+// dh' = dh exp(G_n - mid)): they are only ever used as bf16 tensor-core
+// operands; the running state itself is fp32 in registers of the scan kernels.
 //
 // Kernels
-//   k_scan<false>  h_c,  h <- h * exp(G_n) + (k exp(G_n - G))^T v       (forward scan)
-//   k_scan<true>   dh_c, dh <- dh * exp(G_n) + (q scale exp(G))^T do    (reverse scan)
-//   k_fwd_o        A = tril(q~ k~^T) scale;  o = q~ (h_c exp(mid) scale) + A v
-//   k_bwd_main     dA, dv, dq, dk, dg of one chunk from q, k, v, g, do, h_c, dh_c
+//   k_scan<false>  h'_c,  h <- h * exp(G_n) + (k exp(G_n - G))^T v       (forward scan)
+//   k_scan<true>   dh'_c, dh <- dh * exp(G_n) + (q scale exp(G))^T do    (reverse scan)
+//   k_fwd_o        A = tril(q~ k~^T) scale;  o = q~ h'_c + A v
+//   k_bwd_main     dA, dv, dq, dk, dg of one chunk from q, k, v, g, do, h'_c, dh'_c
 // with G the chunk-local cumulative gate and q~ = q exp(G - mid),
-// k~ = k exp(mid - G), mid = (G_0 + G_n) / 2 per channel.
+// k~ = k exp(mid - G), mid = (G_0 + G_n) / 2 per channel.  The cumulative
+// gates themselves are tensor-core products of the gate tile with constant
+// 0 / 1 / +-1/2 patterns, so the exponents arrive in tensor memory in the
+// layout the gating or the write-out needs.
 //
-// Thread layout (all kernels): 512 threads = 16 warps.  Thread (col, seg) with
-// col = (warp & 3) * 32 + lane and seg = warp >> 2 owns channel `col` for the
-// 16 time steps [16 seg, 16 seg + 16) of the chunk; the cumulative gate is a
-// two-level scan (16 steps in registers, 4 segment sums through shared memory).
-// A warp may only touch the 32 tensor-memory lanes (warp & 3) * 32 .. + 31, so
-// the same thread also owns accumulator row `col` and splits the accumulator
-// columns with the three other warps of its lane quarter by `seg`.
+// Thread layout (scans, k_fwd_o, write-out warps of k_bwd_main): 16 warps.
+// Thread (col, seg) with col = (warp & 3) * 32 + lane and seg = warp >> 2:
+// a warp may only touch the 32 tensor-memory lanes (warp & 3) * 32 .. + 31, so
+// the thread owns accumulator row `col` and splits the accumulator columns
+// with the three other warps of its lane quarter by `seg`.
 #include <mutex>
 
 #include "gla_sm100.cuh"
@@ -43,7 +45,9 @@ __device__ long long g_timing[16];
 #define TSTAMP(i) do { long long _n = clock64(); _acc[i] += _n - _t; _t = _n; } while (0)
 #define TSTART() _t = clock64()
 #define TFLUSH() do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { for (int _i = 0; _i < 16; ++_i) g_timing[_i] += _acc[_i]; } } while (0)
+#define TFLUSH_IF(c) do { if ((c) && blockIdx.x == 0) { for (int _i = 0; _i < 16; ++_i) g_timing[_i] += _acc[_i]; } } while (0)
 #else
+#define TFLUSH_IF(c)
 #define TDECL()
 #define TSTAMP(i)
 #define TSTART()
@@ -66,9 +70,6 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 __device__ __forceinline__ float ld_bf16(const uint8_t* tile, uint32_t off) {
   return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + off));
 }
-__device__ __forceinline__ void st_bf16(uint8_t* tile, uint32_t off, float x) {
-  *reinterpret_cast<__nv_bfloat16*>(tile + off) = __float2bfloat16_rn(x);
-}
 // offset of (row i, this thread's column) in a 64-row tile
 struct ColAddr {
   uint32_t base, cchunk;
@@ -84,26 +85,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 __device__ __forceinline__ void fail(int code) { atomicCAS(&g_error, 0, code); }
-
-// Two-level inclusive scan of this thread's gate column.  gv[t] receives the
-// raw gate of row 16 seg + t; returns the sum over earlier segments (`prefix`)
-// and over the whole chunk (`gn`).  Contains one __syncthreads.
-__device__ __forceinline__ void gate_scan(const uint8_t* gs, const ColAddr& ca, int seg, int col,
-                                          float (*segsum)[D], float (&gv)[SEG], float& prefix, float& gn) {
-  // segsum has 5 rows: [0..3] segment sums, [4] the gate of row 0 (for the mid-point anchor)
-  float s = 0.f;
-#pragma unroll
-  for (int t = 0; t < SEG; ++t) {
-    gv[t] = ld_bf16(gs, ca.at(seg * SEG + t));
-    s += gv[t];
-  }
-  segsum[seg][col] = s;
-  if (seg == 0) segsum[4][col] = gv[0];
-  __syncthreads();
-  const float s0 = segsum[0][col], s1 = segsum[1][col], s2 = segsum[2][col], s3 = segsum[3][col];
-  prefix = (seg > 0 ? s0 : 0.f) + (seg > 1 ? s1 : 0.f) + (seg > 2 ? s2 : 0.f);
-  gn = s0 + s1 + s2 + s3;
-}
 
 // ===========================================================================
 // State scans
@@ -139,21 +120,6 @@ __device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind
     uint32_t w[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) w[t] = pack_bf16(tri_value(kind, i, c8 + 2 * t), tri_value(kind, i, c8 + 2 * t + 1));
-    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
-// 16 x 64 tile: row 0 sums the gates (G_n), row 1 gives the mid-point (G_0 + G_n) / 2
-__device__ __forceinline__ void build_w_tile(uint8_t* tile) {
-  for (int idx = threadIdx.x; idx < 16 * 8; idx += blockDim.x) {
-    const int r = idx >> 3, c8 = (idx & 7) * 8;
-    uint32_t w[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int j = c8 + 2 * t;
-      const float a = r == 0 ? 1.f : (r == 1 ? (j == 0 ? 1.f : 0.5f) : 0.f);
-      const float b = r == 0 ? 1.f : (r == 1 ? 0.5f : 0.f);
-      w[t] = pack_bf16(a, b);
-    }
     *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
@@ -388,7 +354,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     decay = decay_n;
     hscale = hscale_n;
   }
-  TFLUSH();
+  if (!BWD) { TFLUSH(); }
   if (tid == 96) tma_store_wait_all();
   if (ok && p.s_final) {
     float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
@@ -438,7 +404,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, seg = warp >> 2;
-  const int ci = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  // heads vary fastest over the blocks in flight: together they read whole token rows of the
+  // [B,T,H,D] activations (all heads of a time step are contiguous in memory)
+  const int h = blockIdx.x, ci = blockIdx.y, b = blockIdx.z, bh = b * p.H + h;
   const int row = b * p.T + ci * C;
   constexpr uint32_t cO = 0, cE = 0, cA = 128;   // E is consumed before O is produced
 
@@ -562,18 +530,62 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
 // ===========================================================================
 struct BwdParams {
   CUtensorMap mq, mk, mg, mv, mdo, mh, mdh;
-  float *dq, *dk, *dg;   // [B,T,H,K] fp32 (dg may be null)
+  void *dq, *dk, *dg;    // [B,T,H,K] fp32 or bf16 (dg may be null)
   __nv_bfloat16* dv;     // [B,T,H,V]
   int T, H, NT, total;   // total = B * H * NT chunks
   float scale;
 };
 
-__global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ BwdParams p) {
+// Warp roles: warps 0-15 gate q and k of the next chunk and write the gradients of a chunk out of
+// tensor memory (thread = one channel, 16 time steps); warps 16-19 convert A and dA to bf16 operands
+// and reduce sum_v h' dh'; one thread of warp 20 issues every tensor-core product, one thread of warp 21
+// every TMA load.
+// The roles meet only through mbarriers, so the gradient write-out of chunk n runs while the
+// exponent product, the gating and the A / dA products of chunk n+1 are under way; the six
+// gradient products of chunk n+1 start as soon as chunk n has left tensor memory.
+constexpr int BWD_THREADS = 704;
+constexpr int BWD_EPI_THREADS = 512, BWD_GATE_THREADS = 128;
+
+// 4 x 4 transpose over the lanes l, l^1, l^2, l^3.  In: v[j] = value of this lane's channel at
+// time t0 + j.  Out: v[j] = value of channel (lane & ~3) + j at time t0 + (lane & 3), so that a
+// thread can store four neighbouring channels of one time step with one instruction.
+__device__ __forceinline__ void transpose4(float (&v)[4], int lane) {
+  const bool odd = lane & 1, hi = lane & 2;
+  const float r0 = __shfl_xor_sync(0xffffffffu, odd ? v[0] : v[1], 1);
+  const float r1 = __shfl_xor_sync(0xffffffffu, odd ? v[2] : v[3], 1);
+  const float a0 = odd ? r0 : v[0], a1 = odd ? v[1] : r0;   // time t0 + odd:     channels 2m, 2m + 1
+  const float b0 = odd ? r1 : v[2], b1 = odd ? v[3] : r1;   // time t0 + 2 + odd: channels 2m, 2m + 1
+  const float u0 = __shfl_xor_sync(0xffffffffu, hi ? a0 : b0, 2);
+  const float u1 = __shfl_xor_sync(0xffffffffu, hi ? a1 : b1, 2);
+  v[0] = hi ? u0 : a0; v[1] = hi ? u1 : a1; v[2] = hi ? b0 : u0; v[3] = hi ? b1 : u1;
+}
+// The same exchange followed by a store of the four neighbouring channels of time step
+// t0 + (lane & 3) at p[i]; the bf16 form rounds after the first stage and moves packed pairs.
+__device__ __forceinline__ void st_transposed4(float* p, size_t i, float (&v)[4], int lane) {
+  transpose4(v, lane);
+  *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st_transposed4(__nv_bfloat16* p, size_t i, const float (&v)[4], int lane) {
+  const bool odd = lane & 1, hi = lane & 2;
+  const float r0 = __shfl_xor_sync(0xffffffffu, odd ? v[0] : v[1], 1);
+  const float r1 = __shfl_xor_sync(0xffffffffu, odd ? v[2] : v[3], 1);
+  const uint32_t pa = odd ? pack_bf16(r0, v[1]) : pack_bf16(v[0], r0);
+  const uint32_t pb = odd ? pack_bf16(r1, v[3]) : pack_bf16(v[2], r1);
+  const uint32_t u = __shfl_xor_sync(0xffffffffu, hi ? pa : pb, 2);
+  *reinterpret_cast<uint2*>(p + i) = hi ? make_uint2(u, pb) : make_uint2(pa, u);
+}
+__device__ __forceinline__ void st_out(float* p, size_t i, float x) { p[i] = x; }
+__device__ __forceinline__ void st_out(__nv_bfloat16* p, size_t i, float x) { p[i] = __float2bfloat16_rn(x); }
+
+
+// TG: type of dq and dk; TD: type of dg
+template <typename TG, typename TD>
+__global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
-  uint8_t* qs = smem;                 // q -> q exp(G - mid) in place
-  uint8_t* ks = qs + TILE64;          // k -> k exp(mid - G) in place
-  uint8_t* gs = ks + TILE64;          // g
+  uint8_t* qs = smem;                 // 2 x: q -> q exp(G - mid) in place
+  uint8_t* ks = qs + 2 * TILE64;      // 2 x: k -> k exp(mid - G) in place
+  uint8_t* gs = ks + 2 * TILE64;      // g
   uint8_t* vs = gs + TILE64;
   uint8_t* dos = vs + TILE64;
   uint8_t* hs = dos + TILE64;         // h_c exp(mid) scale, 128 x 128
@@ -581,50 +593,50 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   uint8_t* Ps = dhs + TILE128;        // tril(A) scale, bf16 64 x 64
   uint8_t* dAs = Ps + SLAB64;         // tril(dA) scale, bf16 64 x 64
   uint8_t* mtm = dAs + SLAB64;        // TRI_MID pattern, rows repeated to 128
-  __shared__ uint64_t loadA, loadB, bar_e, bar1, bar2, bar3;
+  // single-slot barriers complete once per chunk (parity it & 1); two-slot ones are indexed by it & 1
+  // and complete every other chunk (parity (it >> 1) & 1)
+  __shared__ uint64_t full_g, full_qk[2], full_hdo, full_dhv, bar_gate, bar_A, bar_r1, bar_r2, bar_main, gated, conv_done,
+      hdh_done[2], e_done[2];
   __shared__ uint32_t tmem_slot;
-  __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums   (double-buffered per iteration)
-  __shared__ float part[2][2][4][D];  // [.][0]: sum_v h dh partials; [.][1]: sum_i dk_inter k partials
+  __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums
+  __shared__ float tails[2][4][D];    // per-segment sum_i dk_inter k
+  __shared__ float hdh_s[2][D];       // sum_v h' dh'
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
-  // tensor-memory columns; the exponent tiles are consumed before the accumulators that share their columns
-  constexpr uint32_t cEm = 0, cET = 384;
-  constexpr uint32_t cdq = 0, cdk2 = 64, cdv = 128, cdk1 = 192, cA = 256, cdA = 320;
+  // tensor-memory columns: the exponent tile E_mid is consumed by the gating before A and dA take its place
+  constexpr uint32_t cEm = 0, cA = 0, cdA = 64, cET = 128, cdq = 256, cdk1 = 320, cdk2 = 384, cdv = 448;
+  const int nit = (p.total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
-  auto chunk_rows = [&](int cid, int& h, int& row, int& hrow) {
-    const int ci = cid % p.NT, bh = cid / p.NT, b = bh / p.H;
-    h = bh % p.H;
+  auto chunk_rows = [&](int it, int& h, int& row, int& hrow) {
+    // heads vary fastest over the chunks in flight: together the blocks read and write whole
+    // token rows of the [B,T,H,D] activations
+    const int cid = blockIdx.x + it * gridDim.x;
+    const int ci = (cid / p.H) % p.NT, b = cid / (p.H * p.NT);
+    h = cid % p.H;
     row = b * p.T + ci * C;
     hrow = ((b * p.NT + ci) * p.H + h) * D;
   };
-  auto issue_A = [&](int cid) {   // tiles whose buffers are free once the first batch of products is done
-    int h, row, hrow;
-    chunk_rows(cid, h, row, hrow);
-    mbar_expect_tx(&loadA, 2 * TILE128 + 2 * TILE64);
-    tma_load_3d(gs, &p.mg, &loadA, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &loadA, 64, h, row);
-    tma_load_2d(hs, &p.mh, &loadA, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &loadA, 64, hrow);
-    tma_load_2d(dhs, &p.mdh, &loadA, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &loadA, 64, hrow);
-    tma_load_3d(vs, &p.mv, &loadA, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &loadA, 64, h, row);
-  };
-  auto issue_B = [&](int cid) {   // tiles still read by the second batch
-    int h, row, hrow;
-    chunk_rows(cid, h, row, hrow);
-    mbar_expect_tx(&loadB, 3 * TILE64);
-    tma_load_3d(qs, &p.mq, &loadB, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &loadB, 64, h, row);
-    tma_load_3d(ks, &p.mk, &loadB, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &loadB, 64, h, row);
-    tma_load_3d(dos, &p.mdo, &loadB, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &loadB, 64, h, row);
+  // bounded wait that also gives up when another role has failed
+  auto wait = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((i & 255u) == 255u && abort_flag) return false;
+    }
+    abort_flag = 1;
+    fail(code);
+    return false;
   };
 
   if (tid == 0) {
-    mbar_init(&loadA, 1); mbar_init(&loadB, 1); mbar_init(&bar_e, 1);
-    mbar_init(&bar1, 1); mbar_init(&bar2, 1); mbar_init(&bar3, 1);
+    mbar_init(&full_g, 1); mbar_init(&full_qk[0], 1); mbar_init(&full_qk[1], 1); mbar_init(&full_hdo, 1);
+    mbar_init(&full_dhv, 1); mbar_init(&bar_gate, 1); mbar_init(&bar_A, 1); mbar_init(&bar_r1, 1); mbar_init(&bar_r2, 1);
+    mbar_init(&bar_main, 1);
+    mbar_init(&gated, BWD_EPI_THREADS); mbar_init(&conv_done, BWD_GATE_THREADS);
+    mbar_init(&hdh_done[0], BWD_GATE_THREADS); mbar_init(&hdh_done[1], BWD_GATE_THREADS);
+    mbar_init(&e_done[0], BWD_EPI_THREADS); mbar_init(&e_done[1], BWD_EPI_THREADS);
     fence_barrier_init();
     abort_flag = 0;
-    issue_A(blockIdx.x);
-    issue_B(blockIdx.x);
   }
-  __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
   build_tri_tile(mtm, 128, TRI_MID);
   fence_async_smem();
@@ -632,61 +644,28 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
-  const uint32_t lane_base = q4 * 32;
-  const ColAddr ca = col_prep(64, col);
-  bool ok = true;
   TDECL();
 
-  for (int cid = blockIdx.x, it = 0; cid < p.total; cid += gridDim.x, ++it) {
-    const uint32_t ph = it & 1;
-    const int nxt = cid + gridDim.x;
-    int h, row, hrow;
-    chunk_rows(cid, h, row, hrow);
-    TSTART();
-    if (!mbar_wait(&loadA, ph) || !mbar_wait(&loadB, ph)) { abort_flag = 1; fail(6); }
-    TSTAMP(8);
-    if (tid == 0) {
+  if (warp < 16) {
+    // ------------------------------------------------------------------ gradient write-out
+    const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
+    const uint32_t lane_base = q4 * 32;
+    const ColAddr ca = col_prep(64, col);
+    const size_t ostride = (size_t)p.H * D;
+    TG* const dq_out = reinterpret_cast<TG*>(p.dq);
+    TG* const dk_out = reinterpret_cast<TG*>(p.dk);
+    TD* const dg_out = reinterpret_cast<TD*>(p.dg);
+    // q -> q exp(G - mid), k -> k exp(mid - G) in place: thread (q4, lane, seg) owns time row
+    // (32 q4 + lane) mod 64 and 16 channels
+    auto gate_chunk = [&](int it) -> bool {
+      const int sl = it & 1;
+      if (!wait(&bar_gate, it & 1, 9) || !wait(&full_qk[sl], (it >> 1) & 1, 6)) return false;
       tc_fence_after();
-      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm);
-#pragma unroll
-      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
-        umma_bf16(tm + cEm, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
-#pragma unroll
-      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
-        umma_bf16(tm + cET, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0), umma_idesc(128, 64, 1, 0), j0 > 0);
-      umma_commit(&bar_e);
-    }
-    __syncwarp();
-    TSTAMP(0);
-    // partial of sum_v h'[k][v] dh'[k][v] for k = col over v in [32 seg, 32 seg + 32), while the tensor core works
-    {
-      float hd = 0.f;
-#pragma unroll
-      for (int c8 = 0; c8 < 32; c8 += 8) {
-        const uint32_t off = tile_off(128, col, seg * 32 + c8);
-        const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
-        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-        const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
-          hd = fmaf(fa.x, fd.x, hd);
-          hd = fmaf(fa.y, fd.y, hd);
-        }
-      }
-      part[ph][0][seg][col] = hd;
-    }
-    TSTAMP(1);
-    if (!mbar_wait(&bar_e, ph)) { abort_flag = 1; fail(9); }
-    tc_fence_after();
-    TSTAMP(9);
-    {
-      // gate q, k: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
       const int i = (q4 * 32 + lane) & 63;
       const int cg = (q4 >> 1) * 4 + seg;
       float em[16];
       tmem_ld16(tmem_addr(tm, lane_base, cEm + cg * 16), em);
-      const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+      const uint32_t rowoff = (uint32_t)sl * TILE64 + (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
@@ -699,143 +678,282 @@ __global__ void __launch_bounds__(NTHREADS) k_bwd_main(const __grid_constant__ B
         *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), f);
         *reinterpret_cast<uint4*>(ks + off) = scale8(*reinterpret_cast<const uint4*>(ks + off), r);
       }
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    TSTAMP(10);
-    if (abort_flag) { ok = false; break; }
-    if (tid == 0) {
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&gated);
+      return true;
+    };
+    bool live = gate_chunk(0);
+    for (int it = 0; live && it < nit; ++it) {
+      const int sl = it & 1;
+      int h, row, hrow;
+      chunk_rows(it, h, row, hrow);
+      TSTART();
+      TSTAMP(3);
+      // the next chunk's gating runs while the tensor core works on this chunk's gradient products
+      if (it + 1 < nit && !gate_chunk(it + 1)) break;
+      TSTAMP(4);
+      if (!wait(&bar_main, it & 1, 8) || !wait(&hdh_done[sl], (it >> 1) & 1, 11)) break;
       tc_fence_after();
-      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), va = smem_u32(vs), doa = smem_u32(dos),
-                     ha = smem_u32(hs), dha = smem_u32(dhs);
+      TSTAMP(0);
+      const uint8_t* qt = qs + sl * TILE64;
+      const uint8_t* kt = ks + sl * TILE64;
+      const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
+      const size_t obase4 = obase - (lane & 3) + (size_t)(lane & 3) * ostride;   // channel group, own time row
+      float dgl[SEG];
+      float run = 0.f, tail = 0.f;
 #pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
-        umma_bf16(tm + cA, desc_kmajor(qta, 64, 0, k0), desc_kmajor(kta, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+      for (int blk = 1; blk >= 0; --blk) {
+        float et[8], dq[8], dk1[8], dk2[8], dv[8];
+        const uint32_t c0 = seg * SEG + blk * 8;
+        tmem_ld8(tmem_addr(tm, lane_base, cET + 64 * sl + c0), et);
+        tmem_ld8(tmem_addr(tm, lane_base, cdq + c0), dq);
+        tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
+        tmem_ld8(tmem_addr(tm, lane_base, cdk2 + c0), dk2);
+        tmem_ld8(tmem_addr(tm, lane_base, cdv + c0), dv);
 #pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // dA[i][j] = do v^T
-        umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
-      umma_commit(&bar1);
-#pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
-        umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
-        umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-      for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh'^T k~^T
-        umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
-      umma_commit(&bar2);
-    }
-    __syncwarp();
-    TSTAMP(2);
-    if (!mbar_wait(&bar1, ph)) { abort_flag = 1; fail(7); }
-    tc_fence_after();
-    TSTAMP(11);
-    {
-      const int i = 16 * q4 + lane;   // rows of the M = 64 accumulators sit in lanes 0..15 of each quarter
-      float a[16];
-      tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
-      if (lane < 16) store_tril16(Ps, i, seg * 16, a, p.scale);
-      tmem_ld16(tmem_addr(tm, lane_base, cdA + seg * 16), a);
-      if (lane < 16) store_tril16(dAs, i, seg * 16, a, p.scale);
-    }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    TSTAMP(12);
-    if (abort_flag) { ok = false; break; }
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t qta = smem_u32(qs), kta = smem_u32(ks), doa = smem_u32(dos), pa = smem_u32(Ps), daa = smem_u32(dAs);
-#pragma unroll
-      for (int k0 = 0; k0 < C; k0 += 16)   // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
-        umma_bf16(tm + cdq, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
-#pragma unroll
-      for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
-        umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
-#pragma unroll
-      for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] += sum_i do[i][v] A[i][j]
-        umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
-      umma_commit(&bar3);
-    } else if (tid == 64) {
-      // g, h, dh and v are dead once the first batch is complete: fetch the next chunk's
-      if (!mbar_wait(&bar2, ph)) { abort_flag = 1; fail(10); }
-      if (nxt < p.total) issue_A(nxt);
-    }
-    __syncwarp();
-    // this thread's 16 (time, channel) elements of q~ and k~, kept for the gate gradient
-    uint32_t qk[SEG];
-#pragma unroll
-    for (int t = 0; t < SEG; ++t) {
-      const uint32_t off = ca.at(seg * SEG + t);
-      qk[t] = (uint32_t)*reinterpret_cast<const uint16_t*>(qs + off) |
-              ((uint32_t)*reinterpret_cast<const uint16_t*>(ks + off) << 16);
-    }
-    TSTAMP(3);
-    if (!mbar_wait(&bar3, ph)) { abort_flag = 1; fail(8); }
-    TSTAMP(4);
-    tc_fence_after();
-    __syncthreads();   // every thread holds its q~, k~ values and all products are complete
-    TSTAMP(13);
-    if (abort_flag) { ok = false; break; }
-    if (tid == 96 && nxt < p.total) issue_B(nxt);
-    __syncwarp();
-
-    float dgl[SEG];
-    const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
-    const size_t ostride = (size_t)p.H * D;
-    // dv: this thread owns value channel `col`, time steps of its segment
-    {
-      float a[16];
-      tmem_ld16(tmem_addr(tm, lane_base, cdv + seg * 16), a);
-#pragma unroll
-      for (int t = 0; t < 16; ++t) p.dv[obase + t * ostride] = __float2bfloat16_rn(a[t]);
-    }
-    // dq, dk and the local suffix sums of the gate gradient, walking time backwards
-    float run = 0.f, tail = 0.f;
-#pragma unroll
-    for (int half = 1; half >= 0; --half) {
-      float dq[8], dk1[8], dk2[8], et[8];
-      const uint32_t c0 = seg * 16 + half * 8;
-      tmem_ld8(tmem_addr(tm, lane_base, cET + c0), et);
-      tmem_ld8(tmem_addr(tm, lane_base, cdq + c0), dq);
-      tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
-      tmem_ld8(tmem_addr(tm, lane_base, cdk2 + c0), dk2);
-#pragma unroll
-      for (int u = 7; u >= 0; --u) {
-        const int t = half * 8 + u;
-        const float e = fast_exp(et[u]), r = fast_exp(-et[u]);
-        const float dqs = dq[u];                        // dq exp(mid - G)
-        const float dki = dk2[u];                       // dk_inter exp(G - mid)
-        const float dks = dk1[u] + dki;                 // dk exp(G - mid)
-        p.dq[obase + t * ostride] = e * dqs;
-        p.dk[obase + t * ostride] = r * dks;
-        const float qt = __uint_as_float(qk[t] << 16), kt = __uint_as_float(qk[t] & 0xffff0000u);
-        run += qt * dqs - kt * dks;                     // q dq - k dk
-        tail = fmaf(dki, kt, tail);                     // dk_inter k
-        dgl[t] = run;
+        for (int u = 7; u >= 0; --u) {
+          const int t = blk * 8 + u;
+          const uint32_t off = ca.at(seg * SEG + t);
+          const float qv = ld_bf16(qt, off), kv = ld_bf16(kt, off);   // q~, k~
+          const float e = fast_exp(et[u]), r = fast_exp(-et[u]);
+          const float dqs = dq[u];                        // dq exp(mid - G)
+          const float dki = dk2[u];                       // dk_inter exp(G - mid)
+          const float dks = dk1[u] + dki;                 // dk exp(G - mid)
+          run += qv * dqs - kv * dks;                     // q dq - k dk
+          tail = fmaf(dki, kv, tail);                     // dk_inter k
+          dgl[t] = run;
+          st_out(p.dv, obase + t * ostride, dv[u]);
+          st_out(dq_out, obase + t * ostride, e * dqs);
+          st_out(dk_out, obase + t * ostride, r * dks);
+        }
       }
-    }
-    sufsum[ph][seg][col] = run;
-    part[ph][1][seg][col] = tail;
-    tc_fence_before();
-    __syncthreads();   // also: every tensor-memory read of this chunk is done before the next products overwrite it
-    TSTAMP(14);
-    if (p.dg) {
-      const float later = (seg < 1 ? sufsum[ph][1][col] : 0.f) + (seg < 2 ? sufsum[ph][2][col] : 0.f) +
-                          (seg < 3 ? sufsum[ph][3][col] : 0.f);
-      const float hdh = part[ph][0][0][col] + part[ph][0][1][col] + part[ph][0][2][col] + part[ph][0][3][col];
-      const float tails = part[ph][1][0][col] + part[ph][1][1][col] + part[ph][1][2][col] + part[ph][1][3][col];
-      // exp(G_n) sum_v h dh with h = h' / (exp(mid) scale) and dh = dh' / exp(G_n - mid)
-      const float cst = later + tails + hdh / p.scale;
+      sufsum[sl][seg][col] = run;
+      tails[sl][seg][col] = tail;
+      TSTAMP(1);
+      tc_fence_before();
+      asm volatile("bar.sync 1, %0;" ::"n"(BWD_EPI_THREADS) : "memory");
+      const float later = (seg < 1 ? sufsum[sl][1][col] : 0.f) + (seg < 2 ? sufsum[sl][2][col] : 0.f) +
+                          (seg < 3 ? sufsum[sl][3][col] : 0.f);
+      const float cst = later + tails[sl][0][col] + tails[sl][1][col] + tails[sl][2][col] + tails[sl][3][col] +
+                        hdh_s[sl][col] / p.scale;
+      // (exp(G_n) sum_v h dh = sum_v h' dh' / scale)
+      mbar_arrive(&e_done[sl]);   // tensor memory, the q~ / k~ tiles and hdh_s of this chunk are free
+      if (p.dg) {
+        // after the accumulators are released: four time steps x four channels change hands inside each
+        // group of four lanes, so that every store writes four neighbouring channels of one time step
 #pragma unroll
-      for (int t = 0; t < SEG; ++t) p.dg[obase + t * ostride] = dgl[t] + cst;
+        for (int t = 0; t < SEG; t += 4) {
+          float w[4] = {dgl[t] + cst, dgl[t + 1] + cst, dgl[t + 2] + cst, dgl[t + 3] + cst};
+          st_transposed4(dg_out, obase4 + t * ostride, w, lane);
+        }
+      }
+      TSTAMP(2);
     }
-    TSTAMP(15);
+    TFLUSH_IF(tid == 0);
+  } else if (warp < 20) {
+    // ------------------------------------------------------------------ A / dA -> masked bf16 operands
+    const int g4 = warp & 3;
+    const uint32_t lane_base = g4 * 32;
+    for (int it = 0; it < nit; ++it) {
+      TSTART();
+      // rows of the M = 64 accumulators sit in lanes 0..15 of each quarter
+      if (!wait(&bar_A, it & 1, 7)) break;
+      tc_fence_after();
+      TSTAMP(5);
+      const int ri = 16 * g4 + lane;
+#pragma unroll
+      for (int sg = 0; sg < 4; ++sg) {
+        float a[16];
+        tmem_ld16(tmem_addr(tm, lane_base, cA + sg * 16), a);
+        if (lane < 16) store_tril16(Ps, ri, sg * 16, a, p.scale);
+        tmem_ld16(tmem_addr(tm, lane_base, cdA + sg * 16), a);
+        if (lane < 16) store_tril16(dAs, ri, sg * 16, a, p.scale);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&conv_done);
+      TSTAMP(6);
+      // sum_v h'[k][v] dh'[k][v] for k = this thread, while the gradient products read the same tiles
+      if (!wait(&full_hdo, it & 1, 6) || !wait(&full_dhv, it & 1, 6)) break;
+      {
+        const int gt = g4 * 32 + lane;
+        float hd = 0.f;
+#pragma unroll 4
+        for (int c8 = 0; c8 < D; c8 += 8) {
+          const uint32_t off = tile_off(128, gt, c8);
+          const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
+          const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+          const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
+            hd = fmaf(fa.x, fd.x, hd);
+            hd = fmaf(fa.y, fd.y, hd);
+          }
+        }
+        hdh_s[it & 1][gt] = hd;
+      }
+      mbar_arrive(&hdh_done[it & 1]);   // h' and dh' of this chunk are no longer read by threads
+      TSTAMP(7);
+    }
+    TFLUSH_IF(tid == 512);
+  } else if (warp == 20) {
+    // ------------------------------------------------------------------ tensor-core issue
+    if (lane == 0) {
+      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm), va = smem_u32(vs), doa = smem_u32(dos), ha = smem_u32(hs),
+                     dha = smem_u32(dhs), pa = smem_u32(Ps), daa = smem_u32(dAs);
+      auto issue_gate = [&](int it) {
+#pragma unroll
+        for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
+          umma_bf16(tm + cEm, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+        for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
+          umma_bf16(tm + cET + 64 * (it & 1), desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0),
+                    umma_idesc(128, 64, 1, 0), j0 > 0);
+        umma_commit(&bar_gate);
+      };
+      auto issue_A = [&](int it) {
+        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
+          umma_bf16(tm + cA, desc_kmajor(qta, 64, 0, k0), desc_kmajor(kta, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+      };
+      auto issue_dA = [&]() {
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dA[i][j] = do v^T
+          umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+        umma_commit(&bar_A);
+      };
+      // three groups, ordered so that the operands of the next chunk can be fetched early: after the
+      // first group h' and do are dead, after the second dh' and v
+      auto issue_grads = [&](int it) {
+        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
+          umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] = sum_i do[i][v] A[i][j]
+          umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
+        umma_commit(&bar_r1);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
+          umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] += dh'^T k~^T
+          umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+        umma_commit(&bar_r2);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
+          umma_bf16(tm + cdq, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
+          umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
+        umma_commit(&bar_main);
+      };
+      bool ok = wait(&full_g, 0, 6);
+      if (ok) {
+        tc_fence_after();
+        issue_gate(0);
+        ok = wait(&gated, 0, 12);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_A(0);
+        ok = wait(&full_hdo, 0, 6) && wait(&full_dhv, 0, 6);
+      }
+      if (ok) issue_dA();
+      for (int it = 0; ok && it < nit; ++it) {
+        // A and dA of this chunk are in shared memory; the previous chunk has left tensor memory
+        TSTART();
+        if (!wait(&conv_done, it & 1, 13)) break;
+        TSTAMP(8);
+        if (it >= 1 && !wait(&e_done[(it - 1) & 1], ((it - 1) >> 1) & 1, 14)) break;
+        tc_fence_after();
+        TSTAMP(9);
+        const bool more = it + 1 < nit;
+        if (more) {
+          if (!wait(&full_g, (it + 1) & 1, 6)) break;
+          issue_gate(it + 1);
+        }
+        issue_grads(it);
+        TSTAMP(10);
+        if (more) {
+          if (!wait(&gated, (it + 1) & 1, 12)) break;
+          tc_fence_after();
+          issue_A(it + 1);
+          TSTAMP(11);
+          if (!wait(&full_hdo, (it + 1) & 1, 6) || !wait(&full_dhv, (it + 1) & 1, 6)) break;
+          issue_dA();
+          TSTAMP(12);
+        }
+      }
+      TFLUSH_IF(true);
+    }
+  } else {
+    // ------------------------------------------------------------------ TMA loads
+    if (lane == 0) {
+      auto load_g = [&](int it) {
+        int h, row, hrow;
+        chunk_rows(it, h, row, hrow);
+        mbar_expect_tx(&full_g, TILE64);
+        tma_load_3d(gs, &p.mg, &full_g, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &full_g, 64, h, row);
+      };
+      auto load_qk = [&](int it) {
+        int h, row, hrow;
+        chunk_rows(it, h, row, hrow);
+        uint64_t* bar = &full_qk[it & 1];
+        uint8_t* qd = qs + (it & 1) * TILE64;
+        uint8_t* kd = ks + (it & 1) * TILE64;
+        mbar_expect_tx(bar, 2 * TILE64);
+        tma_load_3d(qd, &p.mq, bar, 0, h, row); tma_load_3d(qd + SLAB64, &p.mq, bar, 64, h, row);
+        tma_load_3d(kd, &p.mk, bar, 0, h, row); tma_load_3d(kd + SLAB64, &p.mk, bar, 64, h, row);
+      };
+      auto load_hdo = [&](int it) {
+        int h, row, hrow;
+        chunk_rows(it, h, row, hrow);
+        mbar_expect_tx(&full_hdo, TILE128 + TILE64);
+        tma_load_3d(dos, &p.mdo, &full_hdo, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &full_hdo, 64, h, row);
+        tma_load_2d(hs, &p.mh, &full_hdo, 0, hrow); tma_load_2d(hs + TILE128 / 2, &p.mh, &full_hdo, 64, hrow);
+      };
+      auto load_dhv = [&](int it) {
+        int h, row, hrow;
+        chunk_rows(it, h, row, hrow);
+        mbar_expect_tx(&full_dhv, TILE128 + TILE64);
+        tma_load_3d(vs, &p.mv, &full_dhv, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &full_dhv, 64, h, row);
+        tma_load_2d(dhs, &p.mdh, &full_dhv, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &full_dhv, 64, hrow);
+      };
+      load_g(0);
+      load_qk(0);
+      load_hdo(0);
+      load_dhv(0);
+      bool ok = true;
+      if (nit > 1) {
+        load_qk(1);
+        ok = wait(&bar_gate, 0, 9);   // the exponent products of chunk 0 have read its gates
+        if (ok) load_g(1);
+      }
+      for (int it = 0; ok && it + 1 < nit; ++it) {
+        // h' and do are dead after the first group of products, dh' and v after the second (and the
+        // h' dh' reduction)
+        TSTART();
+        if (!wait(&bar_r1, it & 1, 8) || !wait(&hdh_done[it & 1], (it >> 1) & 1, 11)) break;
+        load_hdo(it + 1);
+        if (!wait(&bar_r2, it & 1, 8)) break;
+        load_dhv(it + 1);
+        TSTAMP(13);
+        if (it + 2 < nit) {
+          if (!wait(&e_done[it & 1], (it >> 1) & 1, 14)) break;
+          load_qk(it + 2);
+          TSTAMP(14);
+          if (!wait(&bar_gate, (it + 1) & 1, 9)) break;
+          load_g(it + 2);
+          TSTAMP(15);
+        }
+      }
+      TFLUSH_IF(true);
+    }
   }
-  TFLUSH();
-  (void)ok;
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
@@ -910,7 +1028,7 @@ bool device_is_sm100() {
 
 constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 2 * TILE128 + 1024;
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
-constexpr size_t BWD_SMEM = 5 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
+constexpr size_t BWD_SMEM = 7 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
 
 template <class F>
 int opt_in_smem(F f, size_t bytes) {
@@ -977,7 +1095,7 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
   fp.o = reinterpret_cast<__nv_bfloat16*>(p.o); fp.T = pb.T; fp.H = pb.H; fp.NT = NT; fp.scale = pb.scale;
   if ((rc = opt_in_smem(k_fwd_o, FWD_O_SMEM))) return rc;
   KernelScope ks("sm100_fwd_o", st);
-  k_fwd_o<<<dim3(NT, pb.B * pb.H), NTHREADS, FWD_O_SMEM, st>>>(fp);
+  k_fwd_o<<<dim3(pb.H, NT, pb.B), NTHREADS, FWD_O_SMEM, st>>>(fp);
   return post_launch();
 }
 
@@ -985,9 +1103,24 @@ size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p) {
   return (p.h_saved ? 1 : 2) * state_bytes(p.pb) + 256;
 }
 
+bool bwd_dtypes_ok(const tops_chunk_bwd_params& p) {
+  return (p.grad_dtype == TOPS_F32 && p.dg_dtype == TOPS_F32) ||
+         (p.grad_dtype == TOPS_BF16 && (p.dg_dtype == TOPS_F32 || p.dg_dtype == TOPS_BF16));
+}
+
+template <typename TG, typename TD>
+int launch_bwd_main(const BwdParams& bp, cudaStream_t st) {
+  int rc = opt_in_smem(k_bwd_main<TG, TD>, BWD_SMEM);
+  if (rc) return rc;
+  const int grid = bp.total < sm_count() ? bp.total : sm_count();
+  KernelScope ks("sm100_bwd_main", st);
+  k_bwd_main<TG, TD><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
+  return post_launch();
+}
+
 int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st) {
   const tops_chunk_problem& pb = p.pb;
-  if (p.grad_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;
+  if (!bwd_dtypes_ok(p)) return TOPS_E_UNSUPPORTED;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.do_) ||
       !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(ws))
     return TOPS_E_ALIGN;
@@ -1010,14 +1143,12 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
       (rc = act_map(&bp.mdo, p.do_, BT, pb.H)) || (rc = state_map(&bp.mh, h, rows)) ||
       (rc = state_map(&bp.mdh, dh, rows)))
     return rc;
-  bp.dq = reinterpret_cast<float*>(p.dq); bp.dk = reinterpret_cast<float*>(p.dk); bp.dg = p.dg;
+  bp.dq = p.dq; bp.dk = p.dk; bp.dg = p.dg;
   bp.dv = reinterpret_cast<__nv_bfloat16*>(p.dv); bp.T = pb.T; bp.H = pb.H; bp.NT = NT; bp.scale = pb.scale;
   bp.total = NT * pb.B * pb.H;
-  if ((rc = opt_in_smem(k_bwd_main, BWD_SMEM))) return rc;
-  const int grid = bp.total < sm_count() ? bp.total : sm_count();
-  KernelScope ks("sm100_bwd_main", st);
-  k_bwd_main<<<grid, NTHREADS, BWD_SMEM, st>>>(bp);
-  return post_launch();
+  if (p.grad_dtype == TOPS_F32) return launch_bwd_main<float, float>(bp, st);
+  if (p.dg_dtype == TOPS_F32) return launch_bwd_main<__nv_bfloat16, float>(bp, st);
+  return launch_bwd_main<__nv_bfloat16, __nv_bfloat16>(bp, st);
 }
 
 #ifdef TOPS_TIMING

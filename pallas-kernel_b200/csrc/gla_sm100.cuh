@@ -9,6 +9,8 @@ namespace sm100 {
 bool supported(const tops_chunk_problem& pb);
 size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p);
 int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+// output dtype combinations the backward kernel writes: (dq/dk, dg) = (fp32, fp32), (bf16, fp32), (bf16, bf16)
+bool bwd_dtypes_ok(const tops_chunk_bwd_params& p);
 size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p);
 int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 // Reads the device error word (0 = no bounded wait has ever given up).

@@ -341,7 +341,7 @@ static size_t bwd_layout(const tops_chunk_bwd_params* p, void* ws, cudaStream_t 
 
 extern "C" size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p) {
   if (!p || check_problem(p->pb)) return 0;
-  if (use_sm100(p->pb) && p->grad_dtype == TOPS_F32) return sm100::bwd_workspace_bytes(*p);
+  if (use_sm100(p->pb) && sm100::bwd_dtypes_ok(*p)) return sm100::bwd_workspace_bytes(*p);
   Problem pb;
   return bwd_layout(p, nullptr, nullptr, false, &pb, nullptr, nullptr) + 256;
 }
@@ -356,7 +356,8 @@ extern "C" int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* wor
   if (p->pb.impl == TOPS_IMPL_SM100 && !sm100::supported(p->pb)) return TOPS_E_UNSUPPORTED;
   if (!workspace || workspace_bytes < tops_b200_chunk_bwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (use_sm100(p->pb) && p->grad_dtype == TOPS_F32) return sm100::chunk_bwd(*p, workspace, workspace_bytes, st);
+  if (use_sm100(p->pb) && sm100::bwd_dtypes_ok(*p)) return sm100::chunk_bwd(*p, workspace, workspace_bytes, st);
+  if (p->dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;   // the generic kernels write dg in fp32 only
 
   Problem pb;
   BwdLayout L;
@@ -376,11 +377,11 @@ extern "C" int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* wor
   b.q = p->q; b.k = p->k; b.v = p->v; b.do_ = p->do_; b.A = L.A; b.dA = L.dA; b.h = L.h; b.dh = L.dh;
   b.dq = p->dq; b.dk = p->dk; b.dv = p->dv; b.grad_dtype = p->grad_dtype;
   b.dg_stage = nullptr; b.dg_tile_stride = 0;
-  if (p->dg && kind == TOPS_GATE_PER_CHANNEL) b.dg_stage = p->dg;
+  if (p->dg && kind == TOPS_GATE_PER_CHANNEL) b.dg_stage = reinterpret_cast<float*>(p->dg);
   if (p->dg && kind == TOPS_GATE_SCALAR) { b.dg_stage = L.dg_part; b.dg_tile_stride = L.dg_stride; }
   if ((rc = generic::launch_bwd(pb, b, st))) return rc;
   if (p->dg && kind == TOPS_GATE_SCALAR)
-    return generic::launch_sum_partials(L.dg_part, L.dg_stride, L.tilesK, p->dg, L.dg_stride, st);
+    return generic::launch_sum_partials(L.dg_part, L.dg_stride, L.tilesK, reinterpret_cast<float*>(p->dg), L.dg_stride, st);
   return TOPS_OK;
 }
 

@@ -51,9 +51,13 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
 
 
 def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dtype, want_dg, want_dh0,
-                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None):
+                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False):
     """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0).  `h_saved`
-    is the `h` returned by chunk_fwd_call(want_h=True) on the same inputs."""
+    is the scratch returned by chunk_fwd_call(want_saved=True) on the same inputs.
+    With `primal_dtypes` the gradients come back in the dtypes of their primals
+    (dq, dk as q, k; dg as the gate), as the reference's accelerator kernel
+    writes them (`tops/ops/gla/chunk.py:1551-1554`): the tcgen05 kernel then
+    writes bf16 directly, any other kernel family writes fp32 and is cast."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     dev = q.device
@@ -65,28 +69,36 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
     h0 = None if h0 is None else h0.float().contiguous()
     dht = None if dht is None else dht.float().contiguous()
     N = B if cu_seqlens is None else len(cu_seqlens) - 1
-    dq = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
-    dk = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
-    dv = torch.empty(B, T, H, V, dtype=do.dtype, device=dev)
-    dg = None
-    if want_dg and gate_kind == L.GATE_PER_CHANNEL:
-        dg = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
-    elif want_dg and gate_kind == L.GATE_SCALAR:
-        dg = torch.empty(B, T, H, dtype=torch.float32, device=dev)
-    dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
     keep = []
     p = L.ChunkBwdParams()
     p.pb = make_problem(B, T, H, K, V, chunk, L.dtype_code(q.dtype),
                         L.F32 if gate is None else L.dtype_code(gate.dtype), gate_kind, scale, impl,
                         cu_seqlens, keep)
+    dg_dtype = torch.float32
+    direct = primal_dtypes and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100
+    if direct:
+        grad_dtype, dg_dtype = q.dtype, gate.dtype
+    dq = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
+    dk = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
+    dv = torch.empty(B, T, H, V, dtype=do.dtype, device=dev)
+    dg = None
+    if want_dg and gate_kind == L.GATE_PER_CHANNEL:
+        dg = torch.empty(B, T, H, K, dtype=dg_dtype, device=dev)
+    elif want_dg and gate_kind == L.GATE_SCALAR:
+        dg = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    dh0 = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
     p.q, p.k, p.v, p.g, p.h0, p.do_, p.dht = (L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(gate), L.ptr(h0), L.ptr(do),
                                               L.ptr(dht))
     p.dq, p.dk, p.dv, p.dg, p.dh0 = L.ptr(dq), L.ptr(dk), L.ptr(dv), L.ptr(dg), L.ptr(dh0)
     p.grad_dtype = L.dtype_code(grad_dtype)
+    p.dg_dtype = L.dtype_code(dg_dtype)
     if h_saved is not None:
         assert h_saved.dtype == q.dtype and h_saved.shape[-3:] == (H, K, V)
         p.h_saved = L.ptr(h_saved)
     ws = L.workspace(L.lib.tops_b200_chunk_bwd_workspace_bytes(C.byref(p)), dev)
     L.check(L.lib.tops_b200_chunk_gla_bwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)),
             "chunk_gla_bwd")
+    if primal_dtypes and not direct:
+        dq, dk = dq.to(q.dtype), dk.to(k.dtype)
+        dg = dg if dg is None or gate is None else dg.to(gate.dtype)
     return dq, dk, dv, dg, dh0

@@ -82,11 +82,11 @@ class _ChunkGLA(torch.autograd.Function):
     def backward(ctx, do, dht):
         q, k, v, g, h0, hs = ctx.saved_tensors
         kind = L.GATE_PER_CHANNEL if g is not None else L.GATE_NONE
-        dq, dk, dv, dg, dh0 = chunk_bwd_call(q, k, v, g, kind, ctx.scale, h0, do.to(q.dtype), dht, ctx.chunk,
-                                             torch.float32, g is not None, h0 is not None, ctx.cu, h_saved=hs)
         # cotangents take the primal's dtype at this boundary
-        return (dq.to(q.dtype), dk.to(k.dtype), dv, None if g is None else dg.to(g.dtype),
-                None if h0 is None else dh0.to(h0.dtype), None, None, None, None)
+        dq, dk, dv, dg, dh0 = chunk_bwd_call(q, k, v, g, kind, ctx.scale, h0, do.to(q.dtype), dht, ctx.chunk,
+                                             torch.float32, g is not None, h0 is not None, ctx.cu, h_saved=hs,
+                                             primal_dtypes=True)
+        return (dq, dk, dv, dg, None if h0 is None else dh0.to(h0.dtype), None, None, None, None)
 
 
 def chunk_gla(q, k, v, g=None, g_gamma=None, scale=None, initial_state=None, output_final_state=False,

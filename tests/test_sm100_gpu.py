@@ -80,3 +80,25 @@ def test_sm100_rejects_what_it_cannot_take():
     x = to_cuda(make_inputs(33, 1, 100, 1, 128, 128, dtype=torch.bfloat16))      # T not a multiple of 64
     with pytest.raises(L.TopsError):
         chunk_fwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, 0.1, None, False, 64, impl=L.IMPL_SM100)
+
+
+def test_sm100_gradients_in_primal_dtypes():
+    """dq, dk, dg written in bf16 by the kernel (what the reference's accelerator kernel does,
+    tops/ops/gla/chunk.py:1551-1554) are the fp32 results rounded once."""
+    from tops_b200 import _lib as L
+    from tops_b200.ops._chunk import chunk_bwd_call
+    from tops_b200.synth import make_inputs
+    x = to_cuda(make_inputs(34, 2, 256, 3, 128, 128, dtype=torch.bfloat16, with_h0=True, with_grads=True))
+    args = (x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, 128 ** -0.5, x["h0"], x["do"], x["dht"], 64,
+            torch.float32, True, True)
+    wide = chunk_bwd_call(*args)
+    narrow = chunk_bwd_call(*args, primal_dtypes=True)
+    torch.cuda.synchronize()
+    assert L.device_error() == 0
+    for i in (0, 1, 3):      # dq, dk, dg
+        assert narrow[i].dtype == torch.bfloat16 and wide[i].dtype == torch.float32
+        assert torch.equal(narrow[i], wide[i].to(torch.bfloat16))
+    assert torch.equal(narrow[2], wide[2]) and torch.equal(narrow[4], wide[4])
+    # a kernel family without the narrow outputs returns the same dtypes through a cast
+    slow = chunk_bwd_call(*args, impl=L.IMPL_GENERIC, primal_dtypes=True)
+    assert slow[0].dtype == torch.bfloat16 and slow[3].dtype == torch.bfloat16
