@@ -136,97 +136,119 @@ __device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
   return y;
 }
 
-// One block per (batch, head); the whole K x V state lives in registers
-// (thread (q4, lane, seg): row k = 32 q4 + lane, columns 32 seg .. 32 seg + 31).
-// Software pipeline over the chunks p (in scan order):
-//   iteration p:  store h'_p;  gate x(p+1) in place (exponents E(p+1) from tensor memory);
-//                 __syncthreads;  [thread 0] state product of chunk p+1 -> accumulator (p+1)&1,
-//                 [thread 32] exponent product of chunk p+2;  wait for the state product of chunk p;
-//                 state <- state * exp(G_n(p)) + D(p);  [thread 64] TMA for chunk p+3.
-// so the tensor-core latency of one chunk hides behind the gating of the next, and there is one
-// block-wide barrier per chunk.  x/y tiles: 3 stages, g tiles: 2 stages.
+// One block per (batch, head): 16 compute warps and one driver warp.  The whole K x V state lives in
+// registers of the compute warps (thread (q4, lane, seg): row k = 32 q4 + lane, columns 32 seg .. + 31).
+// Software pipeline over the chunks p (in scan order), one block-wide barrier per chunk:
+//   compute warps, iteration p:  stage h'_p for its TMA store;  gate x(p+1) in place (its exponents
+//       were put in tensor memory two iterations ago);  barrier;  wait for the state product of
+//       chunk p;  state <- state * exp(G_n(p)) + D(p).
+//   driver thread, iteration p:  barrier;  state product of chunk p+1 -> accumulator (p+1)&1;  TMA store
+//       of h'_p;  exponent product of chunk p+3 -> exponent slot (p+1)&1;  TMA loads of x, y of chunk
+//       p+3 and g of chunk p+4.
+// No compute warp ever blocks on the issue of a product or a copy.  x/y and g tiles: 3 stages each;
+// state staging: 2 tiles.
+constexpr int SCAN_THREADS = NTHREADS + 32;
+struct ScanShared {
+  uint64_t fullg[3], fullxy[3], ebar[2], sbar[2];
+  uint32_t tmem_slot;
+  int abort_flag;
+  float gn[2][D], e0[2][D];   // row 63 (G_n) and row 0 of the exponent tile, per channel
+};
+
 template <bool BWD>
-__global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
+__global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ ScanParams p) {
+  // every shared object is carved from the dynamic allocation, whose start is 1024-byte aligned when the
+  // kernel has no static shared memory (checked below: the swizzled tiles need that alignment)
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* xs = smem;                       // 3 x (64 x 128): x, gated in place
   uint8_t* ys = xs + 3 * TILE64;            // 3 x (64 x 128): y
-  uint8_t* gs = ys + 3 * TILE64;            // 2 x (64 x 128): g
-  uint8_t* mt = gs + 2 * TILE64;            // exponent pattern, rows repeated to 128
+  uint8_t* gs = ys + 3 * TILE64;            // 3 x (64 x 128): g
+  uint8_t* mt = gs + 3 * TILE64;            // exponent pattern, rows repeated to 128
   uint8_t* hst = mt + 2 * SLAB64;           // 2 x (128 x 128) bf16: chunk-start states on their way to HBM
-  __shared__ uint64_t fullg[2], fullxy[3], ebar, sbar[2];
-  __shared__ uint32_t tmem_slot;
-  __shared__ float gn_s[2][D], e0_s[2][D];  // row 63 (G_n) and row 0 of the exponent tile, per channel
-  __shared__ volatile int abort_flag;
+  ScanShared& sh = *reinterpret_cast<ScanShared*>(hst + 2 * TILE128);
+  volatile int* abort_flag = &sh.abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
+  const bool driver = warp == 16;
+  const int q4 = warp & 3, seg = (warp >> 2) & 3, col = q4 * 32 + lane;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
-  constexpr uint32_t cE = 0, cS = 128;      // tensor-memory columns: exponents, two state-product accumulators
+  // tensor-memory columns: two exponent tiles, two state-product accumulators
+  constexpr uint32_t cE = 0, cS = 256;
+  if ((smem_u32(smem) & 1023u) != 0) {   // uniform over the block
+    if (tid == 0) fail(12);
+    return;
+  }
 
   auto chunk_row = [&](int pp) { return b * p.T + (BWD ? NT - 1 - pp : pp) * C; };
   auto issue_g = [&](int pp) {
-    uint8_t* dst = gs + (pp & 1) * TILE64;
-    mbar_expect_tx(&fullg[pp & 1], TILE64);
-    tma_load_3d(dst, &p.mg, &fullg[pp & 1], 0, h, chunk_row(pp));
-    tma_load_3d(dst + SLAB64, &p.mg, &fullg[pp & 1], 64, h, chunk_row(pp));
+    uint8_t* dst = gs + (pp % 3) * TILE64;
+    mbar_expect_tx(&sh.fullg[pp % 3], TILE64);
+    tma_load_3d(dst, &p.mg, &sh.fullg[pp % 3], 0, h, chunk_row(pp));
+    tma_load_3d(dst + SLAB64, &p.mg, &sh.fullg[pp % 3], 64, h, chunk_row(pp));
   };
   auto issue_xy = [&](int pp) {
     const int st = pp % 3;
-    mbar_expect_tx(&fullxy[st], 2 * TILE64);
-    tma_load_3d(xs + st * TILE64, &p.mx, &fullxy[st], 0, h, chunk_row(pp));
-    tma_load_3d(xs + st * TILE64 + SLAB64, &p.mx, &fullxy[st], 64, h, chunk_row(pp));
-    tma_load_3d(ys + st * TILE64, &p.my, &fullxy[st], 0, h, chunk_row(pp));
-    tma_load_3d(ys + st * TILE64 + SLAB64, &p.my, &fullxy[st], 64, h, chunk_row(pp));
+    mbar_expect_tx(&sh.fullxy[st], 2 * TILE64);
+    tma_load_3d(xs + st * TILE64, &p.mx, &sh.fullxy[st], 0, h, chunk_row(pp));
+    tma_load_3d(xs + st * TILE64 + SLAB64, &p.mx, &sh.fullxy[st], 64, h, chunk_row(pp));
+    tma_load_3d(ys + st * TILE64, &p.my, &sh.fullxy[st], 0, h, chunk_row(pp));
+    tma_load_3d(ys + st * TILE64 + SLAB64, &p.my, &sh.fullxy[st], 64, h, chunk_row(pp));
   };
   if (tid == 0) {
-    mbar_init(&fullg[0], 1); mbar_init(&fullg[1], 1);
-    mbar_init(&fullxy[0], 1); mbar_init(&fullxy[1], 1); mbar_init(&fullxy[2], 1);
-    mbar_init(&ebar, 1); mbar_init(&sbar[0], 1); mbar_init(&sbar[1], 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&sh.fullg[i], 1); mbar_init(&sh.fullxy[i], 1); }
+    mbar_init(&sh.ebar[0], 1); mbar_init(&sh.ebar[1], 1); mbar_init(&sh.sbar[0], 1); mbar_init(&sh.sbar[1], 1);
     fence_barrier_init();
-    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
-    abort_flag = 0;
-    issue_g(0); issue_xy(0);
-    if (NT > 1) { issue_g(1); issue_xy(1); }
-    if (NT > 2) issue_xy(2);
+    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my); tma_prefetch_desc(&p.mst);
+    sh.abort_flag = 0;
+    for (int c = 0; c < 3 && c < NT; ++c) { issue_g(c); issue_xy(c); }
   }
   __syncwarp();
-  if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
   build_tri_tile(mt, 128, BWD ? TRI_INCL : TRI_REVN);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tm = tmem_slot;
+  const uint32_t tm = sh.tmem_slot;
   const uint32_t lane_base = q4 * 32;
+  TDECL();
 
   // exponents E = pattern . g of chunk pp: [time (repeated to 128 lanes)][channel]; row 63 is G_n
   auto issue_gate_mma = [&](int pp) {
-    const uint32_t ga = smem_u32(gs + (pp & 1) * TILE64), ma = smem_u32(mt);
+    if (!mbar_wait(&sh.fullg[pp % 3], (pp / 3) & 1)) { *abort_flag = 1; fail(1); }
+    tc_fence_after();
+    const uint32_t ga = smem_u32(gs + (pp % 3) * TILE64), ma = smem_u32(mt);
 #pragma unroll
     for (int j0 = 0; j0 < C; j0 += 16)
-      umma_bf16(tm + cE, desc_kmajor(ma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
-    umma_commit(&ebar);
+      umma_bf16(tm + cE + (pp & 1) * 128, desc_kmajor(ma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0),
+                umma_idesc(128, 128, 0, 1), j0 > 0);
+    umma_commit(&sh.ebar[pp & 1]);
   };
   auto issue_state_mma = [&](int pp) {
     const uint32_t xa = smem_u32(xs + (pp % 3) * TILE64), ya = smem_u32(ys + (pp % 3) * TILE64);
+    tc_fence_after();
 #pragma unroll
     for (int k0 = 0; k0 < C; k0 += 16)
       umma_bf16(tm + cS + (pp & 1) * 128, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0),
                 umma_idesc(128, 128, 1, 1), k0 > 0);
-    umma_commit(&sbar[pp & 1]);
+    umma_commit(&sh.sbar[pp & 1]);
   };
-  // gate x of chunk pp in place and publish G_n (and G_n - G_0) of its channels
+  // gate x of chunk pp in place and publish G_n (and G_n - G_0, or G_0) of its channels
   auto gate_chunk = [&](int pp) {
-    if (!mbar_wait(&ebar, pp & 1) || !mbar_wait(&fullxy[pp % 3], (pp / 3) & 1)) { abort_flag = 1; fail(1); }
+    if (!mbar_wait(&sh.ebar[pp & 1], (pp >> 1) & 1) || !mbar_wait(&sh.fullxy[pp % 3], (pp / 3) & 1)) {
+      *abort_flag = 1;
+      fail(1);
+    }
     tc_fence_after();
+    TSTAMP(7);
     const int i = (q4 * 32 + lane) & 63;          // time row of this thread
     const int cg = (q4 >> 1) * 4 + seg;           // its 16 channels
     float e[16];
-    tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), e);
+    tmem_ld16(tmem_addr(tm, lane_base, cE + (pp & 1) * 128 + cg * 16), e);
+    TSTAMP(8);
     if (i == 63) {
 #pragma unroll
-      for (int t = 0; t < 16; ++t) gn_s[pp & 1][cg * 16 + t] = e[t];
+      for (int t = 0; t < 16; ++t) sh.gn[pp & 1][cg * 16 + t] = e[t];
       if (!BWD) {
 #pragma unroll
         for (int t = 0; t < 16; ++t) e[t] = 0.f;   // row 63 of TRI_REVN carries G_n, its own exponent is 0
@@ -234,7 +256,7 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
     }
     if (i == 0) {   // forward: G_n - G_0; reverse: G_0
 #pragma unroll
-      for (int t = 0; t < 16; ++t) e0_s[pp & 1][cg * 16 + t] = e[t];
+      for (int t = 0; t < 16; ++t) sh.e0[pp & 1][cg * 16 + t] = e[t];
     }
 #pragma unroll
     for (int t = 0; t < 16; ++t) e[t] = BWD ? fast_exp(e[t]) * p.scale : fast_exp(e[t]);
@@ -245,121 +267,120 @@ __global__ void __launch_bounds__(NTHREADS) k_scan(const __grid_constant__ ScanP
       const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
       *reinterpret_cast<uint4*>(xt + off) = scale8(*reinterpret_cast<const uint4*>(xt + off), e + 8 * u);
     }
+    TSTAMP(9);
     fence_async_smem();
     tc_fence_before();
+    TSTAMP(10);
+  };
+  // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2;
+  // reverse states as dh * exp(G_n - mid) = dh * exp((G_n - G_0) / 2)
+  auto state_scale = [&](int pp) {
+    const float gnv = sh.gn[pp & 1][col], e0 = sh.e0[pp & 1][col];
+    return BWD ? fast_exp(0.5f * (gnv - e0)) : fast_exp(gnv - 0.5f * e0) * p.scale;
   };
 
-  // fp32 state: row k = col, columns 32 seg .. + 31
-  float S[32];
-  {
-    const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-      S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
+  if (driver) {
+    // ------------------------------------------------------------------ products and copies
+    if (lane == 0) {
+      issue_gate_mma(0);
+      if (NT > 1) issue_gate_mma(1);
     }
-  }
-  // prologue: exponents and gating of chunk 0, its state product, exponents of chunk 1
-  if (tid == 0) {
-    if (!mbar_wait(&fullg[0], 0)) { abort_flag = 1; fail(1); }
-    tc_fence_after();
-    issue_gate_mma(0);
-  }
-  __syncwarp();
-  gate_chunk(0);
-  __syncthreads();
-  bool ok = !abort_flag;
-  float decay = 1.f, hscale = 1.f;
-  if (ok) {
-    const float gnv = gn_s[0][col];
-    decay = fast_exp(gnv);
-    // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2;
-    // reverse states as dh * exp(G_n - mid) = dh * exp((G_n - G_0) / 2)
-    hscale = BWD ? fast_exp(0.5f * (gnv - e0_s[0][col])) : fast_exp(gnv - 0.5f * e0_s[0][col]) * p.scale;
-    if (tid == 0) {
-      tc_fence_after();
+    __syncthreads();   // chunk 0 is gated
+    bool ok = !*abort_flag;
+    if (ok && lane == 0) {
       issue_state_mma(0);
-    } else if (tid == 32 && NT > 1) {
-      if (!mbar_wait(&fullg[1], 0)) { abort_flag = 1; fail(1); }
-      tc_fence_after();
-      issue_gate_mma(1);
-    } else if (tid == 64 && NT > 2) {
-      issue_g(2);
+      if (NT > 2) issue_gate_mma(2);
+      if (NT > 3) issue_g(3);    // into the stage of chunk 0, whose exponent product is complete
     }
-    __syncwarp();
-  }
-  TDECL();
-  for (int pp = 0; ok && pp < NT; ++pp) {
-    const int ci = BWD ? NT - 1 - pp : pp;
-    TSTART();
-    // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
-    // memory in the tile format of the states tensor map and written out by a TMA store
-    {
-      uint8_t* tile = hst + (pp & 1) * TILE128;
-#pragma unroll
-      for (int j = 0; j < 32; j += 8)
-        *reinterpret_cast<uint4*>(tile + tile_off(128, col, seg * 32 + j)) =
-            make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
-                       pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
-      fence_async_smem();
-    }
-    TSTAMP(0);
-    if (pp + 1 < NT) gate_chunk(pp + 1);
-    if (tid == 96) tma_store_wait_read();   // the store of chunk pp-1 has drained its staging tile
-    __syncwarp();
-    TSTAMP(1);
-    __syncthreads();
-    TSTAMP(2);
-    if (abort_flag) { ok = false; break; }
-    if (tid == 96) {
-      const int hrow = ((b * NT + ci) * p.H + h) * D;
-      tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
-      tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
-      tma_store_commit();
-    }
-    float decay_n = 1.f, hscale_n = 1.f;
-    if (pp + 1 < NT) {
-      const float gnv = gn_s[(pp + 1) & 1][col];
-      decay_n = fast_exp(gnv);
-      hscale_n = BWD ? fast_exp(0.5f * (gnv - e0_s[(pp + 1) & 1][col]))
-                     : fast_exp(gnv - 0.5f * e0_s[(pp + 1) & 1][col]) * p.scale;
-      if (tid == 0) {
-        tc_fence_after();
-        issue_state_mma(pp + 1);
-      } else if (tid == 32 && pp + 2 < NT) {
-        if (!mbar_wait(&fullg[(pp + 2) & 1], ((pp + 2) >> 1) & 1)) { abort_flag = 1; fail(1); }
-        tc_fence_after();
-        issue_gate_mma(pp + 2);
+    for (int pp = 0; ok && pp < NT; ++pp) {
+      // the store of chunk pp-1 has read its staging tile: after the barrier the compute warps may
+      // overwrite it (with the state of chunk pp+1)
+      if (lane == 0) tma_store_wait_read();
+      __syncthreads();           // h'_pp is staged, chunk pp+1 is gated
+      if (*abort_flag) break;
+      if (lane == 0) {
+        if (pp + 1 < NT) issue_state_mma(pp + 1);
+        const int ci = BWD ? NT - 1 - pp : pp;
+        const int hrow = ((b * NT + ci) * p.H + h) * D;
+        tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
+        tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
+        tma_store_commit();
+        if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
+        if (pp + 4 < NT) issue_g(pp + 4);          // the stage of chunk pp+1, whose exponent product is complete
+        if (pp + 3 < NT) {                         // the x/y stage of chunk pp is free once its state product is done
+          if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
+          issue_xy(pp + 3);
+        }
       }
       __syncwarp();
     }
-    TSTAMP(3);
-    if (!mbar_wait(&sbar[pp & 1], (pp >> 1) & 1)) { abort_flag = 1; fail(2); }
-    tc_fence_after();
-    TSTAMP(4);
+    if (lane == 0) tma_store_wait_all();
+  } else {
+    // ------------------------------------------------------------------ state in registers
+    // fp32 state: row k = col, columns 32 seg .. + 31
+    float S[32];
     {
-      float d[32];
-      tmem_ld32(tmem_addr(tm, lane_base, cS + (pp & 1) * 128 + seg * 32), d);
+      const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
 #pragma unroll
-      for (int t = 0; t < 32; ++t) S[t] = fmaf(S[t], decay, d[t]);
+      for (int j = 0; j < 32; j += 4) {
+        float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
+      }
     }
-    tc_fence_before();
-    TSTAMP(5);
-    // the x/y stage of chunk pp and the g stage of chunk pp+1 are free now
-    if (tid == 64) {
-      if (pp + 3 < NT) { issue_xy(pp + 3); issue_g(pp + 3); }
+    TSTART();
+    gate_chunk(0);
+    __syncthreads();
+    bool ok = !*abort_flag;
+    float decay = 1.f, hscale = 1.f;
+    if (ok) {
+      decay = fast_exp(sh.gn[0][col]);
+      hscale = state_scale(0);
     }
-    __syncwarp();
-    TSTAMP(6);
-    decay = decay_n;
-    hscale = hscale_n;
-  }
-  if (!BWD) { TFLUSH(); }
-  if (tid == 96) tma_store_wait_all();
-  if (ok && p.s_final) {
-    float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+    for (int pp = 0; ok && pp < NT; ++pp) {
+      TSTART();
+      // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
+      // memory in the tile format of the states tensor map and written out by a TMA store
+      {
+        uint8_t* tile = hst + (pp & 1) * TILE128;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+        for (int j = 0; j < 32; j += 8)
+          *reinterpret_cast<uint4*>(tile + tile_off(128, col, seg * 32 + j)) =
+              make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
+                         pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
+        fence_async_smem();
+      }
+      TSTAMP(0);
+      if (pp + 1 < NT) gate_chunk(pp + 1);
+      TSTAMP(1);
+      __syncthreads();
+      TSTAMP(2);
+      if (*abort_flag) { ok = false; break; }
+      float decay_n = 1.f, hscale_n = 1.f;
+      if (pp + 1 < NT) {
+        decay_n = fast_exp(sh.gn[(pp + 1) & 1][col]);
+        hscale_n = state_scale(pp + 1);
+      }
+      TSTAMP(3);
+      if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
+      tc_fence_after();
+      TSTAMP(4);
+      {
+        float d[32];
+        tmem_ld32(tmem_addr(tm, lane_base, cS + (pp & 1) * 128 + seg * 32), d);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) S[t] = fmaf(S[t], decay, d[t]);
+      }
+      tc_fence_before();
+      TSTAMP(5);
+      decay = decay_n;
+      hscale = hscale_n;
+    }
+    if (!BWD) { TFLUSH(); }
+    if (ok && p.s_final) {
+      float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -1026,7 +1047,7 @@ bool device_is_sm100() {
   return cached == 1;
 }
 
-constexpr size_t SCAN_SMEM = 8 * TILE64 + 2 * SLAB64 + 2 * TILE128 + 1024;
+constexpr size_t SCAN_SMEM = 9 * TILE64 + 2 * SLAB64 + 2 * TILE128 + sizeof(ScanShared);
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
 constexpr size_t BWD_SMEM = 7 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
 
@@ -1052,12 +1073,12 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* 
   if (bwd) {
     if ((rc = opt_in_smem(k_scan<true>, SCAN_SMEM))) return rc;
     KernelScope ks("sm100_bwd_dh", st);
-    k_scan<true><<<grid, NTHREADS, SCAN_SMEM, st>>>(sp);
+    k_scan<true><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
     return post_launch();
   }
   if ((rc = opt_in_smem(k_scan<false>, SCAN_SMEM))) return rc;
   KernelScope ks("sm100_fwd_h", st);
-  k_scan<false><<<grid, NTHREADS, SCAN_SMEM, st>>>(sp);
+  k_scan<false><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
   return post_launch();
 }
 
