@@ -146,6 +146,7 @@ def kernel_bytes(label, w, grad_bytes=4):
         # tcgen05 path
         "sm100_fwd_h": tok * (K + V + K) * in2 + state * in2 + 2 * bhkv * 4,
         "sm100_fwd_o": tok * (3 * K + 2 * V) * in2 + state * in2,
+        "sm100_fwd_fused": tok * (3 * K + 2 * V) * in2 + state * in2 + 2 * bhkv * 4,
         "sm100_bwd_dh": tok * (K + V + K) * in2 + state * in2 + 2 * bhkv * 4,
         "sm100_bwd_main": tok * (3 * K + 2 * V) * in2 + 2 * state * in2 + 3 * tok * K * grad_bytes + tok * V * in2,
     }

@@ -545,6 +545,276 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
 }
 
 // ===========================================================================
+// Fused forward: state scan and chunk outputs in one pass
+// ===========================================================================
+// One block per (batch, head) walks its chunks in order with the K x V state in registers, so the
+// chunk-start state never has to come back from HBM: per chunk it is staged once in shared memory
+// as the bf16 operand h' = h exp(mid) scale of the output product (and, when the caller keeps the
+// states for a backward pass, written out from there by a TMA store).  q, k, g, v are read once.
+//   exponents  E = G - mid   [time (repeated to 128 lanes)][channel]      (pattern TRI_MID)
+//              W[channel][0] = G_n,  W[channel][1] = G_n - mid            (pattern rows: ones, TRI_MID row 63)
+//   gating     q~ = q exp(E), k~ = k exp(-E) in place
+//   products   A = q~ k~^T;  o = q~ h' + tril(A) scale v;  D = k~^T v
+//   state      h <- h exp(G_n) + exp(G_n - mid) D      (k exp(G_n - G) = k~ exp(G_n - mid), per channel)
+// 16 compute warps (thread (q4, lane, seg): state row k = 32 q4 + lane, columns 32 seg .. + 31) and a
+// driver warp that issues every product and copy; two block-wide barriers per chunk.
+struct FusedParams {
+  CUtensorMap mq, mk, mg, mv;
+  CUtensorMap mst;         // the states tensor as [B*NT*H*128, 128] (TMA stores); unused when states == nullptr
+  const float* s0;         // h0 [B,H,K,V] or null
+  __nv_bfloat16* states;   // h' [B,NT,H,K,V] or null
+  float* s_final;          // ht or null
+  __nv_bfloat16* o;        // [B,T,H,V]
+  int T, H, NT;
+  float scale;
+};
+struct FusedShared {
+  uint64_t fullin[2], ebar, abar, sbar, obar;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+constexpr uint32_t FUSED_STAGE = 4 * TILE64;   // q, k, g, v
+constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 + sizeof(FusedShared);
+
+// 16 x 64 K-major pattern: row 0 sums the gates (G_n), row 1 gives G_n - mid = (G_n - G_0) / 2
+__device__ __forceinline__ void build_w_tile(uint8_t* tile) {
+  for (int idx = threadIdx.x; idx < 16 * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int j = c8 + 2 * t;
+      const float a = r == 0 ? 1.f : (r == 1 ? (j == 0 ? 0.f : 0.5f) : 0.f);
+      const float b = r == 0 ? 1.f : (r == 1 ? 0.5f : 0.f);
+      w[t] = pack_bf16(a, b);
+    }
+    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constant__ FusedParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* in = smem;                         // 2 stages x (q, k, g, v)
+  uint8_t* hst = in + 2 * FUSED_STAGE;        // 2 x (128 x 128) bf16: h' of the current chunk
+  uint8_t* mt = hst + 2 * TILE128;            // TRI_MID pattern, rows repeated to 128
+  uint8_t* wt = mt + 2 * SLAB64;              // 16 x 64 pattern for G_n and G_n - mid
+  FusedShared& sh = *reinterpret_cast<FusedShared*>(wt + 2048);
+  volatile int* abort_flag = &sh.abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool driver = warp == 16;
+  const int q4 = warp & 3, seg = (warp >> 2) & 3, col = q4 * 32 + lane;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int NT = p.NT;
+  constexpr uint32_t cE = 0, cD = 128, cO = 256, cA = 384, cW = 448;
+  if ((smem_u32(smem) & 1023u) != 0) {   // uniform over the block
+    if (tid == 0) fail(12);
+    return;
+  }
+  auto issue_load = [&](int pp) {
+    uint8_t* qs = in + (pp & 1) * FUSED_STAGE;
+    uint8_t *ks = qs + TILE64, *gs = ks + TILE64, *vs = gs + TILE64;
+    uint64_t* bar = &sh.fullin[pp & 1];
+    const int row = b * p.T + pp * C;
+    mbar_expect_tx(bar, FUSED_STAGE);
+    tma_load_3d(gs, &p.mg, bar, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, bar, 64, h, row);
+    tma_load_3d(qs, &p.mq, bar, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, bar, 64, h, row);
+    tma_load_3d(ks, &p.mk, bar, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, bar, 64, h, row);
+    tma_load_3d(vs, &p.mv, bar, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, bar, 64, h, row);
+  };
+  if (tid == 0) {
+    mbar_init(&sh.fullin[0], 1); mbar_init(&sh.fullin[1], 1);
+    mbar_init(&sh.ebar, 1); mbar_init(&sh.abar, 1); mbar_init(&sh.sbar, 1); mbar_init(&sh.obar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&p.mq); tma_prefetch_desc(&p.mk); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.mv);
+    sh.abort_flag = 0;
+    issue_load(0);
+    if (NT > 1) issue_load(1);
+  }
+  __syncwarp();
+  if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
+  build_tri_tile(mt, 128, TRI_MID);
+  build_w_tile(wt);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm = sh.tmem_slot;
+  const uint32_t lane_base = q4 * 32;
+
+  if (driver) {
+    // ------------------------------------------------------------------ products and copies
+    auto issue_exponents = [&](int pp) {
+      if (!mbar_wait(&sh.fullin[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(3); }
+      tc_fence_after();
+      const uint32_t ga = smem_u32(in + (pp & 1) * FUSED_STAGE + 2 * TILE64), ma = smem_u32(mt), wa = smem_u32(wt);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // E: [time (repeated)][channel]
+        umma_bf16(tm + cE, desc_kmajor(ma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // W: [channel][G_n, G_n - mid, 0 ...]
+        umma_bf16(tm + cW, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(wa, 16, 0, j0), umma_idesc(128, 16, 1, 0), j0 > 0);
+      umma_commit(&sh.ebar);
+    };
+    if (lane == 0) issue_exponents(0);
+    __syncwarp();
+    for (int pp = 0; pp < NT; ++pp) {
+      const uint32_t ph = pp & 1;
+      uint8_t* qs = in + (pp & 1) * FUSED_STAGE;
+      uint8_t *ks = qs + TILE64, *gs = ks + TILE64, *vs = gs + TILE64;
+      uint8_t* ht = hst + (pp & 1) * TILE128;
+      // the state store of chunk pp-1 has read its staging tile, which the compute warps refill after
+      // the next barrier (with the state of chunk pp+1)
+      if (lane == 0) tma_store_wait_read();
+      __syncthreads();   // B1: q~, k~ and h' of chunk pp are in shared memory, E and W have been read
+      if (*abort_flag) break;
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t qa = smem_u32(qs), ka = smem_u32(ks), va = smem_u32(vs), ha = smem_u32(ht);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // A = q~ k~^T
+          umma_bf16(tm + cA, desc_kmajor(qa, 64, 0, k0), desc_kmajor(ka, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
+        umma_commit(&sh.abar);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // D[k][v] = sum_j k~[j][k] v[j][v]
+          umma_bf16(tm + cD, desc_mnmajor(ka, 64, k0, 0), desc_mnmajor(va, 64, k0, 0), umma_idesc(128, 128, 1, 1), k0 > 0);
+        umma_commit(&sh.sbar);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // o = q~ h'
+          umma_bf16(tm + cO, desc_kmajor(qa, 64, 0, k0), desc_mnmajor(ha, 128, k0, 0), umma_idesc(64, 128, 0, 1), k0 > 0);
+        if (p.states) {
+          const int hrow = ((b * NT + pp) * p.H + h) * D;
+          tma_store_2d(&p.mst, ht, 0, hrow);
+          tma_store_2d(&p.mst, ht + TILE128 / 2, 64, hrow);
+          tma_store_commit();
+        }
+      }
+      __syncthreads();   // B2: tril(A) scale is in shared memory (in the gate tile of this stage)
+      if (*abort_flag) break;
+      if (lane == 0) {
+        tc_fence_after();
+        const uint32_t pa = smem_u32(gs), va = smem_u32(vs);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // o += tril(A) scale v
+          umma_bf16(tm + cO, desc_kmajor(pa, 64, 0, k0), desc_mnmajor(va, 64, k0, 0), umma_idesc(64, 128, 0, 1), 1);
+        umma_commit(&sh.obar);
+        // exponents of the next chunk (E and W of this one were read before B1)
+        if (pp + 1 < NT) issue_exponents(pp + 1);
+        // every tile of this stage is dead once its products are complete
+        if (pp + 2 < NT) {
+          if (!mbar_wait(&sh.obar, ph)) { *abort_flag = 1; fail(5); }
+          issue_load(pp + 2);
+        }
+      }
+      __syncwarp();
+    }
+    if (lane == 0) tma_store_wait_all();
+  } else {
+    // ------------------------------------------------------------------ state in registers
+    float S[32];
+    {
+      const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
+      }
+    }
+    bool ok = true;
+    for (int pp = 0; ok && pp < NT; ++pp) {
+      const uint32_t ph = pp & 1;
+      uint8_t* qs = in + (pp & 1) * FUSED_STAGE;
+      uint8_t *ks = qs + TILE64, *gs = ks + TILE64;
+      uint8_t* ht = hst + (pp & 1) * TILE128;
+      if (!mbar_wait(&sh.fullin[pp & 1], (pp >> 1) & 1) || !mbar_wait(&sh.ebar, ph)) { *abort_flag = 1; fail(9); }
+      tc_fence_after();
+      // per-channel factors of this thread's state row
+      float decay, c2;
+      {
+        float w[8];
+        tmem_ld8(tmem_addr(tm, lane_base, cW), w);
+        decay = fast_exp(w[0]);                    // exp(G_n)
+        c2 = fast_exp(w[1]);                       // exp(G_n - mid)
+        const float hscale = fast_exp(w[0] - w[1]) * p.scale;   // exp(mid) scale
+#pragma unroll
+        for (int j = 0; j < 32; j += 8)
+          *reinterpret_cast<uint4*>(ht + tile_off(128, col, seg * 32 + j)) =
+              make_uint4(pack_bf16(S[j] * hscale, S[j + 1] * hscale), pack_bf16(S[j + 2] * hscale, S[j + 3] * hscale),
+                         pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
+      }
+      // gate q, k: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
+      {
+        const int i = (q4 * 32 + lane) & 63;
+        const int cg = (q4 >> 1) * 4 + seg;
+        float em[16];
+        tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), em);
+        const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+          float f[8], r[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            f[t] = fast_exp(em[8 * u + t]);
+            r[t] = fast_exp(-em[8 * u + t]);
+          }
+          *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), f);
+          *reinterpret_cast<uint4*>(ks + off) = scale8(*reinterpret_cast<const uint4*>(ks + off), r);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();   // B1
+      if (*abort_flag) { ok = false; break; }
+      // tril(A) scale -> bf16 operand in the (dead) gate tile
+      if (!mbar_wait(&sh.abar, ph)) { *abort_flag = 1; fail(4); }
+      tc_fence_after();
+      {
+        const int i = 16 * q4 + lane;   // rows of an M = 64 accumulator sit in lanes 0..15 of each quarter
+        float a[16];
+        tmem_ld16(tmem_addr(tm, lane_base, cA + seg * 16), a);
+        if (lane < 16) store_tril16(gs, i, seg * 16, a, p.scale);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();   // B2
+      if (*abort_flag) { ok = false; break; }
+      // state update while the last output product runs
+      if (!mbar_wait(&sh.sbar, ph)) { *abort_flag = 1; fail(2); }
+      tc_fence_after();
+      {
+        float d[32];
+        tmem_ld32(tmem_addr(tm, lane_base, cD + seg * 32), d);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) S[t] = fmaf(S[t], decay, c2 * d[t]);
+      }
+      if (!mbar_wait(&sh.obar, ph)) { *abort_flag = 1; fail(5); }
+      tc_fence_after();
+      {
+        const int i = 16 * q4 + lane;
+        __nv_bfloat16* dst = p.o + ((size_t)(b * p.T + pp * C + i) * p.H + h) * D + seg * 32;
+        float a[32];
+        tmem_ld32(tmem_addr(tm, lane_base, cO + seg * 32), a);
+        if (lane < 16) {
+#pragma unroll
+          for (int t = 0; t < 32; t += 8)
+            *reinterpret_cast<uint4*>(dst + t) = make_uint4(pack_bf16(a[t], a[t + 1]), pack_bf16(a[t + 2], a[t + 3]),
+                                                            pack_bf16(a[t + 4], a[t + 5]), pack_bf16(a[t + 6], a[t + 7]));
+        }
+      }
+      tc_fence_before();
+    }
+    if (ok && p.s_final) {
+      float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm, 512);
+}
+
+// ===========================================================================
 // Backward of the chunks (persistent: each block walks chunks blockIdx.x,
 // blockIdx.x + gridDim.x, ... and fetches the next chunk's tiles while the
 // tensor core and the epilogue of the current one are still busy)
@@ -1058,6 +1328,9 @@ int opt_in_smem(F f, size_t bytes) {
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+// from this many (batch, head) pairs on, the forward runs as one fused pass (one block per pair)
+// instead of a state scan followed by a chunk-parallel output kernel
+constexpr int kFusedMinBlocks = 48;
 
 int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* g, const void* y, const float* s0,
              void* states, float* s_final, cudaStream_t st) {
@@ -1105,10 +1378,29 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
       !aligned16(p.h0) || !aligned16(p.ht) || !aligned16(ws))
     return TOPS_E_ALIGN;
   void* h = p.saved_out ? p.saved_out : ws;
-  int rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, h, p.ht, st);
+  const int BT = pb.B * pb.T, NT = pb.T / C;
+  int rc;
+  if (pb.B * pb.H >= kFusedMinBlocks) {
+    // enough (batch, head) pairs to fill the GPU with one block each: one pass over q, k, g, v
+    FusedParams up;
+    if ((rc = act_map(&up.mq, p.q, BT, pb.H)) || (rc = act_map(&up.mk, p.k, BT, pb.H)) ||
+        (rc = act_map(&up.mg, p.g, BT, pb.H)) || (rc = act_map(&up.mv, p.v, BT, pb.H)))
+      return rc;
+    up.states = nullptr;
+    if (p.saved_out) {   // only a caller that keeps the states for its backward pass needs them in HBM
+      if ((rc = state_map(&up.mst, p.saved_out, (size_t)pb.B * NT * pb.H * D))) return rc;
+      up.states = reinterpret_cast<__nv_bfloat16*>(p.saved_out);
+    }
+    up.s0 = p.h0; up.s_final = p.ht; up.o = reinterpret_cast<__nv_bfloat16*>(p.o);
+    up.T = pb.T; up.H = pb.H; up.NT = NT; up.scale = pb.scale;
+    if ((rc = opt_in_smem(k_fwd_fused, FUSED_SMEM))) return rc;
+    KernelScope ks("sm100_fwd_fused", st);
+    k_fwd_fused<<<pb.B * pb.H, SCAN_THREADS, FUSED_SMEM, st>>>(up);
+    return post_launch();
+  }
+  rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, h, p.ht, st);
   if (rc) return rc;
   FwdOParams fp;
-  const int BT = pb.B * pb.T, NT = pb.T / C;
   if ((rc = act_map(&fp.mq, p.q, BT, pb.H)) || (rc = act_map(&fp.mk, p.k, BT, pb.H)) ||
       (rc = act_map(&fp.mg, p.g, BT, pb.H)) || (rc = act_map(&fp.mv, p.v, BT, pb.H)) ||
       (rc = state_map(&fp.mh, h, (size_t)pb.B * NT * pb.H * D)))
