@@ -574,7 +574,7 @@ struct FusedShared {
   int abort_flag;
 };
 constexpr uint32_t FUSED_STAGE = 4 * TILE64;   // q, k, g, v
-constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 + sizeof(FusedShared);
+constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 + TILE64 + sizeof(FusedShared);
 
 // 16 x 64 K-major pattern: row 0 sums the gates (G_n), row 1 gives G_n - mid = (G_n - G_0) / 2
 __device__ __forceinline__ void build_w_tile(uint8_t* tile) {
@@ -598,7 +598,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
   uint8_t* hst = in + 2 * FUSED_STAGE;        // 2 x (128 x 128) bf16: h' of the current chunk
   uint8_t* mt = hst + 2 * TILE128;            // TRI_MID pattern, rows repeated to 128
   uint8_t* wt = mt + 2 * SLAB64;              // 16 x 64 pattern for G_n and G_n - mid
-  FusedShared& sh = *reinterpret_cast<FusedShared*>(wt + 2048);
+  uint8_t* ost = wt + 2048;                   // 64 x 128 bf16: the outputs of a chunk, row-major, before they leave
+  FusedShared& sh = *reinterpret_cast<FusedShared*>(ost + TILE64);
   volatile int* abort_flag = &sh.abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool driver = warp == 16;
@@ -707,6 +708,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       }
       __syncwarp();
     }
+    __syncthreads();   // (the compute warps copy the last outputs after this barrier)
     if (lane == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ state in registers
@@ -719,6 +721,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
         S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
       }
     }
+    // Outputs leave in two steps: the accumulator rows (an M = 64 accumulator keeps 16 rows in the first
+    // 16 lanes of each warp) are packed to bf16 in a shared tile; after the next block-wide barrier every
+    // thread copies 32 contiguous bytes of it, so that a warp writes whole 256-byte rows.
+    auto copy_out = [&](int pp) {
+      const int r = tid >> 3, piece = tid & 7;   // 64 rows x 8 pieces of 16 channels
+      // 16-byte pieces of a row are stored XOR-permuted by the row number (bank conflicts of the writers)
+      const uint8_t* rowp = ost + r * 256;
+      uint4* dst = reinterpret_cast<uint4*>(p.o + ((size_t)(b * p.T + pp * C + r) * p.H + h) * D + piece * 16);
+      const uint4 x = *reinterpret_cast<const uint4*>(rowp + (((2 * piece) ^ r) & 15) * 16);
+      const uint4 y = *reinterpret_cast<const uint4*>(rowp + (((2 * piece + 1) ^ r) & 15) * 16);
+      dst[0] = x;
+      dst[1] = y;
+    };
     bool ok = true;
     for (int pp = 0; ok && pp < NT; ++pp) {
       const uint32_t ph = pp & 1;
@@ -765,6 +780,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       tc_fence_before();
       __syncthreads();   // B1
       if (*abort_flag) { ok = false; break; }
+      if (pp > 0) copy_out(pp - 1);   // staged before the barrier; the products of this chunk run meanwhile
       // tril(A) scale -> bf16 operand in the (dead) gate tile
       if (!mbar_wait(&sh.abar, ph)) { *abort_flag = 1; fail(4); }
       tc_fence_after();
@@ -791,18 +807,20 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       tc_fence_after();
       {
         const int i = 16 * q4 + lane;
-        __nv_bfloat16* dst = p.o + ((size_t)(b * p.T + pp * C + i) * p.H + h) * D + seg * 32;
         float a[32];
         tmem_ld32(tmem_addr(tm, lane_base, cO + seg * 32), a);
         if (lane < 16) {
 #pragma unroll
           for (int t = 0; t < 32; t += 8)
-            *reinterpret_cast<uint4*>(dst + t) = make_uint4(pack_bf16(a[t], a[t + 1]), pack_bf16(a[t + 2], a[t + 3]),
-                                                            pack_bf16(a[t + 4], a[t + 5]), pack_bf16(a[t + 6], a[t + 7]));
+            *reinterpret_cast<uint4*>(ost + i * 256 + (((seg * 4 + t / 8) ^ i) & 15) * 16) =
+                make_uint4(pack_bf16(a[t], a[t + 1]), pack_bf16(a[t + 2], a[t + 3]), pack_bf16(a[t + 4], a[t + 5]),
+                           pack_bf16(a[t + 6], a[t + 7]));
         }
       }
       tc_fence_before();
     }
+    __syncthreads();   // the outputs of the last chunk are staged
+    if (ok) copy_out(NT - 1);
     if (ok && p.s_final) {
       float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
 #pragma unroll
