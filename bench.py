@@ -410,15 +410,16 @@ def run_extra(args):
                "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                             "frac": nbytes / (ms * 1e-3) / 1e9 / hbm_peak, "peak_source": peak_kind}}
     elif args.workload == "simple_gla_long":
-        from tops_b200.ops.simple_gla import chunk_simple_gla_bwd, chunk_simple_gla_fwd
+        from tops_b200.ops.simple_gla import _fwd as simple_gla_fwd_keep, chunk_simple_gla_bwd
         B, T, H, K, V = 1, args.seq or 65536, 32, 128, 128
         x = {k: v.cuda() for k, v in make_inputs(4, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True,
                                                    with_grads=True).items()}
         sc = K ** -0.5
 
         def step():
-            chunk_simple_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, sc, x["h0"], True, 64)
-            chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"], x["dht"], sc, 64)
+            # what the differentiable op does: the forward keeps its chunk-start states for the backward
+            _, _, hs = simple_gla_fwd_keep(x["q"], x["k"], x["v"], x["g"], None, sc, x["h0"], True, 64, None, True)
+            chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"], x["dht"], sc, 64, h_saved=hs)
         ms = timed(step, args.steps, 2)
         out = {"metric": "simple_gla chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
                "config": {"workload": f"simple_gla B=1 T={T} H=32 K=V=128 chunk 64 bf16 (bf16 gate), one GPU"}}

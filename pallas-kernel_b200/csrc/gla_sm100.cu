@@ -92,10 +92,12 @@ __device__ __forceinline__ void fail(int code) { atomicCAS(&g_error, 0, code); }
 struct ScanParams {
   CUtensorMap mx, mg, my;  // x: k (fwd) / q (bwd); y: v / do
   CUtensorMap mst;         // the states tensor as [B*NT*H*128, 128] (TMA stores)
-  const float* s0;         // h0 / dht  [B,H,K,V] or null
-  __nv_bfloat16* states;   // h / dh    [B,NT,H,K,V]
-  float* s_final;          // ht / dh0  or null
-  int T, H, NT;
+  const float* s0;         // state each block starts from: [B,H,nseg,K,V] or null (zero)
+  __nv_bfloat16* states;   // h' / dh'  [B,T/64,H,K,V]; null: keep no chunk-start states (summary pass)
+  float* s_final;          // state each block ends with: [B,H,nseg,K,V] or null
+  float* gsum;             // summed log-gates of each block's chunks [B,H,nseg,K] or null
+  int T, H, NT;            // T: tokens per sequence; NT: chunks per block (T / 64 / nseg)
+  int nseg;                // time segments per sequence, one block each
   float scale;
 };
 
@@ -170,8 +172,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool driver = warp == 16;
   const int q4 = warp & 3, seg = (warp >> 2) & 3, col = q4 * 32 + lane;
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int blk = blockIdx.x, sg = blk % p.nseg, bh = blk / p.nseg, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
+  const bool keep_states = p.states != nullptr;
   // tensor-memory columns: two exponent tiles, two state-product accumulators
   constexpr uint32_t cE = 0, cS = 256;
   if ((smem_u32(smem) & 1023u) != 0) {   // uniform over the block
@@ -179,7 +182,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     return;
   }
 
-  auto chunk_row = [&](int pp) { return b * p.T + (BWD ? NT - 1 - pp : pp) * C; };
+  // chunk pp of this block (in scan order) within its sequence
+  auto chunk_of = [&](int pp) { return sg * NT + (BWD ? NT - 1 - pp : pp); };
+  auto chunk_row = [&](int pp) { return b * p.T + chunk_of(pp) * C; };
   auto issue_g = [&](int pp) {
     uint8_t* dst = gs + (pp % 3) * TILE64;
     mbar_expect_tx(&sh.fullg[pp % 3], TILE64);
@@ -198,7 +203,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     for (int i = 0; i < 3; ++i) { mbar_init(&sh.fullg[i], 1); mbar_init(&sh.fullxy[i], 1); }
     mbar_init(&sh.ebar[0], 1); mbar_init(&sh.ebar[1], 1); mbar_init(&sh.sbar[0], 1); mbar_init(&sh.sbar[1], 1);
     fence_barrier_init();
-    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my); tma_prefetch_desc(&p.mst);
+    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
+    if (p.states) tma_prefetch_desc(&p.mst);
     sh.abort_flag = 0;
     for (int c = 0; c < 3 && c < NT; ++c) { issue_g(c); issue_xy(c); }
   }
@@ -300,11 +306,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       if (*abort_flag) break;
       if (lane == 0) {
         if (pp + 1 < NT) issue_state_mma(pp + 1);
-        const int ci = BWD ? NT - 1 - pp : pp;
-        const int hrow = ((b * NT + ci) * p.H + h) * D;
-        tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
-        tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
-        tma_store_commit();
+        if (keep_states) {
+          const int hrow = ((b * (p.T / C) + chunk_of(pp)) * p.H + h) * D;
+          tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
+          tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
+          tma_store_commit();
+        }
         if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
         if (pp + 4 < NT) issue_g(pp + 4);          // the stage of chunk pp+1, whose exponent product is complete
         if (pp + 3 < NT) {                         // the x/y stage of chunk pp is free once its state product is done
@@ -320,13 +327,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     // fp32 state: row k = col, columns 32 seg .. + 31
     float S[32];
     {
-      const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
+      const float* src = p.s0 ? p.s0 + ((size_t)blk * D + col) * D + seg * 32 : nullptr;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
         S[j] = x.x; S[j + 1] = x.y; S[j + 2] = x.z; S[j + 3] = x.w;
       }
     }
+    float gtot = 0.f;   // summed log-gates of this thread's channel over the block's chunks
     TSTART();
     gate_chunk(0);
     __syncthreads();
@@ -340,7 +348,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       TSTART();
       // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
       // memory in the tile format of the states tensor map and written out by a TMA store
-      {
+      gtot += sh.gn[pp & 1][col];   // (published by the gating of this chunk, one iteration ago)
+      if (keep_states) {
         uint8_t* tile = hst + (pp & 1) * TILE128;
 #pragma unroll
         for (int j = 0; j < 32; j += 8)
@@ -377,14 +386,38 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     }
     if (!BWD) { TFLUSH(); }
     if (ok && p.s_final) {
-      float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+      float* dst = p.s_final + ((size_t)blk * D + col) * D + seg * 32;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
     }
+    if (ok && p.gsum && seg == 0) p.gsum[(size_t)blk * D + col] = gtot;
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+}
+
+// Joins the time segments of each (batch, head).  A segment acts on the state entering it as
+// h_out = h_in * exp(P) + S, with P the summed log-gates of its chunks (per channel) and S its end
+// state from a zero start.  Forward order for states, reverse order for state gradients.
+//   first [BH,K,V] or null;  P [BH,nseg,K];  S [BH,nseg,K,V];  start [BH,nseg,K,V] (out);  last [BH,K,V] or null (out)
+template <bool REVERSE>
+__global__ void k_join_segments(const float* first, const float* P, const float* S, float* start, float* last,
+                                int nseg) {
+  const int bh = blockIdx.x;
+  for (int e = threadIdx.x * 4; e < D * D; e += blockDim.x * 4) {
+    const int k = e / D;
+    float4 cur = first ? *reinterpret_cast<const float4*>(first + (size_t)bh * D * D + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < nseg; ++i) {
+      const int r = REVERSE ? nseg - 1 - i : i;
+      const size_t sb = ((size_t)bh * nseg + r) * D * D + e;
+      *reinterpret_cast<float4*>(start + sb) = cur;
+      const float w = __expf(P[((size_t)bh * nseg + r) * D + k]);
+      const float4 add = *reinterpret_cast<const float4*>(S + sb);
+      cur = make_float4(fmaf(cur.x, w, add.x), fmaf(cur.y, w, add.y), fmaf(cur.z, w, add.z), fmaf(cur.w, w, add.w));
+    }
+    if (last) *reinterpret_cast<float4*>(last + (size_t)bh * D * D + e) = cur;
+  }
 }
 
 // masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
@@ -561,11 +594,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
 struct FusedParams {
   CUtensorMap mq, mk, mg, mv;
   CUtensorMap mst;         // the states tensor as [B*NT*H*128, 128] (TMA stores); unused when states == nullptr
-  const float* s0;         // h0 [B,H,K,V] or null
-  __nv_bfloat16* states;   // h' [B,NT,H,K,V] or null
-  float* s_final;          // ht or null
+  const float* s0;         // state each block starts from: [B,H,nseg,K,V] or null (zero)
+  __nv_bfloat16* states;   // h' [B,T/64,H,K,V] or null
+  float* s_final;          // state each block ends with: [B,H,nseg,K,V] or null
   __nv_bfloat16* o;        // [B,T,H,V]
-  int T, H, NT;
+  int T, H, NT;            // T: tokens per sequence; NT: chunks per block (T / 64 / nseg)
+  int nseg;                // time segments per sequence, one block each
   float scale;
 };
 struct FusedShared {
@@ -604,8 +638,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool driver = warp == 16;
   const int q4 = warp & 3, seg = (warp >> 2) & 3, col = q4 * 32 + lane;
-  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int blk = blockIdx.x, sg = blk % p.nseg, bh = blk / p.nseg, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
+  const int c0 = sg * NT;   // first chunk of this block within its sequence
   constexpr uint32_t cE = 0, cD = 128, cO = 256, cA = 384, cW = 448;
   if ((smem_u32(smem) & 1023u) != 0) {   // uniform over the block
     if (tid == 0) fail(12);
@@ -615,7 +650,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
     uint8_t* qs = in + (pp & 1) * FUSED_STAGE;
     uint8_t *ks = qs + TILE64, *gs = ks + TILE64, *vs = gs + TILE64;
     uint64_t* bar = &sh.fullin[pp & 1];
-    const int row = b * p.T + pp * C;
+    const int row = b * p.T + (c0 + pp) * C;
     mbar_expect_tx(bar, FUSED_STAGE);
     tma_load_3d(gs, &p.mg, bar, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, bar, 64, h, row);
     tma_load_3d(qs, &p.mq, bar, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, bar, 64, h, row);
@@ -683,7 +718,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
         for (int k0 = 0; k0 < D; k0 += 16)   // o = q~ h'
           umma_bf16(tm + cO, desc_kmajor(qa, 64, 0, k0), desc_mnmajor(ha, 128, k0, 0), umma_idesc(64, 128, 0, 1), k0 > 0);
         if (p.states) {
-          const int hrow = ((b * NT + pp) * p.H + h) * D;
+          const int hrow = ((b * (p.T / C) + c0 + pp) * p.H + h) * D;
           tma_store_2d(&p.mst, ht, 0, hrow);
           tma_store_2d(&p.mst, ht + TILE128 / 2, 64, hrow);
           tma_store_commit();
@@ -714,7 +749,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
     // ------------------------------------------------------------------ state in registers
     float S[32];
     {
-      const float* src = p.s0 ? p.s0 + ((size_t)bh * D + col) * D + seg * 32 : nullptr;
+      const float* src = p.s0 ? p.s0 + ((size_t)blk * D + col) * D + seg * 32 : nullptr;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
         float4 x = src ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -728,7 +763,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       const int r = tid >> 3, piece = tid & 7;   // 64 rows x 8 pieces of 16 channels
       // 16-byte pieces of a row are stored XOR-permuted by the row number (bank conflicts of the writers)
       const uint8_t* rowp = ost + r * 256;
-      uint4* dst = reinterpret_cast<uint4*>(p.o + ((size_t)(b * p.T + pp * C + r) * p.H + h) * D + piece * 16);
+      uint4* dst = reinterpret_cast<uint4*>(p.o + ((size_t)(b * p.T + (c0 + pp) * C + r) * p.H + h) * D + piece * 16);
       const uint4 x = *reinterpret_cast<const uint4*>(rowp + (((2 * piece) ^ r) & 15) * 16);
       const uint4 y = *reinterpret_cast<const uint4*>(rowp + (((2 * piece + 1) ^ r) & 15) * 16);
       dst[0] = x;
@@ -822,7 +857,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
     __syncthreads();   // the outputs of the last chunk are staged
     if (ok) copy_out(NT - 1);
     if (ok && p.s_final) {
-      float* dst = p.s_final + ((size_t)bh * D + col) * D + seg * 32;
+      float* dst = p.s_final + ((size_t)blk * D + col) * D + seg * 32;
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
     }
@@ -1350,26 +1385,64 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 // instead of a state scan followed by a chunk-parallel output kernel
 constexpr int kFusedMinBlocks = 48;
 
-int run_scan(bool bwd, const tops_chunk_problem& pb, const void* x, const void* g, const void* y, const float* s0,
-             void* states, float* s_final, cudaStream_t st) {
+// One launch of the scan kernel over `nseg` time segments per (batch, head).  states == nullptr keeps
+// no chunk-start states (a summary pass: end states and summed gates only).
+int run_scan(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, const void* g, const void* y,
+             const float* s0, void* states, float* s_final, float* gsum, cudaStream_t st) {
   ScanParams sp;
   const int BT = pb.B * pb.T;
   int rc;
-  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.mg, g, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H)) ||
-      (rc = state_map(&sp.mst, states, (size_t)pb.B * (pb.T / C) * pb.H * D)))
+  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.mg, g, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H)))
     return rc;
-  sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final;
-  sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C; sp.scale = pb.scale;
-  dim3 grid(pb.B * pb.H);
+  if (states && (rc = state_map(&sp.mst, states, (size_t)pb.B * (pb.T / C) * pb.H * D))) return rc;
+  sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final; sp.gsum = gsum;
+  sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C / nseg; sp.nseg = nseg; sp.scale = pb.scale;
+  dim3 grid(pb.B * pb.H * nseg);
   if (bwd) {
     if ((rc = opt_in_smem(k_scan<true>, SCAN_SMEM))) return rc;
-    KernelScope ks("sm100_bwd_dh", st);
+    KernelScope ks(states ? "sm100_bwd_dh" : "sm100_bwd_dh_summary", st);
     k_scan<true><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
     return post_launch();
   }
   if ((rc = opt_in_smem(k_scan<false>, SCAN_SMEM))) return rc;
-  KernelScope ks("sm100_fwd_h", st);
+  KernelScope ks(states ? "sm100_fwd_h" : "sm100_fwd_h_summary", st);
   k_scan<false><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
+  return post_launch();
+}
+
+// Time segments per sequence.  The scans walk a sequence chunk by chunk with one block; when there are
+// too few (batch, head) pairs to fill the GPU, each sequence is cut into segments that run as blocks of
+// their own: a first pass finds what every segment does to the state entering it (end state from a zero
+// start and summed gates), a small kernel chains the segments, and the real pass starts every segment
+// from its true state.  At least four chunks per segment.
+int pick_segments(const tops_chunk_problem& pb) {
+  const int bh = pb.B * pb.H, nt = pb.T / C;
+  if (2 * bh > sm_count()) return 1;
+  int best = 1;
+  for (int n = 2; n * bh <= sm_count() && n * 4 <= nt; ++n)
+    if (nt % n == 0) best = n;
+  return best;
+}
+// fp32 scratch of a segmented scan: end states, entry states (nseg x [B,H,K,V] each) and summed gates
+size_t segment_floats(const tops_chunk_problem& pb, int nseg) {
+  return nseg > 1 ? (size_t)pb.B * pb.H * nseg * (2 * D * D + D) : 0;
+}
+struct SegmentScratch {
+  float *ends, *starts, *gsum;
+  SegmentScratch(float* base, const tops_chunk_problem& pb, int nseg) {
+    const size_t n = (size_t)pb.B * pb.H * nseg * D * D;
+    ends = base; starts = base + n; gsum = base + 2 * n;
+  }
+};
+// summary pass + join: leaves the state entering every segment in sc.starts and the state after the last
+// (forward) / before the first (reverse) segment in `last` (may be null)
+int segment_starts(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, const void* g, const void* y,
+                   const float* first, float* last, const SegmentScratch& sc, cudaStream_t st) {
+  int rc = run_scan(bwd, pb, nseg, x, g, y, nullptr, nullptr, sc.ends, sc.gsum, st);
+  if (rc) return rc;
+  KernelScope ks("sm100_join_segments", st);
+  if (bwd) k_join_segments<true><<<pb.B * pb.H, 512, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
+  else k_join_segments<false><<<pb.B * pb.H, 512, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
   return post_launch();
 }
 
@@ -1387,7 +1460,9 @@ static size_t state_bytes(const tops_chunk_problem& pb) {
   return align_up((size_t)pb.B * (pb.T / C) * pb.H * D * D * 2);
 }
 
-size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p) { return (p.saved_out ? 0 : state_bytes(p.pb)) + 256; }
+size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p) {
+  return (p.saved_out ? 0 : state_bytes(p.pb)) + segment_floats(p.pb, pick_segments(p.pb)) * sizeof(float) + 256;
+}
 
 int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st) {
   const tops_chunk_problem& pb = p.pb;
@@ -1395,11 +1470,22 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.o) ||
       !aligned16(p.h0) || !aligned16(p.ht) || !aligned16(ws))
     return TOPS_E_ALIGN;
-  void* h = p.saved_out ? p.saved_out : ws;
   const int BT = pb.B * pb.T, NT = pb.T / C;
+  const int nseg = pick_segments(pb);
+  // workspace: [chunk-start states unless the caller keeps them] [segment scratch]
+  char* wsp = reinterpret_cast<char*>(ws);
+  void* h = p.saved_out ? p.saved_out : wsp;
+  const SegmentScratch sc(reinterpret_cast<float*>(wsp + (p.saved_out ? 0 : state_bytes(pb))), pb, nseg);
   int rc;
-  if (pb.B * pb.H >= kFusedMinBlocks) {
-    // enough (batch, head) pairs to fill the GPU with one block each: one pass over q, k, g, v
+  const float* start = p.h0;
+  float* last = p.ht;
+  if (nseg > 1) {
+    if ((rc = segment_starts(false, pb, nseg, p.k, p.g, p.v, p.h0, p.ht, sc, st))) return rc;
+    start = sc.starts;
+    last = nullptr;   // the join kernel has written the final state
+  }
+  if (pb.B * pb.H * nseg >= kFusedMinBlocks) {
+    // enough blocks to fill the GPU with one per (batch, head, segment): one pass over q, k, g, v
     FusedParams up;
     if ((rc = act_map(&up.mq, p.q, BT, pb.H)) || (rc = act_map(&up.mk, p.k, BT, pb.H)) ||
         (rc = act_map(&up.mg, p.g, BT, pb.H)) || (rc = act_map(&up.mv, p.v, BT, pb.H)))
@@ -1409,14 +1495,14 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
       if ((rc = state_map(&up.mst, p.saved_out, (size_t)pb.B * NT * pb.H * D))) return rc;
       up.states = reinterpret_cast<__nv_bfloat16*>(p.saved_out);
     }
-    up.s0 = p.h0; up.s_final = p.ht; up.o = reinterpret_cast<__nv_bfloat16*>(p.o);
-    up.T = pb.T; up.H = pb.H; up.NT = NT; up.scale = pb.scale;
+    up.s0 = start; up.s_final = last; up.o = reinterpret_cast<__nv_bfloat16*>(p.o);
+    up.T = pb.T; up.H = pb.H; up.NT = NT / nseg; up.nseg = nseg; up.scale = pb.scale;
     if ((rc = opt_in_smem(k_fwd_fused, FUSED_SMEM))) return rc;
     KernelScope ks("sm100_fwd_fused", st);
-    k_fwd_fused<<<pb.B * pb.H, SCAN_THREADS, FUSED_SMEM, st>>>(up);
+    k_fwd_fused<<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
     return post_launch();
   }
-  rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, h, p.ht, st);
+  rc = run_scan(false, pb, nseg, p.k, p.g, p.v, start, h, last, nullptr, st);
   if (rc) return rc;
   FwdOParams fp;
   if ((rc = act_map(&fp.mq, p.q, BT, pb.H)) || (rc = act_map(&fp.mk, p.k, BT, pb.H)) ||
@@ -1431,7 +1517,7 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
 }
 
 size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p) {
-  return (p.h_saved ? 1 : 2) * state_bytes(p.pb) + 256;
+  return (p.h_saved ? 1 : 2) * state_bytes(p.pb) + segment_floats(p.pb, pick_segments(p.pb)) * sizeof(float) + 256;
 }
 
 bool bwd_dtypes_ok(const tops_chunk_bwd_params& p) {
@@ -1455,17 +1541,32 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.do_) ||
       !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(ws))
     return TOPS_E_ALIGN;
+  // workspace: [dh'] [h' unless the forward kept it] [segment scratch]
+  const int nseg = pick_segments(pb);
   const char* h = reinterpret_cast<const char*>(p.h_saved);
   char* dh = reinterpret_cast<char*>(ws);
+  const SegmentScratch sc(reinterpret_cast<float*>(dh + (h ? 1 : 2) * state_bytes(pb)), pb, nseg);
   int rc = TOPS_OK;
   if (!h) {
-    if (!aligned16(p.h_saved)) return TOPS_E_ALIGN;
-    char* hw = reinterpret_cast<char*>(ws);
-    dh = hw + state_bytes(pb);
-    if ((rc = run_scan(false, pb, p.k, p.g, p.v, p.h0, hw, nullptr, st))) return rc;
+    char* hw = dh + state_bytes(pb);
+    const float* start = p.h0;
+    if (nseg > 1) {
+      if ((rc = segment_starts(false, pb, nseg, p.k, p.g, p.v, p.h0, nullptr, sc, st))) return rc;
+      start = sc.starts;
+    }
+    if ((rc = run_scan(false, pb, nseg, p.k, p.g, p.v, start, hw, nullptr, nullptr, st))) return rc;
     h = hw;
   }
-  if ((rc = run_scan(true, pb, p.q, p.g, p.do_, p.dht, dh, p.dh0, st))) return rc;
+  {
+    const float* start = p.dht;
+    float* last = p.dh0;
+    if (nseg > 1) {
+      if ((rc = segment_starts(true, pb, nseg, p.q, p.g, p.do_, p.dht, p.dh0, sc, st))) return rc;
+      start = sc.starts;
+      last = nullptr;   // the join kernel has written dh0
+    }
+    if ((rc = run_scan(true, pb, nseg, p.q, p.g, p.do_, start, dh, last, nullptr, st))) return rc;
+  }
   BwdParams bp;
   const int BT = pb.B * pb.T, NT = pb.T / C;
   const size_t rows = (size_t)pb.B * NT * pb.H * D;

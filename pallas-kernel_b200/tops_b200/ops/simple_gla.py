@@ -64,30 +64,38 @@ def _expand_gate(g, K):
     return g.unsqueeze(-1).expand(*g.shape, K).contiguous()
 
 
-def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
-                         cu_seqlens=None):
-    """Forward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:53-129`).
-    Returns (o in v.dtype, ht fp32 or None)."""
+def _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, want_saved):
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
     if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
         gate, kind = _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL
-    o, ht, _, _, _ = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
-                                    _cu(cu_seqlens))
+    o, ht, _, _, saved = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
+                                        _cu(cu_seqlens), want_saved=want_saved)
+    return o, ht, (saved if want_saved else None)
+
+
+def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
+                         cu_seqlens=None):
+    """Forward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:53-129`).
+    Returns (o in v.dtype, ht fp32 or None)."""
+    o, ht, _ = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, False)
     return o, ht
 
 
-def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chunk_size=64, cu_seqlens=None):
+def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chunk_size=64, cu_seqlens=None,
+                         h_saved=None):
     """Backward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:668-788`).
     Returns (dq, dk in the input dtype, dv in do.dtype, dg fp32 `[B,T,H]` or
-    None, dh0 fp32 or None)."""
+    None, dh0 fp32 or None).  `h_saved`: the chunk-start states the tcgen05
+    forward kept (None recomputes them, as the reference does)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
     if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
+        # dq, dk leave the kernel in bf16; the per-channel gate gradient stays fp32 for the sum over K
         dq, dk, dv, dgk, dh0 = chunk_bwd_call(q, k, v, _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale,
-                                              initial_state, do, dht, chunk_size, torch.float32, True,
-                                              initial_state is not None)
-        return dq.to(q.dtype), dk.to(k.dtype), dv, dgk.sum(-1), dh0
+                                              initial_state, do, dht, chunk_size, q.dtype, True,
+                                              initial_state is not None, h_saved=h_saved)
+        return dq, dk, dv, dgk.sum(-1), dh0
     return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
                           g is not None, initial_state is not None, _cu(cu_seqlens))
 
@@ -95,16 +103,17 @@ def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chu
 class _ChunkSimpleGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, g_gamma, initial_state, scale, output_final_state, cu, chunk_size):
-        o, ht = chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu)
-        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state)
+        keep = any(t is not None and t.requires_grad for t in (q, k, v, g, initial_state))
+        o, ht, hs = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu, keep)
+        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state, hs)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, g_gamma, h0 = ctx.saved_tensors
+        q, k, v, g, g_gamma, h0, hs = ctx.saved_tensors
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(q, k, v, g, g_gamma, h0, do.to(q.dtype), dht, ctx.scale, ctx.chunk,
-                                                   ctx.cu)
+                                                   ctx.cu, h_saved=hs)
         # a constant decay gets a zero cotangent, as in the reference (tops/ops/simple_gla/chunk.py:764)
         dgamma = None if g_gamma is None else torch.zeros_like(g_gamma)
         return (dq, dk, dv, None if g is None else dg.to(g.dtype), dgamma,
