@@ -1169,24 +1169,28 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
           umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
         umma_commit(&bar_A);
       };
-      // three groups, ordered so that the operands of the next chunk can be fetched early: after the
-      // first group h' and do are dead, after the second dh' and v
-      auto issue_grads = [&](int it) {
-        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+      // The gradient products in two groups.  The first needs neither A nor dA, so it starts as soon as
+      // the chunk's tiles have landed, while the conversion warps still work on A and dA; after it dh'
+      // and v are dead and the next chunk's are fetched.  The second group needs the converted operands.
+      auto issue_inter = [&](int it) {
+        const uint32_t kta = smem_u32(ks + (it & 1) * TILE64);
 #pragma unroll
         for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
           umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
 #pragma unroll
-        for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] = sum_i do[i][v] A[i][j]
-          umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
-        umma_commit(&bar_r1);
-#pragma unroll
         for (int k0 = 0; k0 < D; k0 += 16)   // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
           umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
 #pragma unroll
-        for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] += dh'^T k~^T
-          umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+        for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh'^T k~^T
+          umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
         umma_commit(&bar_r2);
+      };
+      auto issue_intra = [&](int it) {
+        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] += sum_i do[i][v] A[i][j]
+          umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
+        umma_commit(&bar_r1);                // h' and do are dead
 #pragma unroll
         for (int k0 = 0; k0 < C; k0 += 16)   // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
           umma_bf16(tm + cdq, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
@@ -1208,19 +1212,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       }
       if (ok) issue_dA();
       for (int it = 0; ok && it < nit; ++it) {
-        // A and dA of this chunk are in shared memory; the previous chunk has left tensor memory
+        // A and dA of this chunk are issued; the previous chunk has left tensor memory
         TSTART();
-        if (!wait(&conv_done, it & 1, 13)) break;
-        TSTAMP(8);
         if (it >= 1 && !wait(&e_done[(it - 1) & 1], ((it - 1) >> 1) & 1, 14)) break;
         tc_fence_after();
         TSTAMP(9);
+        issue_inter(it);
+        if (!wait(&conv_done, it & 1, 13)) break;   // A and dA of this chunk are in shared memory
+        tc_fence_after();
+        TSTAMP(8);
         const bool more = it + 1 < nit;
-        if (more) {
+        if (more) {   // the next chunk's exponents take the place of A and dA in tensor memory
           if (!wait(&full_g, (it + 1) & 1, 6)) break;
           issue_gate(it + 1);
         }
-        issue_grads(it);
+        issue_intra(it);
         TSTAMP(10);
         if (more) {
           if (!wait(&gated, (it + 1) & 1, 12)) break;
@@ -1278,13 +1284,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         if (ok) load_g(1);
       }
       for (int it = 0; ok && it + 1 < nit; ++it) {
-        // h' and do are dead after the first group of products, dh' and v after the second (and the
-        // h' dh' reduction)
+        // dh' and v are dead after the first group of products (and the h' dh' reduction), h' and do
+        // after the first product of the second group
         TSTART();
-        if (!wait(&bar_r1, it & 1, 8) || !wait(&hdh_done[it & 1], (it >> 1) & 1, 11)) break;
-        load_hdo(it + 1);
-        if (!wait(&bar_r2, it & 1, 8)) break;
+        if (!wait(&bar_r2, it & 1, 8) || !wait(&hdh_done[it & 1], (it >> 1) & 1, 11)) break;
         load_dhv(it + 1);
+        if (!wait(&bar_r1, it & 1, 8)) break;
+        load_hdo(it + 1);
         TSTAMP(13);
         if (it + 2 < nit) {
           if (!wait(&e_done[it & 1], (it >> 1) & 1, 14)) break;
