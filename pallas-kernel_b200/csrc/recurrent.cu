@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(FW_THREADS) k_rec_fwd(tops_recurrent_fwd_param
     for (int c = 0; c < 4; ++c) S[r][c] = 0.f;
     if (a.state_in && k < K) {
       if (vec && col < V) {
-        float4 x = *reinterpret_cast<const float4*>(a.state_in + sbase + (size_t)k * V + col);
+        // the state is touched once per call: streaming loads and stores keep it from displacing the rest of L2
+        float4 x = __ldcs(reinterpret_cast<const float4*>(a.state_in + sbase + (size_t)k * V + col));
         S[r][0] = x.x; S[r][1] = x.y; S[r][2] = x.z; S[r][3] = x.w;
       } else {
 #pragma unroll
@@ -101,8 +102,8 @@ __global__ void __launch_bounds__(FW_THREADS) k_rec_fwd(tops_recurrent_fwd_param
       int k = kr + 16 * r;
       if (k >= K) continue;
       if (vec && col < V) {
-        *reinterpret_cast<float4*>(a.state_out + sbase + (size_t)k * V + col) =
-            make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+        __stcs(reinterpret_cast<float4*>(a.state_out + sbase + (size_t)k * V + col),
+               make_float4(S[r][0], S[r][1], S[r][2], S[r][3]));
       } else {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
