@@ -766,8 +766,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       uint4* dst = reinterpret_cast<uint4*>(p.o + ((size_t)(b * p.T + (c0 + pp) * C + r) * p.H + h) * D + piece * 16);
       const uint4 x = *reinterpret_cast<const uint4*>(rowp + (((2 * piece) ^ r) & 15) * 16);
       const uint4 y = *reinterpret_cast<const uint4*>(rowp + (((2 * piece + 1) ^ r) & 15) * 16);
-      dst[0] = x;
-      dst[1] = y;
+      __stcs(dst, x);
+      __stcs(dst + 1, y);
     };
     bool ok = true;
     for (int pp = 0; ok && pp < NT; ++pp) {
@@ -907,7 +907,7 @@ __device__ __forceinline__ void transpose4(float (&v)[4], int lane) {
 // t0 + (lane & 3) at p[i]; the bf16 form rounds after the first stage and moves packed pairs.
 __device__ __forceinline__ void st_transposed4(float* p, size_t i, float (&v)[4], int lane) {
   transpose4(v, lane);
-  *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+  __stcs(reinterpret_cast<float4*>(p + i), make_float4(v[0], v[1], v[2], v[3]));
 }
 __device__ __forceinline__ void st_transposed4(__nv_bfloat16* p, size_t i, const float (&v)[4], int lane) {
   const bool odd = lane & 1, hi = lane & 2;
@@ -916,10 +916,13 @@ __device__ __forceinline__ void st_transposed4(__nv_bfloat16* p, size_t i, const
   const uint32_t pa = odd ? pack_bf16(r0, v[1]) : pack_bf16(v[0], r0);
   const uint32_t pb = odd ? pack_bf16(r1, v[3]) : pack_bf16(v[2], r1);
   const uint32_t u = __shfl_xor_sync(0xffffffffu, hi ? pa : pb, 2);
-  *reinterpret_cast<uint2*>(p + i) = hi ? make_uint2(u, pb) : make_uint2(pa, u);
+  __stcs(reinterpret_cast<uint2*>(p + i), hi ? make_uint2(u, pb) : make_uint2(pa, u));
 }
-__device__ __forceinline__ void st_out(float* p, size_t i, float x) { p[i] = x; }
-__device__ __forceinline__ void st_out(__nv_bfloat16* p, size_t i, float x) { p[i] = __float2bfloat16_rn(x); }
+// gradients are written once and not read again by these kernels: streaming stores
+__device__ __forceinline__ void st_out(float* p, size_t i, float x) { __stcs(p + i, x); }
+__device__ __forceinline__ void st_out(__nv_bfloat16* p, size_t i, float x) {
+  __stcs(reinterpret_cast<unsigned short*>(p) + i, __bfloat16_as_ushort(__float2bfloat16_rn(x)));
+}
 
 
 // TG: type of dq and dk; TD: type of dg
