@@ -43,6 +43,25 @@ __global__ void __launch_bounds__(FW_THREADS) k_kda_fwd(tops_kda_fwd_params a, f
       S[r][c] = (a.h0 && k < K && col + c < V) ? a.h0[sbase + (size_t)k * V + col + c] : 0.f;
     }
 
+  // The vectors of token t+1 are fetched into registers while token t is processed, so that the
+  // HBM latency of one token hides behind the arithmetic and barriers of the previous one.
+  constexpr int NL = (16 * RK + FW_THREADS - 1) / FW_THREADS;
+  float rq[NL], rk[NL], rg[NL], rv = 0.f, rb = 0.f;
+  auto fetch = [&](int t) {
+    const size_t tok = ((size_t)b * a.T + t) * a.H + h;
+#pragma unroll
+    for (int n = 0; n < NL; ++n) {
+      const int i = tid + n * FW_THREADS;
+      if (i < K) {
+        rq[n] = load_any(a.q, a.dtype, tok * K + i) * a.scale;
+        rk[n] = load_any(a.k, a.dtype, tok * K + i);
+        rg[n] = load_any(a.g, a.gate_dtype, tok * K + i);
+      }
+    }
+    if (tid < FW_BV) rv = (v0 + tid < V) ? load_any(a.v, a.dtype, tok * V + v0 + tid) : 0.f;
+    if (tid == 0) rb = load_any(a.beta, a.dtype, tok);
+  };
+  if (a.T > 0) fetch(0);
   for (int t = 0; t < a.T; ++t) {
     if (seg_states && (t % SEGMENT) == 0) {
       float* dst = seg_states + ((size_t)blockIdx.y * nseg + t / SEGMENT) * K * (size_t)V;
@@ -55,14 +74,19 @@ __global__ void __launch_bounds__(FW_THREADS) k_kda_fwd(tops_kda_fwd_params a, f
         }
     }
     const size_t tok = ((size_t)b * a.T + t) * a.H + h;
-    for (int i = tid; i < K; i += FW_THREADS) {
-      qs[i] = load_any(a.q, a.dtype, tok * K + i) * a.scale;
-      ks[i] = load_any(a.k, a.dtype, tok * K + i);
-      egs[i] = expf(load_any(a.g, a.gate_dtype, tok * K + i));
+#pragma unroll
+    for (int n = 0; n < NL; ++n) {
+      const int i = tid + n * FW_THREADS;
+      if (i < K) {
+        qs[i] = rq[n];
+        ks[i] = rk[n];
+        egs[i] = expf(rg[n]);
+      }
     }
-    if (tid < FW_BV) vs[tid] = (v0 + tid < V) ? load_any(a.v, a.dtype, tok * V + v0 + tid) : 0.f;
-    if (tid == 0) beta_s = load_any(a.beta, a.dtype, tok);
+    if (tid < FW_BV) vs[tid] = rv;
+    if (tid == 0) beta_s = rb;
     __syncthreads();
+    if (t + 1 < a.T) fetch(t + 1);
     // decay, and this thread's share of k^T S'
     float pp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -186,17 +210,31 @@ __global__ void __launch_bounds__(BW_THREADS) k_kda_bwd(tops_kda_bwd_params a, c
           int k = kg + 16 * r, v = vg + 16 * j;
           S[r][j] = (k < K && v < V) ? src[(size_t)k * V + v] : 0.f;
         }
+      // (token t+1 is fetched into registers while token t is processed; DM <= BW_THREADS)
+      float rk = 0.f, rg = 0.f, rv = 0.f, rdo = 0.f, rb = 0.f;
+      auto fetch = [&](int t) {
+        const size_t tok = ((size_t)b * a.T + t) * a.H + h;
+        if (tid < DM) {
+          const bool okk = tid < K, okv = tid < V;
+          rk = okk ? load_any(a.k, a.dtype, tok * K + tid) : 0.f;
+          rg = okk ? load_any(a.g, a.gate_dtype, tok * K + tid) : 0.f;
+          rv = okv ? load_any(a.v, a.dtype, tok * V + tid) : 0.f;
+          rdo = okv ? load_any(a.do_, a.dtype, tok * V + tid) : 0.f;
+        }
+        if (tid == 0) rb = load_any(a.beta, a.dtype, tok);
+      };
+      fetch(t0);
       for (int t = t0; t < t1; ++t) {
         const size_t tok = ((size_t)b * a.T + t) * a.H + h;
-        for (int i = tid; i < DM; i += BW_THREADS) {
-          bool okk = i < K, okv = i < V;
-          ks[i] = okk ? load_any(a.k, a.dtype, tok * K + i) : 0.f;
-          egs[i] = okk ? expf(load_any(a.g, a.gate_dtype, tok * K + i)) : 1.f;
-          vs[i] = okv ? load_any(a.v, a.dtype, tok * V + i) : 0.f;
-          dos[i] = okv ? load_any(a.do_, a.dtype, tok * V + i) : 0.f;
+        if (tid < DM) {
+          ks[tid] = rk;
+          egs[tid] = expf(rg);
+          vs[tid] = rv;
+          dos[tid] = rdo;
         }
-        if (tid == 0) beta_s = load_any(a.beta, a.dtype, tok);
+        if (tid == 0) beta_s = rb;
         __syncthreads();
+        if (t + 1 < t1) fetch(t + 1);
         float* hp_t = hp_blk + (size_t)(t - t0) * K * V;
         float pp[R];
 #pragma unroll
@@ -244,18 +282,32 @@ __global__ void __launch_bounds__(BW_THREADS) k_kda_bwd(tops_kda_bwd_params a, c
       }
     }
     // ---- reverse recurrence over the segment
+    float xq = 0.f, xk = 0.f, xg = 0.f, xdo = 0.f, xe = 0.f, xb = 0.f;
+    auto fetch_rev = [&](int t) {
+      const size_t tok = ((size_t)b * a.T + t) * a.H + h;
+      if (tid < DM) {
+        const bool okk = tid < K, okv = tid < V;
+        xq = okk ? load_any(a.q, a.dtype, tok * K + tid) * a.scale : 0.f;
+        xk = okk ? load_any(a.k, a.dtype, tok * K + tid) : 0.f;
+        xg = okk ? load_any(a.g, a.gate_dtype, tok * K + tid) : 0.f;
+        xdo = okv ? load_any(a.do_, a.dtype, tok * V + tid) : 0.f;
+        xe = okv ? e_blk[(size_t)(t - t0) * V + tid] : 0.f;
+      }
+      if (tid == 0) xb = load_any(a.beta, a.dtype, tok);
+    };
+    fetch_rev(t1 - 1);
     for (int t = t1 - 1; t >= t0; --t) {
       const size_t tok = ((size_t)b * a.T + t) * a.H + h;
-      for (int i = tid; i < DM; i += BW_THREADS) {
-        bool okk = i < K, okv = i < V;
-        qs[i] = okk ? load_any(a.q, a.dtype, tok * K + i) * a.scale : 0.f;
-        ks[i] = okk ? load_any(a.k, a.dtype, tok * K + i) : 0.f;
-        egs[i] = okk ? expf(load_any(a.g, a.gate_dtype, tok * K + i)) : 1.f;
-        dos[i] = okv ? load_any(a.do_, a.dtype, tok * V + i) : 0.f;
-        es[i] = okv ? e_blk[(size_t)(t - t0) * V + i] : 0.f;
+      if (tid < DM) {
+        qs[tid] = xq;
+        ks[tid] = xk;
+        egs[tid] = expf(xg);
+        dos[tid] = xdo;
+        es[tid] = xe;
       }
-      if (tid == 0) beta_s = load_any(a.beta, a.dtype, tok);
+      if (tid == 0) beta_s = xb;
       __syncthreads();
+      if (t > t0) fetch_rev(t - 1);
       const float bt = beta_s;
       const float* hp_t = hp_blk + (size_t)(t - t0) * K * V;
       // dh += (q scale) (x) do ;  k^T dh
