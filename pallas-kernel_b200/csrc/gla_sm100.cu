@@ -17,15 +17,20 @@
 // Kernels
 //   k_scan<false>  h'_c,  h <- h * exp(G_n) + (k exp(G_n - G))^T v       (forward scan)
 //   k_scan<true>   dh'_c, dh <- dh * exp(G_n) + (q scale exp(G))^T do    (reverse scan)
-//   k_fwd_o        A = tril(q~ k~^T) scale;  o = q~ h'_c + A v
+//   k_fwd_o        A = tril(q~ k~^T) scale;  o = q~ h'_c + A v            (chunk-parallel outputs)
+//   k_fwd_fused    the forward scan and the outputs in one pass, state kept on chip
 //   k_bwd_main     dA, dv, dq, dk, dg of one chunk from q, k, v, g, do, h'_c, dh'_c
-// with G the chunk-local cumulative gate and q~ = q exp(G - mid),
+//   k_join_segments  chains the time segments a sequence is cut into when there are few sequences
+// A forward is k_fwd_fused when there are enough (batch, head, segment) blocks to fill the GPU,
+// else k_scan<false> + k_fwd_o; a backward is k_scan<true> + k_bwd_main (and k_scan<false> first
+// when the caller did not keep the forward's states).
+// G is the chunk-local cumulative gate and q~ = q exp(G - mid),
 // k~ = k exp(mid - G), mid = (G_0 + G_n) / 2 per channel.  The cumulative
 // gates themselves are tensor-core products of the gate tile with constant
 // 0 / 1 / +-1/2 patterns, so the exponents arrive in tensor memory in the
 // layout the gating or the write-out needs.
 //
-// Thread layout (scans, k_fwd_o, write-out warps of k_bwd_main): 16 warps.
+// Thread layout (scans, k_fwd_o, k_fwd_fused, write-out warps of k_bwd_main): 16 compute warps.
 // Thread (col, seg) with col = (warp & 3) * 32 + lane and seg = warp >> 2:
 // a warp may only touch the 32 tensor-memory lanes (warp & 3) * 32 .. + 31, so
 // the thread owns accumulator row `col` and splits the accumulator columns
