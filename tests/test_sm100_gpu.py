@@ -17,6 +17,9 @@ SHAPES = [
     (1, 1024, 2, False),
     (3, 192, 16, True),      # 48 (batch, head) pairs: the fused forward
     (4, 128, 13, False),
+    (4, 64, 12, True),       # fused forward, a single chunk
+    (1, 2048, 3, True),      # 3 pairs x 8 time segments of 4 chunks
+    (2, 1536, 37, False),    # 74 pairs: 2 segments, fused forward over segments
 ]
 
 
