@@ -3,12 +3,12 @@
 // (reference: tops/cpu/ops/kda/naive.py:10-118, tops/ops/kda/fused_recurrent.py:19-105) and its
 // explicit backward (tops/cpu/ops/kda/fused_recurrent.py:212-418).
 //
-// Forward: one block per (batch, head, 32-column slice of V), state slice in
-// registers.  Backward: the forward kernel also records the state at every
-// 64-token boundary; one block per (batch, head) then walks the boundaries
-// backwards, replays the 64 tokens of a segment (storing the decayed states
-// h'_t and the prediction errors e_t of that segment in scratch), and runs the
-// reverse recurrence over the segment with the state gradient in registers.
+// Forward and backward run one block per (batch, head, 32-column slice of V) with a warp per 8
+// columns (k_kda_fwd_w, k_kda_bwd_w below).  The backward first re-runs the forward, which then
+// records the state at every 64-token boundary; it walks the boundaries backwards, replays the
+// 64 tokens of a segment (storing the decayed states h'_t of that segment in scratch), and runs
+// the reverse recurrence over the segment with the state gradient in registers.
+// k_kda_fwd<RK> is the older block-wide forward, kept for 128 < K <= 256.
 // These kernels are the correctness path for KDA; the chunked WY / UT-transform
 // formulation on the tensor cores is not built.
 #include "kda.cuh"
