@@ -173,6 +173,24 @@ __device__ __forceinline__ float warp_sum(float x) {
 
 constexpr int W_TT = 16;         // tokens staged in shared memory at a time
 
+// Sums eight per-lane values over the warp with 9 shuffles instead of 40: each exchange halves the
+// number of values a lane is responsible for.  Every lane gets the total of column (lane >> 2) & 7
+// (so lane 4 c holds column c).
+__device__ __forceinline__ float warp_sum8(const float (&v)[W_CW], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float k4[4], k2[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    k4[i] = (b4 ? v[i + 4] : v[i]) + __shfl_xor_sync(0xffffffffu, b4 ? v[i] : v[i + 4], 16);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    k2[i] = (b3 ? k4[i + 2] : k4[i]) + __shfl_xor_sync(0xffffffffu, b3 ? k4[i] : k4[i + 2], 8);
+  float x = (b2 ? k2[1] : k2[0]) + __shfl_xor_sync(0xffffffffu, b2 ? k2[0] : k2[1], 4);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  return x;
+}
+
 // The vectors of W_TT consecutive tokens (time order t0 .. t0 + n - 1) of one (batch, head) as fp32 in
 // shared memory: one exposed HBM latency per tile instead of one per token.
 struct TokenTile {
@@ -253,21 +271,21 @@ __global__ void __launch_bounds__(W_THREADS) k_kda_fwd_w(tops_kda_fwd_params a, 
           pp[c] = fmaf(kk_[j], S[j][c], pp[c]);
         }
       }
-      const float beta = tl.beta[tt];
-      float mine = 0.f;
+      const int myc = (lane >> 2) & 7;   // the column whose sums this lane ends up with
+      const float e_mine = (tl.v[tt][cw + myc] - warp_sum8(pp, lane)) * tl.beta[tt];
+      float acc[W_CW];
 #pragma unroll
       for (int c = 0; c < W_CW; ++c) {
-        const float e = (tl.v[tt][cw + c] - warp_sum(pp[c])) * beta;
-        float acc = 0.f;
+        const float e = __shfl_sync(0xffffffffu, e_mine, 4 * c);
+        acc[c] = 0.f;
 #pragma unroll
         for (int j = 0; j < W_RJ; ++j) {
           S[j][c] = fmaf(kk_[j], e, S[j][c]);
-          acc = fmaf(kq[j], S[j][c], acc);
+          acc[c] = fmaf(kq[j], S[j][c], acc[c]);
         }
-        acc = warp_sum(acc);
-        mine = lane == c ? acc : mine;
       }
-      if (lane < W_CW && c0 + lane < V) store_any(a.o, a.dtype, tok * V + c0 + lane, mine);
+      const float o_mine = warp_sum8(acc, lane);
+      if ((lane & 3) == 0 && c0 + myc < V) store_any(a.o, a.dtype, tok * V + c0 + myc, o_mine);
     }
   }
   if (a.ht) store_state(a.ht + sbase);
@@ -354,19 +372,18 @@ __global__ void __launch_bounds__(W_THREADS) k_kda_bwd_w(tops_kda_bwd_params a, 
           }
           const float beta = tl.beta[tt];
           float dqv[W_RJ] = {0.f, 0.f, 0.f, 0.f};
-          float mine = 0.f;
+          const int myc = (lane >> 2) & 7;   // the column whose sums this lane ends up with
+          const float e_mine = tl.v[tt][cw + myc] - warp_sum8(pp, lane);
 #pragma unroll
           for (int c = 0; c < W_CW; ++c) {
-            const float e = tl.v[tt][cw + c] - warp_sum(pp[c]);
-            mine = lane == c ? e : mine;
-            const float be = beta * e, dc = tl.d[tt][cw + c];
+            const float be = beta * __shfl_sync(0xffffffffu, e_mine, 4 * c), dc = tl.d[tt][cw + c];
 #pragma unroll
             for (int j = 0; j < W_RJ; ++j) {
               S[j][c] = fmaf(kk_[j], be, S[j][c]);
               dqv[j] = fmaf(S[j][c], dc, dqv[j]);
             }
           }
-          if (lane < W_CW) es[t - s0][cw + lane] = mine;
+          if ((lane & 3) == 0) es[t - s0][cw + myc] = e_mine;
           // this block's share of dq_t = scale sum_v h_t[k, v] do_t[v]
           const int par = step & 1;
 #pragma unroll
@@ -409,23 +426,27 @@ __global__ void __launch_bounds__(W_THREADS) k_kda_bwd_w(tops_kda_bwd_params a, 
         }
         const float beta = tl.beta[tt];
         // dh += (q scale) (x) do ;  k^T dh ;  de = beta k^T dh
-        float de[W_CW], ec[W_CW], mine = 0.f, dbeta = 0.f;
+        float de[W_CW], ec[W_CW], pk[W_CW], dbeta = 0.f;
 #pragma unroll
         for (int c = 0; c < W_CW; ++c) {
           const float dc = tl.d[tt][cw + c];
           ec[c] = es[t - s0][cw + c];
-          float pk = 0.f;
+          pk[c] = 0.f;
 #pragma unroll
           for (int j = 0; j < W_RJ; ++j) {
             dh[j][c] = fmaf(kq[j], dc, dh[j][c]);
-            pk = fmaf(dh[j][c], kk_[j], pk);
+            pk[c] = fmaf(dh[j][c], kk_[j], pk[c]);
           }
-          pk = warp_sum(pk);
-          de[c] = beta * pk;
-          mine = lane == c ? de[c] : mine;
-          dbeta = fmaf(pk, ec[c], dbeta);   // columns beyond V have e = 0
         }
-        if (lane < W_CW && c0 + lane < V) store_any(a.dv, a.dtype, tok * V + c0 + lane, mine);
+        const int myc = (lane >> 2) & 7;   // the column whose sums this lane ends up with
+        const float pk_mine = warp_sum8(pk, lane);
+#pragma unroll
+        for (int c = 0; c < W_CW; ++c) {
+          const float s = __shfl_sync(0xffffffffu, pk_mine, 4 * c);
+          de[c] = beta * s;
+          dbeta = fmaf(s, ec[c], dbeta);   // columns beyond V have e = 0
+        }
+        if ((lane & 3) == 0 && c0 + myc < V) store_any(a.dv, a.dtype, tok * V + c0 + myc, beta * pk_mine);
         // dk, dg, and the step back through the delta update and the decay
         const int par = step & 1;
 #pragma unroll
