@@ -465,7 +465,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   const int q4 = warp & 3, seg = warp >> 2;
   // heads vary fastest over the blocks in flight: together they read whole token rows of the
   // [B,T,H,D] activations (all heads of a time step are contiguous in memory)
-  const int h = blockIdx.x, ci = blockIdx.y, b = blockIdx.z, bh = b * p.H + h;
+  const int h = blockIdx.x, ci = blockIdx.y, b = blockIdx.z;
   const int row = b * p.T + ci * C;
   constexpr uint32_t cO = 0, cE = 0, cA = 128;   // E is consumed before O is produced
 

@@ -179,9 +179,6 @@ extern "C" int tops_b200_profile_read(char* buf, size_t cap) {
 
 extern "C" int tops_b200_chunk_local_cumsum(const tops_cumsum_params* p, void* stream) {
   if (!p || !p->g || !p->out) return TOPS_E_NULL;
-  tops_chunk_problem in{};
-  in.B = p->B; in.T = p->T; in.H = p->H; in.K = p->D; in.V = 1; in.chunk = p->chunk;
-  in.dtype = p->dtype; in.gate_dtype = p->dtype; in.gate_kind = TOPS_GATE_NONE;
   if (p->B < 1 || p->T < 1 || p->H < 1 || p->D < 1) return TOPS_E_BAD_SHAPE;
   if (p->chunk < 1 || (p->chunk & (p->chunk - 1))) return TOPS_E_BAD_SHAPE;
   if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
