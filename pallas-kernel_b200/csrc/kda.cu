@@ -536,7 +536,7 @@ size_t bwd_workspace_bytes(const tops_kda_bwd_params& p) {
 int bwd(const tops_kda_bwd_params& p, void* workspace, cudaStream_t st) {
   if (p.K > 128 || p.V > 128) return TOPS_E_BAD_SHAPE;
   const int ns = n_slices(p);
-  const size_t ntk = (size_t)p.B * p.T * p.H * p.K, nt = (size_t)p.B * p.T * p.H;
+  const size_t ntk = (size_t)p.B * p.T * p.H * p.K;
   char* w = reinterpret_cast<char*>(workspace);
   float* seg = reinterpret_cast<float*>(w); w += align_up(seg_elems(p) * 4);
   float* hp = reinterpret_cast<float*>(w); w += align_up(hp_elems(p) * 4);
