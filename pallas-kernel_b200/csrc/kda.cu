@@ -155,8 +155,8 @@ __global__ void __launch_bounds__(FW_THREADS) k_kda_fwd(tops_kda_fwd_params a, f
 // the value columns is a sum inside a thread.  The recurrences of different
 // columns are independent, so the warps of a block never wait for each other
 // in the forward pass; in the backward pass they meet once per token and loop
-// to add up their shares of dq, dk, dg and dbeta.  The vectors of the next
-// token are fetched into registers while the current one is processed.
+// to add up their shares of dq, dk, dg and dbeta.  The vectors of 16 tokens at a
+// time are staged in shared memory as fp32.
 // ---------------------------------------------------------------------------
 constexpr int W_THREADS = 128;   // 4 warps = 32 value columns per block
 constexpr int W_CW = 8;          // columns per warp
