@@ -162,15 +162,6 @@ constexpr int W_THREADS = 128;   // 4 warps = 32 value columns per block
 constexpr int W_CW = 8;          // columns per warp
 constexpr int W_RJ = 4;          // rows per lane
 
-__device__ __forceinline__ float warp_sum(float x) {
-  x += __shfl_xor_sync(0xffffffffu, x, 16);
-  x += __shfl_xor_sync(0xffffffffu, x, 8);
-  x += __shfl_xor_sync(0xffffffffu, x, 4);
-  x += __shfl_xor_sync(0xffffffffu, x, 2);
-  x += __shfl_xor_sync(0xffffffffu, x, 1);
-  return x;
-}
-
 constexpr int W_TT = 16;         // tokens staged in shared memory at a time
 
 // Sums eight per-lane values over the warp with 9 shuffles instead of 40: each exchange halves the
