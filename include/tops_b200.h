@@ -64,6 +64,13 @@ int64_t tops_b200_launch_count(void);
  * `*out` (0 = no wait has ever given up).  It synchronises with the device.
  * No counterpart in the reference. */
 int tops_b200_device_error(int* out);
+/* The word is sticky: it keeps the first code until it is cleared.  A kernel that gives up also
+ * writes NaN into the first element of an output it owns (o, ht, dq, a chunk state), so that a
+ * caller who never reads the word still sees a poisoned result instead of stale memory.
+ * `_reset` clears the word; `_set` overwrites it from the host (host-side fault injection for
+ * tests of the error reporting path; no kernel is involved).  Both synchronise with the device. */
+int tops_b200_device_error_reset(void);
+int tops_b200_device_error_set(int code);
 
 /* Per-kernel device timing (no counterpart behind the reference's op API; its
  * benchmarks wrap timed loops in jax.profiler traces, `benchmarks/utils.py:71-83`).
@@ -79,7 +86,9 @@ int tops_b200_profile_read(char* buf, size_t cap);
  * (accelerator: `tops/ops/common/cumsum.py:472-540`).
  * Inclusive (or, reversed, suffix) sum of `g` inside each chunk along T.
  * `D` is K for per-channel gates, 1 for scalar gates.  Output is fp32.
- * cu_seqlens (device int32 [N+1], B must be 1) restarts chunks per sequence.
+ * Dense batches only: with `cu_seqlens` set this stand-alone call returns
+ * TOPS_E_UNSUPPORTED (packed batches restart chunks per sequence inside the
+ * fused chunk entry points, which carry the chunk tables in their workspace).
  * ------------------------------------------------------------------------ */
 typedef struct {
   int32_t B, T, H, D, chunk;
@@ -87,8 +96,8 @@ typedef struct {
   int32_t reverse; /* 0 prefix sums, 1 suffix sums */
   const void* g;
   float* out;
-  const int32_t* cu_seqlens; /* NULL: dense batch */
-  int32_t N;                 /* number of sequences when cu_seqlens != NULL */
+  const int32_t* cu_seqlens; /* must be NULL (see above) */
+  int32_t N;                 /* unused */
 } tops_cumsum_params;
 int tops_b200_chunk_local_cumsum(const tops_cumsum_params* p, void* stream);
 
@@ -306,6 +315,38 @@ typedef struct {
   float* ht;       /* [B,H,K,V] or NULL */
 } tops_kda_fwd_params;
 int tops_b200_kda_fwd(const tops_kda_fwd_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_kda_fwd — replaces `chunk_kda_fwd` (`tops/ops/kda/chunk.py:25-190`): the
+ * chunked WY / UT-transform forward built from the intra-chunk kernel
+ * (`tops/ops/kda/chunk_intra.py:91-165`, blocked unit-lower solve `:28-88`), the
+ * delta-rule state scan (`tops/ops/common/chunk_delta_h.py:569-736`) and the
+ * output kernel (`tops/ops/gla/chunk.py:1279-1440`), here one pass per (batch,
+ * head) on the tensor cores.  bf16 q, k, v, g (natural-log gate), beta `[B,T,H]`;
+ * K = V = 128, chunk = 64, T % 64 == 0 (`tops_b200_chunk_kda_supported` says
+ * whether a problem qualifies; other problems go to `tops_b200_kda_fwd`).
+ * Optional outputs (NULL to skip):
+ *   Aqk_out, Akk_out  fp32 `[B,T,H,64]`: row i of its chunk at token i —
+ *                     tril(scale q k^T exp(G_i - G_j)) and (I + stril(beta k k^T exp(G_i - G_j)))^-1,
+ *                     the matrices `chunk_kda_fwd` returns;
+ *   saved_h     bf16 `[B,NT,H,K,V]`  chunk-start states times exp(mid) per key channel,
+ *   saved_vnew  bf16 `[B,T,H,V]`     the delta-corrected values v' = u - w h,
+ *   saved_T     bf16 `[B,T,H,64]`    the inverse above in bf16:
+ *               residuals `tops_b200_chunk_kda_bwd` takes back (opaque to callers).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V, chunk;
+  int32_t dtype, gate_dtype;
+  float scale;
+  const void *q, *k, *v, *g, *beta;
+  const float* h0; /* [B,H,K,V] or NULL */
+  void* o;         /* [B,T,H,V] */
+  float* ht;       /* [B,H,K,V] or NULL */
+  float *Aqk_out, *Akk_out;
+  void *saved_h, *saved_vnew, *saved_T;
+} tops_chunk_kda_fwd_params;
+int tops_b200_chunk_kda_supported(const tops_chunk_kda_fwd_params* p);
+int tops_b200_chunk_kda_fwd(const tops_chunk_kda_fwd_params* p, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * KDA backward — replaces `chunk_kda_bwd` (`tops/cpu/ops/kda/chunk_bwd.py:525-668`)

@@ -38,58 +38,14 @@
 #include <mutex>
 
 #include "gla_sm100.cuh"
-#include "sm100_prims.cuh"
+#include "sm100_host.cuh"
+#include "sm100_tiles.cuh"
 
 namespace tops {
 namespace sm100 {
 
-__device__ int g_error;  // first bounded wait that gave up (0 = none)
-#ifdef TOPS_TIMING
-__device__ long long g_timing[16];
-#define TDECL() long long _acc[16] = {0}; long long _t = 0
-#define TSTAMP(i) do { long long _n = clock64(); _acc[i] += _n - _t; _t = _n; } while (0)
-#define TSTART() _t = clock64()
-#define TFLUSH() do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0) { for (int _i = 0; _i < 16; ++_i) g_timing[_i] += _acc[_i]; } } while (0)
-#define TFLUSH_IF(c) do { if ((c) && blockIdx.x == 0) { for (int _i = 0; _i < 16; ++_i) g_timing[_i] += _acc[_i]; } } while (0)
-#else
-#define TFLUSH_IF(c)
-#define TDECL()
-#define TSTAMP(i)
-#define TSTART()
-#define TFLUSH()
-#endif
 
 namespace {
-
-constexpr int C = 64;    // chunk
-constexpr int D = 128;   // K = V
-constexpr int NTHREADS = 512;
-constexpr int SEG = 16;  // time steps per thread
-constexpr uint32_t SLAB64 = 64 * 128;        // bytes of a 64-row slab
-constexpr uint32_t TILE64 = 2 * SLAB64;      // 64 x 128 bf16 tile
-constexpr uint32_t TILE128 = 2 * 128 * 128;  // 128 x 128 bf16 tile
-
-__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
-  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
-}
-__device__ __forceinline__ float ld_bf16(const uint8_t* tile, uint32_t off) {
-  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + off));
-}
-// offset of (row i, this thread's column) in a 64-row tile
-struct ColAddr {
-  uint32_t base, cchunk;
-  __device__ __forceinline__ uint32_t at(int i) const {
-    return base + (uint32_t)i * 128u + (((cchunk ^ (uint32_t)i) & 7u) << 4);
-  }
-};
-__device__ __forceinline__ ColAddr col_prep(int rows, int col) {
-  return ColAddr{(uint32_t)((col >> 6) * rows * 128 + (col & 7) * 2), (uint32_t)((col & 63) >> 3)};
-}
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&t);
-}
-__device__ __forceinline__ void fail(int code) { atomicCAS(&g_error, 0, code); }
 
 // ===========================================================================
 // State scans
@@ -105,43 +61,6 @@ struct ScanParams {
   int nseg;                // time segments per sequence, one block each
   float scale;
 };
-
-// Constant 64 x 64 patterns, stored as K-major bf16 tiles, that turn the gate
-// tile g [time j][channel] into exponents with one tensor-core product:
-//   TRI_INCL  L[i][j] = (j <= i)                 -> G_i           (inclusive cumulative gate)
-//   TRI_REV   U[i][j] = (j > i)                  -> G_n - G_i
-//   TRI_REVN  TRI_REV with row 63 all ones       -> G_n - G_i for i < 63 and G_n itself in row 63 (whose own
-//             exponent, 0, needs no product)
-//   TRI_MID   L - 1/2 [j == 0] - 1/2             -> G_i - (G_0 + G_n) / 2
-// All entries (0, 1, +-1/2) are exact in bf16 and the products accumulate in fp32.
-enum { TRI_INCL = 0, TRI_REV = 1, TRI_MID = 2, TRI_REVN = 3 };
-__device__ __forceinline__ float tri_value(int kind, int i, int j) {
-  if (kind == TRI_INCL) return j <= i ? 1.f : 0.f;
-  if (kind == TRI_REV) return j > i ? 1.f : 0.f;
-  if (kind == TRI_REVN) return (i == 63 || j > i) ? 1.f : 0.f;
-  return j == 0 ? 0.f : (j <= i ? 0.5f : -0.5f);
-}
-__device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind) {
-  for (int idx = threadIdx.x; idx < rows * 8; idx += blockDim.x) {
-    const int r = idx >> 3, c8 = (idx & 7) * 8, i = r & 63;
-    uint32_t w[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) w[t] = pack_bf16(tri_value(kind, i, c8 + 2 * t), tri_value(kind, i, c8 + 2 * t + 1));
-    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
-// multiply 8 packed bf16 by 8 fp32 factors
-__device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
-  __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);
-  uint4 y;
-  uint32_t* py = reinterpret_cast<uint32_t*>(&y);
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const float2 v = __bfloat1622float2(px[t]);
-    py[t] = pack_bf16(v.x * f[2 * t], v.y * f[2 * t + 1]);
-  }
-  return y;
-}
 
 // One block per (batch, head): 16 compute warps and one driver warp.  The whole K x V state lives in
 // registers of the compute warps (thread (q4, lane, seg): row k = 32 q4 + lane, columns 32 seg .. + 31).
@@ -222,7 +141,6 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
   tc_fence_after();
   const uint32_t tm = sh.tmem_slot;
   const uint32_t lane_base = q4 * 32;
-  TDECL();
 
   // exponents E = pattern . g of chunk pp: [time (repeated to 128 lanes)][channel]; row 63 is G_n
   auto issue_gate_mma = [&](int pp) {
@@ -251,12 +169,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       fail(1);
     }
     tc_fence_after();
-    TSTAMP(7);
     const int i = (q4 * 32 + lane) & 63;          // time row of this thread
     const int cg = (q4 >> 1) * 4 + seg;           // its 16 channels
     float e[16];
     tmem_ld16(tmem_addr(tm, lane_base, cE + (pp & 1) * 128 + cg * 16), e);
-    TSTAMP(8);
     if (i == 63) {
 #pragma unroll
       for (int t = 0; t < 16; ++t) sh.gn[pp & 1][cg * 16 + t] = e[t];
@@ -278,10 +194,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
       *reinterpret_cast<uint4*>(xt + off) = scale8(*reinterpret_cast<const uint4*>(xt + off), e + 8 * u);
     }
-    TSTAMP(9);
     fence_async_smem();
     tc_fence_before();
-    TSTAMP(10);
   };
   // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2;
   // reverse states as dh * exp(G_n - mid) = dh * exp((G_n - G_0) / 2)
@@ -296,8 +210,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       issue_gate_mma(0);
       if (NT > 1) issue_gate_mma(1);
     }
-    __syncthreads();   // chunk 0 is gated
-    bool ok = !*abort_flag;
+    bool ok = !__syncthreads_or(*abort_flag);   // chunk 0 is gated
     if (ok && lane == 0) {
       issue_state_mma(0);
       if (NT > 2) issue_gate_mma(2);
@@ -307,8 +220,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       // the store of chunk pp-1 has read its staging tile: after the barrier the compute warps may
       // overwrite it (with the state of chunk pp+1)
       if (lane == 0) tma_store_wait_read();
-      __syncthreads();           // h'_pp is staged, chunk pp+1 is gated
-      if (*abort_flag) break;
+      // h'_pp is staged, chunk pp+1 is gated; every thread of the block sees the same verdict, so
+      // all of them leave the loop at the same barrier
+      if (__syncthreads_or(*abort_flag)) break;
       if (lane == 0) {
         if (pp + 1 < NT) issue_state_mma(pp + 1);
         if (keep_states) {
@@ -340,17 +254,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       }
     }
     float gtot = 0.f;   // summed log-gates of this thread's channel over the block's chunks
-    TSTART();
     gate_chunk(0);
-    __syncthreads();
-    bool ok = !*abort_flag;
+    bool ok = !__syncthreads_or(*abort_flag);
     float decay = 1.f, hscale = 1.f;
     if (ok) {
       decay = fast_exp(sh.gn[0][col]);
       hscale = state_scale(0);
     }
     for (int pp = 0; ok && pp < NT; ++pp) {
-      TSTART();
       // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
       // memory in the tile format of the states tensor map and written out by a TMA store
       gtot += sh.gn[pp & 1][col];   // (published by the gating of this chunk, one iteration ago)
@@ -363,21 +274,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
                          pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
         fence_async_smem();
       }
-      TSTAMP(0);
       if (pp + 1 < NT) gate_chunk(pp + 1);
-      TSTAMP(1);
-      __syncthreads();
-      TSTAMP(2);
-      if (*abort_flag) { ok = false; break; }
+      if (__syncthreads_or(*abort_flag)) { ok = false; break; }
       float decay_n = 1.f, hscale_n = 1.f;
       if (pp + 1 < NT) {
         decay_n = fast_exp(sh.gn[(pp + 1) & 1][col]);
         hscale_n = state_scale(pp + 1);
       }
-      TSTAMP(3);
       if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
       tc_fence_after();
-      TSTAMP(4);
       {
         float d[32];
         tmem_ld32(tmem_addr(tm, lane_base, cS + (pp & 1) * 128 + seg * 32), d);
@@ -385,11 +290,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
         for (int t = 0; t < 32; ++t) S[t] = fmaf(S[t], decay, d[t]);
       }
       tc_fence_before();
-      TSTAMP(5);
       decay = decay_n;
       hscale = hscale_n;
     }
-    if (!BWD) { TFLUSH(); }
     if (ok && p.s_final) {
       float* dst = p.s_final + ((size_t)blk * D + col) * D + seg * 32;
 #pragma unroll
@@ -400,6 +303,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+  if (tid == 0 && sh.abort_flag) {
+    if (p.states) poison(p.states + ((size_t)(b * (p.T / C) + chunk_of(0)) * p.H + h) * D * D);
+    if (p.s_final) poison(p.s_final + (size_t)blk * D * D);
+    if (p.gsum) poison(p.gsum + (size_t)blk * D);
+  }
 }
 
 // Joins the time segments of each (batch, head).  A segment acts on the state entering it as
@@ -422,21 +330,6 @@ __global__ void k_join_segments(const float* first, const float* P, const float*
       cur = make_float4(fmaf(cur.x, w, add.x), fmaf(cur.y, w, add.y), fmaf(cur.z, w, add.z), fmaf(cur.w, w, add.w));
     }
     if (last) *reinterpret_cast<float4*>(last + (size_t)bh * D * D + e) = cur;
-  }
-}
-
-// masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
-// 64 x 64 fp32 accumulator into a K-major 64 x 64 tile
-__device__ __forceinline__ void store_tril16(uint8_t* dst, int i, int j0, const float (&a)[16], float scale) {
-#pragma unroll
-  for (int c8 = 0; c8 < 16; c8 += 8) {
-    uint32_t w[4];
-#pragma unroll
-    for (int t = 0; t < 8; t += 2) {
-      const int j = j0 + c8 + t;
-      w[t >> 1] = pack_bf16(j <= i ? a[c8 + t] * scale : 0.f, j + 1 <= i ? a[c8 + t + 1] * scale : 0.f);
-    }
-    *reinterpret_cast<uint4*>(dst + slab_off(i, j0 + c8)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -580,6 +473,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 256);
+  if (tid == 0 && !ok) poison(p.o + ((size_t)row * p.H + h) * D);
 }
 
 // ===========================================================================
@@ -614,22 +508,6 @@ struct FusedShared {
 };
 constexpr uint32_t FUSED_STAGE = 4 * TILE64;   // q, k, g, v
 constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 + TILE64 + sizeof(FusedShared);
-
-// 16 x 64 K-major pattern: row 0 sums the gates (G_n), row 1 gives G_n - mid = (G_n - G_0) / 2
-__device__ __forceinline__ void build_w_tile(uint8_t* tile) {
-  for (int idx = threadIdx.x; idx < 16 * 8; idx += blockDim.x) {
-    const int r = idx >> 3, c8 = (idx & 7) * 8;
-    uint32_t w[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int j = c8 + 2 * t;
-      const float a = r == 0 ? 1.f : (r == 1 ? (j == 0 ? 0.f : 0.5f) : 0.f);
-      const float b = r == 0 ? 1.f : (r == 1 ? 0.5f : 0.f);
-      w[t] = pack_bf16(a, b);
-    }
-    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
 
 __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constant__ FusedParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -706,8 +584,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       // the state store of chunk pp-1 has read its staging tile, which the compute warps refill after
       // the next barrier (with the state of chunk pp+1)
       if (lane == 0) tma_store_wait_read();
-      __syncthreads();   // B1: q~, k~ and h' of chunk pp are in shared memory, E and W have been read
-      if (*abort_flag) break;
+      // B1: q~, k~ and h' of chunk pp are in shared memory, E and W have been read
+      if (__syncthreads_or(*abort_flag)) break;
       if (lane == 0) {
         tc_fence_after();
         const uint32_t qa = smem_u32(qs), ka = smem_u32(ks), va = smem_u32(vs), ha = smem_u32(ht);
@@ -729,8 +607,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
           tma_store_commit();
         }
       }
-      __syncthreads();   // B2: tril(A) scale is in shared memory (in the gate tile of this stage)
-      if (*abort_flag) break;
+      // B2: tril(A) scale is in shared memory (in the gate tile of this stage)
+      if (__syncthreads_or(*abort_flag)) break;
       if (lane == 0) {
         tc_fence_after();
         const uint32_t pa = smem_u32(gs), va = smem_u32(vs);
@@ -818,8 +696,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       }
       fence_async_smem();
       tc_fence_before();
-      __syncthreads();   // B1
-      if (*abort_flag) { ok = false; break; }
+      if (__syncthreads_or(*abort_flag)) { ok = false; break; }   // B1
       if (pp > 0) copy_out(pp - 1);   // staged before the barrier; the products of this chunk run meanwhile
       // tril(A) scale -> bf16 operand in the (dead) gate tile
       if (!mbar_wait(&sh.abar, ph)) { *abort_flag = 1; fail(4); }
@@ -832,8 +709,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       }
       fence_async_smem();
       tc_fence_before();
-      __syncthreads();   // B2
-      if (*abort_flag) { ok = false; break; }
+      if (__syncthreads_or(*abort_flag)) { ok = false; break; }   // B2
       // state update while the last output product runs
       if (!mbar_wait(&sh.sbar, ph)) { *abort_flag = 1; fail(2); }
       tc_fence_after();
@@ -870,6 +746,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+  if (tid == 0 && sh.abort_flag) {
+    poison(p.o + ((size_t)(b * p.T + c0 * C) * p.H + h) * D);
+    if (p.s_final) poison(p.s_final + (size_t)blk * D * D);
+  }
 }
 
 // ===========================================================================
@@ -996,7 +876,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tm = tmem_slot;
-  TDECL();
 
   if (warp < 16) {
     // ------------------------------------------------------------------ gradient write-out
@@ -1040,14 +919,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       const int sl = it & 1;
       int h, row, hrow;
       chunk_rows(it, h, row, hrow);
-      TSTART();
-      TSTAMP(3);
       // the next chunk's gating runs while the tensor core works on this chunk's gradient products
       if (it + 1 < nit && !gate_chunk(it + 1)) break;
-      TSTAMP(4);
       if (!wait(&bar_main, it & 1, 8) || !wait(&hdh_done[sl], (it >> 1) & 1, 11)) break;
       tc_fence_after();
-      TSTAMP(0);
       const uint8_t* qt = qs + sl * TILE64;
       const uint8_t* kt = ks + sl * TILE64;
       const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
@@ -1082,7 +957,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       }
       sufsum[sl][seg][col] = run;
       tails[sl][seg][col] = tail;
-      TSTAMP(1);
       tc_fence_before();
       asm volatile("bar.sync 1, %0;" ::"n"(BWD_EPI_THREADS) : "memory");
       const float later = (seg < 1 ? sufsum[sl][1][col] : 0.f) + (seg < 2 ? sufsum[sl][2][col] : 0.f) +
@@ -1100,19 +974,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
           st_transposed4(dg_out, obase4 + t * ostride, w, lane);
         }
       }
-      TSTAMP(2);
     }
-    TFLUSH_IF(tid == 0);
   } else if (warp < 20) {
     // ------------------------------------------------------------------ A / dA -> masked bf16 operands
     const int g4 = warp & 3;
     const uint32_t lane_base = g4 * 32;
     for (int it = 0; it < nit; ++it) {
-      TSTART();
       // rows of the M = 64 accumulators sit in lanes 0..15 of each quarter
       if (!wait(&bar_A, it & 1, 7)) break;
       tc_fence_after();
-      TSTAMP(5);
       const int ri = 16 * g4 + lane;
 #pragma unroll
       for (int sg = 0; sg < 4; ++sg) {
@@ -1125,7 +995,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&conv_done);
-      TSTAMP(6);
       // sum_v h'[k][v] dh'[k][v] for k = this thread, while the gradient products read the same tiles
       if (!wait(&full_hdo, it & 1, 6) || !wait(&full_dhv, it & 1, 6)) break;
       {
@@ -1147,9 +1016,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         hdh_s[it & 1][gt] = hd;
       }
       mbar_arrive(&hdh_done[it & 1]);   // h' and dh' of this chunk are no longer read by threads
-      TSTAMP(7);
     }
-    TFLUSH_IF(tid == 512);
   } else if (warp == 20) {
     // ------------------------------------------------------------------ tensor-core issue
     if (lane == 0) {
@@ -1221,32 +1088,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       if (ok) issue_dA();
       for (int it = 0; ok && it < nit; ++it) {
         // A and dA of this chunk are issued; the previous chunk has left tensor memory
-        TSTART();
         if (it >= 1 && !wait(&e_done[(it - 1) & 1], ((it - 1) >> 1) & 1, 14)) break;
         tc_fence_after();
-        TSTAMP(9);
         issue_inter(it);
         if (!wait(&conv_done, it & 1, 13)) break;   // A and dA of this chunk are in shared memory
         tc_fence_after();
-        TSTAMP(8);
         const bool more = it + 1 < nit;
         if (more) {   // the next chunk's exponents take the place of A and dA in tensor memory
           if (!wait(&full_g, (it + 1) & 1, 6)) break;
           issue_gate(it + 1);
         }
         issue_intra(it);
-        TSTAMP(10);
         if (more) {
           if (!wait(&gated, (it + 1) & 1, 12)) break;
           tc_fence_after();
           issue_A(it + 1);
-          TSTAMP(11);
           if (!wait(&full_hdo, (it + 1) & 1, 6) || !wait(&full_dhv, (it + 1) & 1, 6)) break;
           issue_dA();
-          TSTAMP(12);
         }
       }
-      TFLUSH_IF(true);
     }
   } else {
     // ------------------------------------------------------------------ TMA loads
@@ -1294,107 +1154,37 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       for (int it = 0; ok && it + 1 < nit; ++it) {
         // dh' and v are dead after the first group of products (and the h' dh' reduction), h' and do
         // after the first product of the second group
-        TSTART();
         if (!wait(&bar_r2, it & 1, 8) || !wait(&hdh_done[it & 1], (it >> 1) & 1, 11)) break;
         load_dhv(it + 1);
         if (!wait(&bar_r1, it & 1, 8)) break;
         load_hdo(it + 1);
-        TSTAMP(13);
         if (it + 2 < nit) {
           if (!wait(&e_done[it & 1], (it >> 1) & 1, 14)) break;
           load_qk(it + 2);
-          TSTAMP(14);
           if (!wait(&bar_gate, (it + 1) & 1, 9)) break;
           load_g(it + 2);
-          TSTAMP(15);
         }
       }
-      TFLUSH_IF(true);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
+  if (tid == 0 && abort_flag && nit > 0) {
+    int h, row, hrow;
+    chunk_rows(0, h, row, hrow);
+    poison(reinterpret_cast<TG*>(p.dq) + ((size_t)row * p.H + h) * D);
+    poison(p.dv + ((size_t)row * p.H + h) * D);
+  }
 }
 
 // ===========================================================================
 // host side
 // ===========================================================================
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(p);
-  });
-  return fn;
-}
-
-// [B*T, H, 128] bf16 activations: box = 64 channels x 1 head x 64 tokens
-int act_map(CUtensorMap* m, const void* ptr, int BT, int H) {
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)BT};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2};
-  cuuint32_t box[3] = {64, 1, 64};
-  cuuint32_t es[3] = {1, 1, 1};
-  CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? TOPS_OK : TOPS_E_CUDA;
-}
-// [rows, 128] bf16 chunk states: box = 64 columns x 128 rows
-int state_map(CUtensorMap* m, const void* ptr, size_t rows) {
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-  cuuint32_t box[2] = {64, 128};
-  cuuint32_t es[2] = {1, 1};
-  CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? TOPS_OK : TOPS_E_CUDA;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      n = 148;
-  }
-  return n;
-}
-
-bool device_is_sm100() {
-  static int cached = -1;
-  if (cached < 0) {
-    int dev = 0, major = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
-      cudaGetLastError();
-      return false;
-    }
-    cached = (major == 10) ? 1 : 0;
-  }
-  return cached == 1;
-}
-
 constexpr size_t SCAN_SMEM = 9 * TILE64 + 2 * SLAB64 + 2 * TILE128 + sizeof(ScanShared);
 constexpr size_t FWD_O_SMEM = 4 * TILE64 + TILE128 + SLAB64 + 1024;
 constexpr size_t BWD_SMEM = 7 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
 
-template <class F>
-int opt_in_smem(F f, size_t bytes) {
-  return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess ? TOPS_OK
-                                                                                                         : TOPS_E_CUDA;
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 // from this many (batch, head) pairs on, the forward runs as one fused pass (one block per pair)
 // instead of a state scan followed by a chunk-parallel output kernel
 constexpr int kFusedMinBlocks = 48;
@@ -1474,22 +1264,30 @@ static size_t state_bytes(const tops_chunk_problem& pb) {
   return align_up((size_t)pb.B * (pb.T / C) * pb.H * D * D * 2);
 }
 
+// The fused one-pass forward keeps the chunk-start states on chip: only the two-kernel form (too few
+// blocks for one per (batch, head, segment)) needs them in scratch, and only when the caller does not
+// keep them itself.
+static bool fwd_is_fused(const tops_chunk_problem& pb, int nseg) { return pb.B * pb.H * nseg >= kFusedMinBlocks; }
+
 size_t fwd_workspace_bytes(const tops_chunk_fwd_params& p) {
-  return (p.saved_out ? 0 : state_bytes(p.pb)) + segment_floats(p.pb, pick_segments(p.pb)) * sizeof(float) + 256;
+  const int nseg = pick_segments(p.pb);
+  const bool states_in_ws = !p.saved_out && !fwd_is_fused(p.pb, nseg);
+  return (states_in_ws ? state_bytes(p.pb) : 0) + segment_floats(p.pb, nseg) * sizeof(float) + 256;
 }
 
 int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st) {
   const tops_chunk_problem& pb = p.pb;
   if (p.g_cumsum_out || p.A_out || p.h_out) return TOPS_E_UNSUPPORTED;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.o) ||
-      !aligned16(p.h0) || !aligned16(p.ht) || !aligned16(ws))
+      !aligned16(p.h0) || !aligned16(p.ht) || !aligned16(p.saved_out) || !aligned16(ws))
     return TOPS_E_ALIGN;
   const int BT = pb.B * pb.T, NT = pb.T / C;
   const int nseg = pick_segments(pb);
   // workspace: [chunk-start states unless the caller keeps them] [segment scratch]
   char* wsp = reinterpret_cast<char*>(ws);
   void* h = p.saved_out ? p.saved_out : wsp;
-  const SegmentScratch sc(reinterpret_cast<float*>(wsp + (p.saved_out ? 0 : state_bytes(pb))), pb, nseg);
+  const bool fused = fwd_is_fused(pb, nseg);
+  const SegmentScratch sc(reinterpret_cast<float*>(wsp + ((p.saved_out || fused) ? 0 : state_bytes(pb))), pb, nseg);
   int rc;
   const float* start = p.h0;
   float* last = p.ht;
@@ -1498,7 +1296,7 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
     start = sc.starts;
     last = nullptr;   // the join kernel has written the final state
   }
-  if (pb.B * pb.H * nseg >= kFusedMinBlocks) {
+  if (fused) {
     // enough blocks to fill the GPU with one per (batch, head, segment): one pass over q, k, g, v
     FusedParams up;
     if ((rc = act_map(&up.mq, p.q, BT, pb.H)) || (rc = act_map(&up.mk, p.k, BT, pb.H)) ||
@@ -1553,7 +1351,8 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   const tops_chunk_problem& pb = p.pb;
   if (!bwd_dtypes_ok(p)) return TOPS_E_UNSUPPORTED;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.do_) ||
-      !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(ws))
+      !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(p.dq) || !aligned16(p.dk) ||
+      !aligned16(p.dv) || !aligned16(p.dg) || !aligned16(p.h_saved) || !aligned16(ws))
     return TOPS_E_ALIGN;
   // workspace: [dh'] [h' unless the forward kept it] [segment scratch]
   const int nseg = pick_segments(pb);
@@ -1597,20 +1396,15 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   return launch_bwd_main<__nv_bfloat16, __nv_bfloat16>(bp, st);
 }
 
-#ifdef TOPS_TIMING
-extern "C" int tops_b200_debug_timing(long long* out, int n, int reset) {
-  long long z[16] = {0};
-  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(long long) * (n < 16 ? n : 16)) != cudaSuccess) return TOPS_E_CUDA;
-  if (reset) cudaMemcpyToSymbol(g_timing, z, sizeof z);
-  return TOPS_OK;
-}
-#endif
-
 int device_error(int* out) {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return TOPS_E_CUDA;
   *out = v;
   return TOPS_OK;
+}
+
+int device_error_set(int code) {
+  return cudaMemcpyToSymbol(g_error, &code, sizeof(int)) == cudaSuccess ? TOPS_OK : TOPS_E_CUDA;
 }
 
 }  // namespace sm100

@@ -15,5 +15,7 @@ size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p);
 int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
 // Reads the device error word (0 = no bounded wait has ever given up).
 int device_error(int* out);
+// Overwrites the device error word (0 clears it).
+int device_error_set(int code);
 }  // namespace sm100
 }  // namespace tops

@@ -1,0 +1,119 @@
+// Device-side pieces shared by the tcgen05 kernel files: tile sizes, the constant patterns that turn a
+// gate tile into cumulative-gate exponents with one tensor-core product, small packing helpers, and the
+// per-file error word of the bounded waits.
+#pragma once
+#include "sm100_prims.cuh"
+
+namespace tops {
+namespace sm100 {
+
+// First bounded wait that gave up in a kernel of this translation unit (0 = none).
+static __device__ int g_error;
+
+namespace {
+
+constexpr int C = 64;    // chunk
+constexpr int D = 128;   // K = V
+constexpr int NTHREADS = 512;
+constexpr int SEG = 16;  // time steps per thread
+constexpr uint32_t SLAB64 = 64 * 128;        // bytes of a 64-row slab
+constexpr uint32_t TILE64 = 2 * SLAB64;      // 64 x 128 bf16 tile
+constexpr uint32_t TILE128 = 2 * 128 * 128;  // 128 x 128 bf16 tile
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+__device__ __forceinline__ float ld_bf16(const uint8_t* tile, uint32_t off) {
+  return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + off));
+}
+// offset of (row i, this thread's column) in a 64-row tile
+struct ColAddr {
+  uint32_t base, cchunk;
+  __device__ __forceinline__ uint32_t at(int i) const {
+    return base + (uint32_t)i * 128u + (((cchunk ^ (uint32_t)i) & 7u) << 4);
+  }
+};
+__device__ __forceinline__ ColAddr col_prep(int rows, int col) {
+  return ColAddr{(uint32_t)((col >> 6) * rows * 128 + (col & 7) * 2), (uint32_t)((col & 63) >> 3)};
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ void fail(int code) { atomicCAS(&g_error, 0, code); }
+// A block that gave up marks one element of every output it owns with NaN, so that a caller who
+// never reads the error word sees a poisoned result rather than whatever the buffer held before.
+__device__ __forceinline__ void poison(float* p) { if (p) *p = __int_as_float(0x7fc00000); }
+__device__ __forceinline__ void poison(__nv_bfloat16* p) { if (p) *reinterpret_cast<unsigned short*>(p) = 0x7fc0; }
+
+// Constant 64 x 64 patterns, stored as K-major bf16 tiles, that turn the gate
+// tile g [time j][channel] into exponents with one tensor-core product:
+//   TRI_INCL  L[i][j] = (j <= i)                 -> G_i           (inclusive cumulative gate)
+//   TRI_REV   U[i][j] = (j > i)                  -> G_n - G_i
+//   TRI_REVN  TRI_REV with row 63 all ones       -> G_n - G_i for i < 63 and G_n itself in row 63 (whose own
+//             exponent, 0, needs no product)
+//   TRI_MID   L - 1/2 [j == 0] - 1/2             -> G_i - (G_0 + G_n) / 2
+// All entries (0, 1, +-1/2) are exact in bf16 and the products accumulate in fp32.
+enum { TRI_INCL = 0, TRI_REV = 1, TRI_MID = 2, TRI_REVN = 3 };
+__device__ __forceinline__ float tri_value(int kind, int i, int j) {
+  if (kind == TRI_INCL) return j <= i ? 1.f : 0.f;
+  if (kind == TRI_REV) return j > i ? 1.f : 0.f;
+  if (kind == TRI_REVN) return (i == 63 || j > i) ? 1.f : 0.f;
+  return j == 0 ? 0.f : (j <= i ? 0.5f : -0.5f);
+}
+__device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind) {
+  for (int idx = threadIdx.x; idx < rows * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8, i = r & 63;
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) w[t] = pack_bf16(tri_value(kind, i, c8 + 2 * t), tri_value(kind, i, c8 + 2 * t + 1));
+    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+// multiply 8 packed bf16 by 8 fp32 factors
+__device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
+  __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);
+  uint4 y;
+  uint32_t* py = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = __bfloat1622float2(px[t]);
+    py[t] = pack_bf16(v.x * f[2 * t], v.y * f[2 * t + 1]);
+  }
+  return y;
+}
+
+// masked, scaled bf16 copy of 16 columns [16 seg, 16 seg + 16) of row i of a
+// 64 x 64 fp32 accumulator into a K-major 64 x 64 tile
+__device__ __forceinline__ void store_tril16(uint8_t* dst, int i, int j0, const float (&a)[16], float scale) {
+#pragma unroll
+  for (int c8 = 0; c8 < 16; c8 += 8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 8; t += 2) {
+      const int j = j0 + c8 + t;
+      w[t >> 1] = pack_bf16(j <= i ? a[c8 + t] * scale : 0.f, j + 1 <= i ? a[c8 + t + 1] * scale : 0.f);
+    }
+    *reinterpret_cast<uint4*>(dst + slab_off(i, j0 + c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// 16 x 64 K-major pattern: row 0 sums the gates (G_n), row 1 gives G_n - mid = (G_n - G_0) / 2
+__device__ __forceinline__ void build_w_tile(uint8_t* tile) {
+  for (int idx = threadIdx.x; idx < 16 * 8; idx += blockDim.x) {
+    const int r = idx >> 3, c8 = (idx & 7) * 8;
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int j = c8 + 2 * t;
+      const float a = r == 0 ? 1.f : (r == 1 ? (j == 0 ? 0.f : 0.5f) : 0.f);
+      const float b = r == 0 ? 1.f : (r == 1 ? 0.5f : 0.f);
+      w[t] = pack_bf16(a, b);
+    }
+    *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace
+}  // namespace sm100
+}  // namespace tops

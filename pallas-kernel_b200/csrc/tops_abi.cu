@@ -11,6 +11,7 @@
 #include "gla_generic.cuh"
 #include "gla_sm100.cuh"
 #include "kda.cuh"
+#include "kda_sm100.cuh"
 #include "recurrent.cuh"
 
 namespace tops {
@@ -144,8 +145,19 @@ extern "C" int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb) {
 
 extern "C" int tops_b200_device_error(int* out) {
   if (!out) return TOPS_E_NULL;
-  return sm100::device_error(out);
+  int a = 0, b = 0;
+  int rc = sm100::device_error(&a);
+  if (rc == TOPS_OK) rc = sm100::kda_device_error(&b);
+  *out = a ? a : b;
+  return rc;
 }
+
+extern "C" int tops_b200_device_error_set(int code) {
+  int rc = sm100::device_error_set(code);
+  return rc ? rc : sm100::kda_device_error_set(code);
+}
+
+extern "C" int tops_b200_device_error_reset(void) { return tops_b200_device_error_set(0); }
 
 extern "C" int tops_b200_profile_enable(int on) {
   g_prof_on.store(on ? 1 : 0);
@@ -182,7 +194,7 @@ extern "C" int tops_b200_chunk_local_cumsum(const tops_cumsum_params* p, void* s
   if (p->B < 1 || p->T < 1 || p->H < 1 || p->D < 1) return TOPS_E_BAD_SHAPE;
   if (p->chunk < 1 || (p->chunk & (p->chunk - 1))) return TOPS_E_BAD_SHAPE;
   if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
-  if (p->cu_seqlens) return TOPS_E_UNSUPPORTED;  // packed cumsum goes through the chunked entry points
+  if (p->cu_seqlens) return TOPS_E_UNSUPPORTED;  // packed batches: the fused chunk entry points do their own cumsum
   SeqMap m{};
   m.N = p->B; m.T = p->T; m.C = p->chunk; m.NT = cdiv(p->T, p->chunk);
   return generic::launch_cumsum(m, p->H, p->D, p->dtype, p->reverse, p->g, p->out, p->B * m.NT,
@@ -413,6 +425,19 @@ extern "C" int tops_b200_kda_fwd(const tops_kda_fwd_params* p, void* stream) {
   if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1 || p->K > 256) return TOPS_E_BAD_SHAPE;
   if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
   return kda::fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_chunk_kda_supported(const tops_chunk_kda_fwd_params* p) {
+  if (!p || p->B < 1 || p->T < 1 || p->H < 1) return 0;
+  return sm100::kda_supported(*p) ? 1 : 0;
+}
+
+extern "C" int tops_b200_chunk_kda_fwd(const tops_chunk_kda_fwd_params* p, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->g || !p->beta || !p->o) return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
+  if (!sm100::kda_supported(*p)) return TOPS_E_UNSUPPORTED;
+  return sm100::kda_chunk_fwd(*p, (cudaStream_t)stream);
 }
 
 extern "C" size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p) {

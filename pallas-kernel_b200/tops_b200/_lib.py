@@ -6,6 +6,7 @@ not been built, and every op raises when the library reports an error.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 import os
 
 import torch
@@ -91,6 +92,13 @@ class KdaBwdParams(C.Structure):
                 ("dg", _vp), ("dbeta", _vp), ("dh0", _vp)]
 
 
+class ChunkKdaFwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("chunk", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("beta", _vp),
+                ("h0", _vp), ("o", _vp), ("ht", _vp), ("Aqk_out", _vp), ("Akk_out", _vp), ("saved_h", _vp),
+                ("saved_vnew", _vp), ("saved_T", _vp)]
+
+
 lib.tops_b200_strerror.restype = C.c_char_p
 lib.tops_b200_strerror.argtypes = [C.c_int]
 lib.tops_b200_launch_count.restype = C.c_int64
@@ -99,6 +107,10 @@ lib.tops_b200_chunk_selected_impl.restype = C.c_int
 lib.tops_b200_chunk_selected_impl.argtypes = [C.POINTER(ChunkProblem)]
 lib.tops_b200_device_error.restype = C.c_int
 lib.tops_b200_device_error.argtypes = [C.POINTER(C.c_int)]
+lib.tops_b200_device_error_reset.restype = C.c_int
+lib.tops_b200_device_error_reset.argtypes = []
+lib.tops_b200_device_error_set.restype = C.c_int
+lib.tops_b200_device_error_set.argtypes = [C.c_int]
 lib.tops_b200_profile_enable.restype = C.c_int
 lib.tops_b200_profile_enable.argtypes = [C.c_int]
 lib.tops_b200_profile_read.restype = C.c_int
@@ -117,6 +129,10 @@ for _name, _ptype, _ws in [
     _f = getattr(lib, _name)
     _f.restype = C.c_int
     _f.argtypes = [C.POINTER(_ptype), _vp, _sz, _vp] if _ws else [C.POINTER(_ptype), _vp]
+lib.tops_b200_chunk_kda_supported.restype = C.c_int
+lib.tops_b200_chunk_kda_supported.argtypes = [C.POINTER(ChunkKdaFwdParams)]
+lib.tops_b200_chunk_kda_fwd.restype = C.c_int
+lib.tops_b200_chunk_kda_fwd.argtypes = [C.POINTER(ChunkKdaFwdParams), _vp]
 lib.tops_b200_chunk_gla_fwd_static.restype = C.c_int
 lib.tops_b200_chunk_gla_fwd_static.argtypes = [C.POINTER(ChunkFwdParams), _vp]
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
@@ -163,6 +179,38 @@ def device_error() -> int:
     out = C.c_int(0)
     check(lib.tops_b200_device_error(C.byref(out)), "device_error")
     return out.value
+
+
+def device_error_reset() -> None:
+    check(lib.tops_b200_device_error_reset(), "device_error_reset")
+
+
+def raise_on_device_error(what: str = "tops_b200") -> None:
+    """Synchronise and raise TopsError when a kernel of this library gave up on a bounded wait
+    since the word was last cleared (its outputs are then poisoned with NaN, not valid results).
+    The word is cleared before raising so that one failure does not mark every later call."""
+    code = device_error()
+    if code != 0:
+        device_error_reset()
+        raise TopsError(f"{what}: a kernel gave up on a bounded device-side wait (code {code}); "
+                        "its outputs are invalid")
+
+
+# TOPS_B200_CHECK_DEVICE=1 makes every differentiable op check the device error word after its
+# backward pass (one synchronisation per step); off by default, the word stays readable at any time.
+CHECK_DEVICE = os.environ.get("TOPS_B200_CHECK_DEVICE", "0") not in ("", "0")
+
+
+def on_tensor_device(fn):
+    """Run `fn(t, ...)` with the CUDA device of its first argument current: kernel selection,
+    workspace sizes and launches all follow the current device."""
+    @functools.wraps(fn)
+    def wrapped(t, *args, **kwargs):
+        if not (isinstance(t, torch.Tensor) and t.is_cuda):
+            return fn(t, *args, **kwargs)   # the op's own assertions reject it
+        with torch.cuda.device(t.device):
+            return fn(t, *args, **kwargs)
+    return wrapped
 
 
 def workspace(nbytes: int, device) -> torch.Tensor:

@@ -10,6 +10,7 @@ from .. import _lib as L
 from .common import make_problem, total_chunks
 
 
+@L.on_tensor_device
 def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqlens=None,
                    want_gcum=False, want_A=False, want_h=False, impl=L.IMPL_AUTO, want_saved=False):
     """Run tops_b200_chunk_gla_fwd.  Returns (o, ht, g_cumsum, A, h); the last
@@ -50,6 +51,7 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
     return o, ht, gcum, A, hs
 
 
+@L.on_tensor_device
 def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dtype, want_dg, want_dh0,
                    cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False):
     """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0).  `h_saved`

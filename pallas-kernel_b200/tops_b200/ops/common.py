@@ -43,6 +43,7 @@ def total_chunks(B, T, chunk, cu_seqlens=None) -> int:
     return sum(cdiv(cu[i + 1] - cu[i], chunk) for i in range(len(cu) - 1))
 
 
+@L.on_tensor_device
 def chunk_local_cumsum(g: torch.Tensor, chunk_size: int, reverse: bool = False,
                        cu_seqlens=None) -> torch.Tensor:
     """Chunk-local inclusive cumsum of log-gates along T, fp32 out
@@ -72,6 +73,7 @@ def _gate_args(g, g_gamma, gk):
     return L.GATE_NONE, None
 
 
+@L.on_tensor_device
 def chunk_fwd_h(k, v, *, g=None, g_gamma=None, gk=None, h0=None, output_final_state=False,
                 states_in_fp32=False, chunk_size=64):
     """Chunk-start states of h <- h*exp(gate_last) + k~^T v~
@@ -98,6 +100,7 @@ def chunk_fwd_h(k, v, *, g=None, g_gamma=None, gk=None, h0=None, output_final_st
     return h, ht
 
 
+@L.on_tensor_device
 def chunk_bwd_dh(q, do, *, g=None, g_gamma=None, gk=None, h0=None, dht=None, scale=1.0, chunk_size=64):
     """Reverse state-gradient scan (reference `tops/cpu/ops/common/chunk_h.py:229-427`).
     Returns (dh `[B,NT,H,K,V]` fp32, dh0 fp32 or None — only when h0 is given)."""

@@ -98,6 +98,8 @@ class _ChunkGLA(torch.autograd.Function):
         dq, dk, dv, dg, dh0 = chunk_bwd_call(q, k, v, g, kind, ctx.scale, h0, do.to(q.dtype), dht, ctx.chunk,
                                              torch.float32, g is not None, h0 is not None, ctx.cu, h_saved=hs,
                                              primal_dtypes=True)
+        if L.CHECK_DEVICE:
+            L.raise_on_device_error("chunk_gla backward")
         return (dq, dk, dv, dg, None if h0 is None else dh0.to(h0.dtype), None, None, None, None)
 
 
@@ -108,13 +110,15 @@ def chunk_gla(q, k, v, g=None, g_gamma=None, scale=None, initial_state=None, out
     g defaults to zeros, scale to K^-0.5, chunk_size to 16.  Returns
     (o in v.dtype, final state fp32 or None).  Differentiable in q, k, v, g,
     initial_state."""
-    assert g_gamma is None or g is None, "pass g or g_gamma, not both"
     B, T, H, K, V, N = _check_qkvg(q, k, v, g, initial_state, cu_seqlens)
     if scale is None:
         scale = K ** -0.5
-    if g_gamma is not None:
-        # constant per-head decay: the same log-gate on every channel and token
-        g = g_gamma.to(torch.float32).view(1, 1, H, 1).expand(B, T, H, K).contiguous()
+    # `g_gamma` is "used only when g is None" upstream (tops/ops/gla/chunk.py:1224-1228)
+    if g is None and g_gamma is not None:
+        # constant decay: `[H]` (one log-gate per head) or anything that broadcasts to [B,T,H,K]
+        gg = g_gamma.to(torch.float32)
+        gg = gg.view(1, 1, H, 1) if gg.ndim == 1 and gg.shape[0] == H else gg
+        g = torch.broadcast_to(gg, (B, T, H, K)).contiguous()
     if initial_state is not None:
         initial_state = initial_state.to(torch.float32)
     o, ht = _ChunkGLA.apply(q, k, v, g, initial_state, float(scale), bool(output_final_state),
@@ -131,6 +135,7 @@ def fused_chunk_gla(q, k, v, g=None, scale=None, initial_state=None, output_fina
 # ---------------------------------------------------------------------------
 # token-serial recurrence
 # ---------------------------------------------------------------------------
+@L.on_tensor_device
 def _rec_fwd_call(q, k, v, gk, gv, scale, initial_state, want_state, reverse, cu, o_dtype, state_out=None):
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -183,6 +188,7 @@ def fused_recurrent_fwd(q, k, v, gk=None, gv=None, scale=None, initial_state=Non
                          _cu_list(cu_seqlens), torch.float32)
 
 
+@L.on_tensor_device
 def fused_recurrent_bwd(q, k, v, gk=None, gv=None, o=None, do=None, dht=None, scale=None,
                         initial_state=None, reverse=False, cu_seqlens=None):
     """Two-pass recurrent backward (reference

@@ -6,9 +6,9 @@ update) with the reference's signatures (`tops/ops/kda/chunk.py:193-216`,
 
 `g` is the natural-log decay `[B,T,H,K]`, `beta` `[B,T,H]`.  `chunk_kda` and
 `fused_recurrent_kda` compute the same function; both are differentiable in
-q, k, v, g, beta, initial_state.  The kernels behind them walk the tokens one
-by one (the chunked WY form on the tensor cores is not built), so
-`chunk_size` only has to be valid, it does not change the result.
+q, k, v, g, beta, initial_state.  bf16 problems with K = V = 128, chunk 64 and
+T a multiple of 64 run the chunked WY / UT-transform kernels on the tensor
+cores (`chunk_kda_fwd`); everything else walks the tokens one by one.
 """
 from __future__ import annotations
 
@@ -35,6 +35,7 @@ def _check(q, k, v, g, beta, initial_state):
     return B, T, H, K, V
 
 
+@L.on_tensor_device
 def kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state):
     """One call of tops_b200_kda_fwd.  Returns (o in q.dtype, final state fp32 or None)."""
     B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
@@ -53,6 +54,7 @@ def kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state):
     return o, ht
 
 
+@L.on_tensor_device
 def kda_bwd(q, k, v, g, beta, do, scale, initial_state=None, dht=None):
     """Explicit backward (reference `tops/cpu/ops/kda/fused_recurrent.py:212-418`,
     `tops/cpu/ops/kda/chunk_bwd.py:525-668`).  Returns (dq, dk, dv, dg, dbeta in
@@ -79,10 +81,77 @@ def kda_bwd(q, k, v, g, beta, do, scale, initial_state=None, dht=None):
     return dq, dk, dv, dg, dbeta.to(beta.dtype), dh0
 
 
+def _chunk_params(q, k, v, g, beta, scale, chunk_size):
+    B, T, H, K = q.shape
+    p = L.ChunkKdaFwdParams()
+    p.B, p.T, p.H, p.K, p.V, p.chunk = B, T, H, K, v.shape[-1], int(chunk_size)
+    p.dtype, p.gate_dtype, p.scale = L.dtype_code(q.dtype), L.dtype_code(g.dtype), float(scale)
+    return p
+
+
+def chunk_kernels_take(q, k, v, g, beta, chunk_size=64):
+    """True when the chunked tensor-core kernels serve this problem."""
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and g.dtype == torch.bfloat16):
+        return False
+    with torch.cuda.device(q.device):
+        return bool(L.lib.tops_b200_chunk_kda_supported(C.byref(_chunk_params(q, k, v, g, beta, 1.0, chunk_size))))
+
+
+@L.on_tensor_device
+def _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, chunk_size, want_A, want_saved):
+    """One call of tops_b200_chunk_kda_fwd.  Returns (o, ht, Aqk, Akk, saved) with Aqk / Akk fp32
+    `[B,T,H,C]` when `want_A`, and saved = (h', v', T) residuals for the backward when `want_saved`."""
+    B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
+    dev = q.device
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    beta_c = beta.to(q.dtype).contiguous()
+    h0 = None if initial_state is None else initial_state.float().contiguous()
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    Aqk = torch.empty(B, T, H, chunk_size, dtype=torch.float32, device=dev) if want_A else None
+    Akk = torch.empty(B, T, H, chunk_size, dtype=torch.float32, device=dev) if want_A else None
+    saved = None
+    if want_saved:
+        saved = (torch.empty(B, T // chunk_size, H, K, V, dtype=q.dtype, device=dev),
+                 torch.empty(B, T, H, V, dtype=q.dtype, device=dev),
+                 torch.empty(B, T, H, chunk_size, dtype=q.dtype, device=dev))
+    p = _chunk_params(q, k, v, g, beta_c, scale, chunk_size)
+    p.q, p.k, p.v, p.g, p.beta, p.h0 = L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta_c), L.ptr(h0)
+    p.o, p.ht, p.Aqk_out, p.Akk_out = L.ptr(o), L.ptr(ht), L.ptr(Aqk), L.ptr(Akk)
+    if saved is not None:
+        p.saved_h, p.saved_vnew, p.saved_T = (L.ptr(t) for t in saved)
+    L.check(L.lib.tops_b200_chunk_kda_fwd(C.byref(p), L.stream_ptr(dev)), "chunk_kda_fwd")
+    return o, ht, Aqk, Akk, saved
+
+
+def chunk_kda_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,
+                  chunk_size=64):
+    """Chunked forward orchestrator (reference `tops/ops/kda/chunk.py:25-190`).  Returns
+    (o, final state or None, g_cumsum, Aqk, Akk): g_cumsum the chunk-local cumulative gate in log2
+    space (fp32 `[B,T,H,K]`, `tops/ops/kda/gate.py:19-51`), Aqk / Akk fp32 `[B,T,H,chunk]` — row i of
+    its chunk at token i of tril(scale q k^T 2^(G_i-G_j)) and of (I + stril(beta k k^T 2^(G_i-G_j)))^-1."""
+    from .common import chunk_local_cumsum
+    assert cu_seqlens is None, "packed KDA batches are not supported"
+    assert q.shape[1] % chunk_size == 0, \
+        f"Sequence length T={q.shape[1]} must be divisible by chunk_size={chunk_size}"
+    assert chunk_kernels_take(q, k, v, g, beta, chunk_size), \
+        "chunk_kda_fwd takes bf16 q/k/v/g with K = V = 128 and chunk_size 64 (use chunk_kda for other problems)"
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    o, ht, Aqk, Akk, _ = _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, chunk_size,
+                                         True, False)
+    g_cumsum = chunk_local_cumsum(g, chunk_size) * 1.4426950408889634
+    return o, ht, g_cumsum, Aqk, Akk
+
+
 class _KDA(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state):
-        o, ht = kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state)
+    def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, chunked):
+        if chunked:
+            o, ht, _, _, _ = _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, 64, False,
+                                             False)
+        else:
+            o, ht = kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state)
         ctx.save_for_backward(q, k, v, g, beta, initial_state)
         ctx.scale = scale
         return o, ht
@@ -91,7 +160,7 @@ class _KDA(torch.autograd.Function):
     def backward(ctx, do, dht):
         q, k, v, g, beta, h0 = ctx.saved_tensors
         dq, dk, dv, dg, dbeta, dh0 = kda_bwd(q, k, v, g, beta, do, ctx.scale, h0, dht)
-        return dq, dk, dv, dg, dbeta, None if h0 is None else dh0.to(h0.dtype), None, None
+        return dq, dk, dv, dg, dbeta, None if h0 is None else dh0.to(h0.dtype), None, None, None
 
 
 def fused_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False):
@@ -99,7 +168,7 @@ def fused_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output
     B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
     if scale is None:
         scale = K ** -0.5
-    o, ht = _KDA.apply(q, k, v, g, beta, initial_state, float(scale), bool(output_final_state))
+    o, ht = _KDA.apply(q, k, v, g, beta, initial_state, float(scale), bool(output_final_state), False)
     return o, (ht if output_final_state else None)
 
 
@@ -110,4 +179,11 @@ def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_sta
     assert cu_seqlens is None, "packed KDA batches are not supported"
     assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, "chunk_size must be a power of 2"
     assert q.shape[1] % chunk_size == 0, f"T ({q.shape[1]}) must be divisible by chunk_size ({chunk_size})"
-    return fused_recurrent_kda(q, k, v, g, beta, scale, initial_state, output_final_state)
+    B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
+    if scale is None:
+        scale = K ** -0.5
+    # the result does not depend on the chunk length beyond where roundings fall: a problem the
+    # tensor-core kernels take runs with their chunk of 64
+    chunked = T % 64 == 0 and chunk_kernels_take(q, k, v, g, beta, 64)
+    o, ht = _KDA.apply(q, k, v, g, beta, initial_state, float(scale), bool(output_final_state), chunked)
+    return o, (ht if output_final_state else None)

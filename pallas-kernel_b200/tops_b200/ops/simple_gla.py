@@ -115,6 +115,8 @@ class _ChunkSimpleGLA(torch.autograd.Function):
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(q, k, v, g, g_gamma, h0, do.to(q.dtype), dht, ctx.scale, ctx.chunk,
                                                    ctx.cu, h_saved=hs)
         # a constant decay gets a zero cotangent, as in the reference (tops/ops/simple_gla/chunk.py:764)
+        if L.CHECK_DEVICE:
+            L.raise_on_device_error("chunk_simple_gla backward")
         dgamma = None if g_gamma is None else torch.zeros_like(g_gamma)
         return (dq, dk, dv, None if g is None else dg.to(g.dtype), dgamma,
                 None if h0 is None else dh0.to(h0.dtype), None, None, None, None)

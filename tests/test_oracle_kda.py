@@ -45,3 +45,50 @@ def test_explicit_backward_equals_autodiff():
     ((o2 * do).sum() + (s2 * dht).sum()).backward()
     for a, b in zip(leaves2, leaves):
         assert (a.grad - b.grad).abs().max() < 1e-7
+
+
+@pytest.mark.parametrize("B,T,H,Kd,V,C", [(2, 64, 2, 16, 24, 16), (1, 128, 2, 32, 16, 64), (1, 64, 3, 8, 8, 32)])
+@pytest.mark.parametrize("use_h0", [False, True])
+def test_staged_chunk_forward_equals_recurrent(B, T, H, Kd, V, C, use_h0):
+    """chunk_kda_fwd (cumsum -> Aqk / Akk^-1 -> w, u -> delta-rule scan -> output) against the token
+    recurrence: one convention for Akk ((I + stril(beta k k^T 2^dG))^-1, beta on the right-hand
+    sides), pinned end to end (fp64, 1e-10)."""
+    q, k, v, g, beta, h0 = _rand(2, B, T, H, Kd, V)
+    h0 = h0 if use_h0 else None
+    o1, s1 = K.naive_recurrent_kda(q, k, v, g, beta, None, h0, True)
+    o2, s2, gcs, Aqk, Akk = K.chunk_kda_fwd(q, k, v, g, beta, None, h0, True, chunk_size=C)
+    assert (o1 - o2).abs().max() < 1e-10 and (s1 - s2).abs().max() < 1e-10
+    assert gcs.shape == g.shape and Aqk.shape == (B, T, H, C) and Akk.shape == (B, T, H, C)
+    # Akk is unit lower triangular; Aqk is lower triangular with the diagonal
+    A = Akk.reshape(B, T // C, C, H, C)
+    i = torch.arange(C)
+    assert (A[:, :, i, :, i] - 1).abs().max() < 1e-12
+    assert torch.triu(A.permute(0, 1, 3, 2, 4), 1).abs().max() == 0
+    assert torch.triu(Aqk.reshape(B, T // C, C, H, C).permute(0, 1, 3, 2, 4), 1).abs().max() == 0
+
+
+@pytest.mark.parametrize("B,T,H,Kd,V,C", [(2, 64, 2, 16, 24, 16), (1, 128, 2, 32, 16, 64)])
+@pytest.mark.parametrize("use_h0", [False, True])
+def test_staged_chunk_backward_equals_autodiff(B, T, H, Kd, V, C, use_h0):
+    """The six-stage chunk backward (dAv, dhu, fused WY, intra, reverse cumsum, 1/ln2) against autodiff
+    of the token recurrence and against the explicit token-level backward (fp64, 1e-7), as
+    tests/ref/kda/test_naive_kda.py:198-293 does for the reference."""
+    q, k, v, g, beta, h0 = _rand(3, B, T, H, Kd, V)
+    h0 = h0 if use_h0 else None
+    gen = torch.Generator().manual_seed(9)
+    do = torch.randn(B, T, H, V, dtype=DT, generator=gen)
+    dht = torch.randn(B, H, Kd, V, dtype=DT, generator=gen)
+    names = ("q", "k", "v", "g", "beta") + (("h0",) if use_h0 else ())
+    leaves = [x.clone().requires_grad_() for x in (q, k, v, g, beta)] + ([h0.clone().requires_grad_()] if use_h0 else [])
+    o, s = K.naive_recurrent_kda(*leaves[:5], None, leaves[5] if use_h0 else None, True)
+    ((o * do).sum() + (s * dht).sum()).backward()
+    o2, ht2, dq, dk, dv, dg, db, dh0 = K.chunk_kda_with_grads(q, k, v, g, beta, do, None, h0, dht, chunk_size=C)
+    assert (o2 - o).abs().max() < 1e-10 and (ht2 - s).abs().max() < 1e-10
+    got = dict(q=dq, k=dk, v=dv, g=dg, beta=db, h0=dh0)
+    for n, leaf in zip(names, leaves):
+        assert (got[n] - leaf.grad).abs().max() < 1e-7, n
+    if not use_h0:
+        assert dh0 is None
+    exp = K.fused_recurrent_kda_bwd(q, k, v, g, beta, do, None, h0, dht)
+    for a, b in zip((dq, dk, dv, dg, db), exp):
+        assert (a - b).abs().max() < 1e-7

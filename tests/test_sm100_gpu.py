@@ -115,3 +115,16 @@ def test_sm100_gradients_in_primal_dtypes():
     # a kernel family without the narrow outputs returns the same dtypes through a cast
     slow = chunk_bwd_call(*args, impl=L.IMPL_GENERIC, primal_dtypes=True)
     assert slow[0].dtype == torch.bfloat16 and slow[3].dtype == torch.bfloat16
+
+
+def test_device_error_word_raises_and_clears():
+    """Host-side injection: a non-zero device error word (what a kernel leaves behind when a bounded
+    wait gives up) turns into TopsError at the next check, and the check clears it."""
+    from tops_b200 import _lib as L
+    assert L.device_error() == 0
+    L.check(L.lib.tops_b200_device_error_set(7), "device_error_set")
+    assert L.device_error() == 7
+    with pytest.raises(L.TopsError):
+        L.raise_on_device_error("test")
+    assert L.device_error() == 0
+    L.raise_on_device_error("test")   # clean word: no exception

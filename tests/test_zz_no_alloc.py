@@ -29,7 +29,8 @@ def _params(x, o, ht, chunk, dtype):
 
 @pytest.mark.parametrize("dtype,B,T,H,K,V,chunk", [
     (torch.float32, 2, 200, 2, 64, 48, 32),        # generic kernels, ragged T
-    (torch.bfloat16, 1, 256, 2, 128, 128, 64),     # tcgen05 kernels
+    (torch.bfloat16, 1, 256, 2, 128, 128, 64),     # tcgen05 kernels: state scan + chunk outputs
+    (torch.bfloat16, 4, 1024, 16, 128, 128, 64),   # tcgen05 kernels: one fused pass over two time segments
 ])
 def test_static_scratch_forward_matches_workspace_forward(dtype, B, T, H, K, V, chunk):
     from tops_b200 import _lib as L
@@ -46,11 +47,32 @@ def test_static_scratch_forward_matches_workspace_forward(dtype, B, T, H, K, V, 
         o = torch.full_like(o_ref, float("nan"))
         ht = torch.full_like(ht_ref, float("nan"))
         p2 = _params(x, o, ht, chunk, dtype)
+        # the claim itself: the device has exactly as much free memory after the call as before
+        # (the ordinary call above has already loaded every kernel the static call launches)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         L.check(L.lib.tops_b200_chunk_gla_fwd_static(C.byref(p2), stream), "chunk_gla_fwd_static")
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert_close("o", o, o_ref, dtype)
         assert_close("ht", ht, ht_ref, dtype)
         assert L.device_error() == 0
+
+
+def test_fused_forward_needs_no_state_scratch():
+    """The one-pass tcgen05 forward keeps its chunk-start states on chip, so its scratch is the
+    segment bookkeeping only — far less than the bf16 [B,NT,H,K,V] states of the two-kernel form."""
+    from tops_b200 import _lib as L
+    from tops_b200.ops.common import make_problem
+    B, T, H = 8, 4096, 16
+    p = L.ChunkFwdParams()
+    p.pb = make_problem(B, T, H, 128, 128, 64, L.BF16, L.BF16, L.GATE_PER_CHANNEL, 0.1, keep=[])
+    p.q = p.k = p.v = p.g = p.o = 256
+    if L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) != L.IMPL_SM100:
+        pytest.skip("needs the tcgen05 kernels")
+    states = B * (T // 64) * H * 128 * 128 * 2
+    assert L.lib.tops_b200_chunk_fwd_workspace_bytes(C.byref(p)) < states // 100
+    assert L.lib.tops_b200_chunk_fwd_workspace_bytes(C.byref(p)) <= L.STATIC_SCRATCH_BYTES
 
 
 def test_static_scratch_refuses_problems_beyond_its_size():
