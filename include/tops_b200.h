@@ -200,7 +200,11 @@ int tops_b200_chunk_gla_fwd(const tops_chunk_fwd_params* p, void* workspace, siz
  *    TOPS_STATIC_SCRATCH_BYTES are refused with TOPS_E_STATIC_LIMIT; nothing
  *    is launched.
  *  - The first call on each device looks up the array's device address (with
- *    that device current).  Make that first call outside any stream capture.
+ *    that device current); the CUDA runtime may load the part of the library
+ *    image that holds the array at that moment, which is when the
+ *    TOPS_STATIC_SCRATCH_BYTES leave the device's free memory.  Make that
+ *    first call outside any stream capture.  From the second call on the
+ *    free memory of the device is the same before and after a call.
  *  - All calls on a device share the one array and it keeps whatever the last
  *    call left there.  The forward pass overwrites every element it later
  *    reads, so nothing has to be cleared; but two calls whose kernels overlap
@@ -367,6 +371,72 @@ typedef struct {
 } tops_kda_bwd_params;
 size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p);
 int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Gate activations — the step before the attention kernels.
+ *   TOPS_GATE_ACT_KDA              y = -exp(A_log[h]) softplus(g + dt_bias[h,k])
+ *   TOPS_GATE_ACT_KDA_LOWER_BOUND  y = lower_bound sigmoid(exp(A_log[h]) (g + dt_bias[h,k]))
+ *       replace `kda_gate_fwd` / `fused_kda_gate` / `kda_gate_bwd`
+ *       (`tops/cpu/ops/kda/gate.py:60-204`, `tops/ops/kda/gate.py:54-125`);
+ *   TOPS_GATE_ACT_LOG_SIGMOID      y = log_sigmoid(g) / normalizer, optionally clipped from below
+ *       replaces the gate of the GLA layer (`tops/layers/gla.py:277-279`).
+ * g is `[rows, H, K]` (rows = B*T), K % 4 == 0.  The backward writes dg in the dtype of g and, for the
+ * KDA kinds, dA_log `[H]` and d dt_bias `[H*K]` (fp32; NULL to skip) through per-row-block partial sums
+ * in the workspace, added in a fixed order.
+ * ------------------------------------------------------------------------ */
+enum { TOPS_GATE_ACT_KDA = 0, TOPS_GATE_ACT_KDA_LOWER_BOUND = 1, TOPS_GATE_ACT_LOG_SIGMOID = 2 };
+typedef struct {
+  int64_t rows;
+  int32_t H, K;
+  int32_t kind;
+  int32_t dtype, out_dtype;
+  const void* g;
+  const float* A_log;   /* [H]; KDA kinds */
+  const float* dt_bias; /* [H*K] or NULL */
+  float lower_bound, normalizer, clamp_min;
+  int32_t has_clamp_min;
+  void* out;            /* [rows,H,K] in out_dtype */
+} tops_gate_act_params;
+typedef struct {
+  tops_gate_act_params fwd; /* `out` unused */
+  const void* dy;           /* [rows,H,K] */
+  int32_t dy_dtype;
+  void* dg;                 /* [rows,H,K] in fwd.dtype */
+  float* dA_log;            /* [H] or NULL */
+  float* dbias;             /* [H*K] or NULL */
+} tops_gate_act_bwd_params;
+int tops_b200_gate_act_fwd(const tops_gate_act_params* p, void* stream);
+size_t tops_b200_gate_act_bwd_workspace_bytes(const tops_gate_act_bwd_params* p);
+int tops_b200_gate_act_bwd(const tops_gate_act_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Row normalisations over the last dimension D (D % 4 == 0, D <= 1024), `[rows, D]`.
+ *   l2norm          y = x / sqrt(sum(x^2) + eps)      — the q/k normalisation of KDA
+ *                   (`tops/cpu/ops/kda/fused_recurrent.py:14-18`, eps 1e-6); `rstd` (fp32 [rows]) optional.
+ *   rmsnorm_gated   y = x rsqrt(mean(x^2) + eps) weight silu(gate)   — `FusedRMSNormGated`
+ *                   (`tops/modules/fused_norm_gate.py:6-37`); weight fp32 [D] or NULL.
+ * Backward: dx (and dgate, dweight fp32 [D] or NULL for the gated norm) from x, gate, dy.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int64_t rows;
+  int32_t D;
+  int32_t dtype;
+  float eps;
+  const void* x;
+  const void* gate;     /* rmsnorm_gated only */
+  const float* weight;  /* rmsnorm_gated only, may be NULL */
+  void* y;              /* forward output (unused by the backward) */
+  float* rstd;          /* l2norm forward, may be NULL */
+  const void* dy;       /* backward */
+  void* dx;             /* backward */
+  void* dgate;          /* rmsnorm_gated backward */
+  float* dweight;       /* rmsnorm_gated backward, may be NULL */
+} tops_norm_params;
+int tops_b200_l2norm_fwd(const tops_norm_params* p, void* stream);
+int tops_b200_l2norm_bwd(const tops_norm_params* p, void* stream);
+int tops_b200_rmsnorm_gated_fwd(const tops_norm_params* p, void* stream);
+size_t tops_b200_rmsnorm_gated_bwd_workspace_bytes(const tops_norm_params* p);
+int tops_b200_rmsnorm_gated_bwd(const tops_norm_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

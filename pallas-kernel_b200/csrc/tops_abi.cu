@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "elementwise.cuh"
 #include "gla_generic.cuh"
 #include "gla_sm100.cuh"
 #include "kda.cuh"
@@ -452,4 +453,69 @@ extern "C" int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, 
   if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype)) return TOPS_E_BAD_DTYPE;
   if (!workspace || workspace_bytes < kda::bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
   return kda::bwd(*p, workspace, (cudaStream_t)stream);
+}
+
+// ---- gate activations and row normalisations -------------------------------------
+extern "C" int tops_b200_gate_act_fwd(const tops_gate_act_params* p, void* stream) {
+  if (!p || !p->g || !p->out) return TOPS_E_NULL;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->out_dtype)) return TOPS_E_BAD_DTYPE;
+  int rc = elementwise::gate_check(*p);
+  return rc ? rc : elementwise::gate_fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" size_t tops_b200_gate_act_bwd_workspace_bytes(const tops_gate_act_bwd_params* p) {
+  if (!p || p->fwd.rows < 1 || p->fwd.H < 1 || p->fwd.K < 1) return 0;
+  return elementwise::gate_bwd_workspace_bytes(*p);
+}
+
+extern "C" int tops_b200_gate_act_bwd(const tops_gate_act_bwd_params* p, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
+  if (!p || !p->fwd.g || !p->dy || !p->dg) return TOPS_E_NULL;
+  if (!valid_dtype(p->fwd.dtype) || !valid_dtype(p->dy_dtype)) return TOPS_E_BAD_DTYPE;
+  tops_gate_act_params f = p->fwd;
+  f.out = p->dg;   // (only checked for alignment)
+  int rc = elementwise::gate_check(f);
+  if (rc) return rc;
+  if (!workspace || workspace_bytes < elementwise::gate_bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
+  return elementwise::gate_bwd(*p, workspace, (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_l2norm_fwd(const tops_norm_params* p, void* stream) {
+  if (!p) return TOPS_E_NULL;
+  if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
+  int rc = elementwise::norm_check(*p);
+  return rc ? rc : elementwise::l2norm_fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_l2norm_bwd(const tops_norm_params* p, void* stream) {
+  if (!p) return TOPS_E_NULL;
+  if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
+  tops_norm_params q = *p;
+  q.y = q.dx;
+  int rc = elementwise::norm_check(q);
+  return rc ? rc : elementwise::l2norm_bwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_rmsnorm_gated_fwd(const tops_norm_params* p, void* stream) {
+  if (!p) return TOPS_E_NULL;
+  if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
+  int rc = elementwise::norm_check(*p);
+  return rc ? rc : elementwise::rmsnorm_gated_fwd(*p, (cudaStream_t)stream);
+}
+
+extern "C" size_t tops_b200_rmsnorm_gated_bwd_workspace_bytes(const tops_norm_params* p) {
+  if (!p || p->rows < 1 || p->D < 1) return 0;
+  return elementwise::rmsnorm_gated_bwd_workspace_bytes(*p);
+}
+
+extern "C" int tops_b200_rmsnorm_gated_bwd(const tops_norm_params* p, void* workspace, size_t workspace_bytes,
+                                           void* stream) {
+  if (!p) return TOPS_E_NULL;
+  if (!valid_dtype(p->dtype)) return TOPS_E_BAD_DTYPE;
+  tops_norm_params q = *p;
+  q.y = q.dx;
+  int rc = elementwise::norm_check(q);
+  if (rc) return rc;
+  if (!workspace || workspace_bytes < elementwise::rmsnorm_gated_bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
+  return elementwise::rmsnorm_gated_bwd(*p, workspace, (cudaStream_t)stream);
 }

@@ -99,6 +99,25 @@ class ChunkKdaFwdParams(C.Structure):
                 ("saved_vnew", _vp), ("saved_T", _vp)]
 
 
+_i64 = C.c_int64
+GATE_ACT_KDA, GATE_ACT_KDA_LOWER_BOUND, GATE_ACT_LOG_SIGMOID = 0, 1, 2
+
+
+class GateActParams(C.Structure):
+    _fields_ = [("rows", _i64), ("H", _i32), ("K", _i32), ("kind", _i32), ("dtype", _i32), ("out_dtype", _i32),
+                ("g", _vp), ("A_log", _vp), ("dt_bias", _vp), ("lower_bound", _f32), ("normalizer", _f32),
+                ("clamp_min", _f32), ("has_clamp_min", _i32), ("out", _vp)]
+
+
+class GateActBwdParams(C.Structure):
+    _fields_ = [("fwd", GateActParams), ("dy", _vp), ("dy_dtype", _i32), ("dg", _vp), ("dA_log", _vp), ("dbias", _vp)]
+
+
+class NormParams(C.Structure):
+    _fields_ = [("rows", _i64), ("D", _i32), ("dtype", _i32), ("eps", _f32), ("x", _vp), ("gate", _vp), ("weight", _vp),
+                ("y", _vp), ("rstd", _vp), ("dy", _vp), ("dx", _vp), ("dgate", _vp), ("dweight", _vp)]
+
+
 lib.tops_b200_strerror.restype = C.c_char_p
 lib.tops_b200_strerror.argtypes = [C.c_int]
 lib.tops_b200_launch_count.restype = C.c_int64
@@ -133,6 +152,21 @@ lib.tops_b200_chunk_kda_supported.restype = C.c_int
 lib.tops_b200_chunk_kda_supported.argtypes = [C.POINTER(ChunkKdaFwdParams)]
 lib.tops_b200_chunk_kda_fwd.restype = C.c_int
 lib.tops_b200_chunk_kda_fwd.argtypes = [C.POINTER(ChunkKdaFwdParams), _vp]
+for _name, _ptype, _ws in [
+    ("tops_b200_gate_act_fwd", GateActParams, False),
+    ("tops_b200_gate_act_bwd", GateActBwdParams, True),
+    ("tops_b200_l2norm_fwd", NormParams, False),
+    ("tops_b200_l2norm_bwd", NormParams, False),
+    ("tops_b200_rmsnorm_gated_fwd", NormParams, False),
+    ("tops_b200_rmsnorm_gated_bwd", NormParams, True),
+]:
+    _f = getattr(lib, _name)
+    _f.restype = C.c_int
+    _f.argtypes = [C.POINTER(_ptype), _vp, _sz, _vp] if _ws else [C.POINTER(_ptype), _vp]
+lib.tops_b200_gate_act_bwd_workspace_bytes.restype = _sz
+lib.tops_b200_gate_act_bwd_workspace_bytes.argtypes = [C.POINTER(GateActBwdParams)]
+lib.tops_b200_rmsnorm_gated_bwd_workspace_bytes.restype = _sz
+lib.tops_b200_rmsnorm_gated_bwd_workspace_bytes.argtypes = [C.POINTER(NormParams)]
 lib.tops_b200_chunk_gla_fwd_static.restype = C.c_int
 lib.tops_b200_chunk_gla_fwd_static.argtypes = [C.POINTER(ChunkFwdParams), _vp]
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
