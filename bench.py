@@ -681,6 +681,85 @@ def secondary(name, steps, seq):
     return out
 
 
+def run_time_shard(args):
+    """`--workload simple_gla_long --gpus N`: BASELINE configs[3], ONE sequence of 65536 tokens sharded
+    over time across N ranks.  A step is forward + backward of every shard, with one all-gather of the shard
+    summaries (fp32 [B,H,K,V] + the summed gates) per direction; strong scaling (the sequence is fixed)."""
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=dev)
+    from tops_b200 import _lib as L
+    from tops_b200 import time_shard as TS
+    from tops_b200.synth import make_inputs
+    B, T, H, K, V, C = 1, args.seq or 65536, 32, 128, 128, 64
+    assert T % (world * C) == 0
+    full = make_inputs(4, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
+    sl = slice(rank * T // world, (rank + 1) * T // world)
+    x = {n: (t[:, sl] if t.ndim >= 3 and t.shape[1] == T else t).contiguous().to(dev) for n, t in full.items()}
+    del full
+    scale = K ** -0.5
+    ops = TS.cuda_ops("simple_gla", C)
+    # the exchange alone, timed with its own events inside the step
+    ev = []
+
+    gather = TS._gather
+
+    def timed_gather(t, group):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = gather(t, group)
+        e1.record()
+        ev.append((e0, e1))
+        return out
+    TS._gather = timed_gather
+
+    def step():
+        o, final, h_in = TS.forward(ops, x["q"], x["k"], x["v"], x["g"], scale, x["h0"])
+        return TS.backward(ops, x["q"], x["k"], x["v"], x["g"], scale, h_in, x["do"], x["dht"])
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ev.clear()
+    n0 = L.launch_count()
+    steps = max(3, min(args.steps, 10))
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1) / steps
+    ms_x = sum(a.elapsed_time(b) for a, b in ev) / steps
+    t = torch.tensor([ms, ms_x], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_x = float(t[0]), float(t[1])
+    err = L.device_error()
+    assert err == 0, f"a kernel gave up on a bounded wait (code {err})"
+    hbm_peak, _, peak_kind = measured_peaks()
+    nbytes = B * T * H * 3080
+    if rank == 0:
+        print(json.dumps({
+            "metric": "simple_gla chunk fwd+bwd tokens/s, one sequence sharded over time", "value": B * T / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"simple_gla fwd+bwd B=1 T={T} H=32 K=V=128 chunk 64 bf16, scalar bf16 gate, "
+                                   f"{T // world} tokens per GPU (BASELINE configs[3])",
+                       "exchange": "2 NCCL all-gathers per direction (summed gates, fp32 [B,H,K,V] shard summary), NVLS off"},
+            "exchange_ms_per_step": ms_x, "exchange_share": ms_x / ms,
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak, "unit": "GB/s per GPU",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm_peak, "peak_source": peak_kind},
+            "gpu_launches": int(L.launch_count() - n0), "clocks": clocks.summary(), "device_error": err}), flush=True)
+    dist.destroy_process_group()
+
+
 def run_extra(args):
     """`--workload decode|simple_gla_long|kda`: one JSON line for that workload on one GPU."""
     assert torch.cuda.is_available()
@@ -714,6 +793,8 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "simple_gla_long" and int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        run_time_shard(args)
     elif args.workload != "gla_train":
         run_extra(args)
     else:

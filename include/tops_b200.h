@@ -55,6 +55,9 @@ enum {
 enum { TOPS_IMPL_AUTO = 0, TOPS_IMPL_GENERIC = 1, TOPS_IMPL_SM100 = 2 };
 
 const char* tops_b200_strerror(int code);
+/* Text of the CUDA error behind the most recent TOPS_E_CUDA ("<call>: <cudaGetErrorString> (<code>)"),
+ * copied NUL-terminated into `buf`.  No counterpart in the reference. */
+int tops_b200_last_cuda_error(char* buf, size_t cap);
 /* Number of kernels launched by this library since load (all entry points). */
 int64_t tops_b200_launch_count(void);
 
@@ -335,6 +338,7 @@ int tops_b200_kda_fwd(const tops_kda_fwd_params* p, void* stream);
  *                     the matrices `chunk_kda_fwd` returns;
  *   saved_h     bf16 `[B,NT,H,K,V]`  chunk-start states times exp(mid) per key channel,
  *   saved_vnew  bf16 `[B,T,H,V]`     the delta-corrected values v' = u - w h,
+ *   saved_R     bf16 `[B,T,H,V]`     beta (v - k exp(G) h), the right-hand side of the solve (v' = Akk R),
  *   saved_T     bf16 `[B,T,H,64]`    the inverse above in bf16:
  *               residuals `tops_b200_chunk_kda_bwd` takes back (opaque to callers).
  * ------------------------------------------------------------------------ */
@@ -347,10 +351,39 @@ typedef struct {
   void* o;         /* [B,T,H,V] */
   float* ht;       /* [B,H,K,V] or NULL */
   float *Aqk_out, *Akk_out;
-  void *saved_h, *saved_vnew, *saved_T;
+  void *saved_h, *saved_vnew, *saved_T, *saved_R;
 } tops_chunk_kda_fwd_params;
 int tops_b200_chunk_kda_supported(const tops_chunk_kda_fwd_params* p);
 int tops_b200_chunk_kda_fwd(const tops_chunk_kda_fwd_params* p, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * chunk_kda_bwd — replaces `chunk_kda_bwd` (`tops/cpu/ops/kda/chunk_bwd.py:525-668`;
+ * accelerator kernels `tops/ops/kda/chunk_bwd.py:19-141, 309-351, 457-520`,
+ * `tops/ops/kda/chunk_intra.py:283-574`) for the problems `tops_b200_chunk_kda_fwd` takes.
+ * Its stages are regrouped into three kernels on the tensor cores: the reverse scan of the state
+ * gradient (`chunk_gated_delta_rule_bwd_dhu` together with the dv part of `chunk_kda_bwd_dAv` and of
+ * the WY backward), the gradients of the two per-chunk matrices (dAqk of `chunk_kda_bwd_dAv`, the
+ * inverse's gradient of `prepare_wy_repr_bwd` `tops/cpu/ops/kda/wy_fast.py:96-224`), and the chunk
+ * outputs (`chunk_kda_bwd_wy_dqkg_fused` + `chunk_kda_bwd_intra` + the reverse cumsum of dg).
+ * `saved_*` are the residuals the forward wrote.  dq, dk, dg `[B,T,H,K]` and dbeta `[B,T,H]` in
+ * `grad_dtype` (TOPS_F32 as the reference's orchestrator returns them, or TOPS_BF16); dv bf16;
+ * dg is with respect to the natural-log gate; dh0 fp32 (NULL to skip).
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  int32_t B, T, H, K, V, chunk;
+  int32_t dtype, gate_dtype;
+  float scale;
+  const void *q, *k, *v, *g, *beta;
+  const void* do_;
+  const float* dht; /* [B,H,K,V] or NULL */
+  const void *saved_h, *saved_vnew, *saved_T, *saved_R;
+  void *dq, *dk, *dg, *dbeta;
+  int32_t grad_dtype;
+  void* dv;
+  float* dh0;
+} tops_chunk_kda_bwd_params;
+size_t tops_b200_chunk_kda_bwd_workspace_bytes(const tops_chunk_kda_bwd_params* p);
+int tops_b200_chunk_kda_bwd(const tops_chunk_kda_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * KDA backward — replaces `chunk_kda_bwd` (`tops/cpu/ops/kda/chunk_bwd.py:525-668`)
@@ -371,6 +404,43 @@ typedef struct {
 } tops_kda_bwd_params;
 size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p);
 int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * State exchange of a sequence sharded over time across ranks.  No counterpart
+ * in the reference, which has no multi-device path; it generalises its
+ * `initial_state` / `output_final_state` contract (`tops/cpu/ops/gla/chunk.py:655-656,694-709`,
+ * state-split test `tests/ops/gla/test_pallas_chunk_gla.py:223-247`) to R shards: a shard acts on
+ * the state entering it as h_out = h_in * exp(P) + S.
+ *   pack   the summary S of this rank's shard: the end state from a zero start (reverse = 0:
+ *          x = k, y = v) or the state gradient before the shard for a zero gradient after it
+ *          (reverse = 1: x = q, y = do; x is scaled by pb.scale).  tcgen05 problems only (bf16,
+ *          K = V = 128, chunk 64, per-channel gate `[B,T,H,K]`): TOPS_E_UNSUPPORTED otherwise.
+ *          P, the summed log-gates of the shard `[B,H,K]`, is a plain sum the caller makes.
+ *   apply  after the ranks have all-gathered P `[R,B*H,K]` and S `[R,B*H,K,V]` (fp32): the state
+ *          entering shard `rank` (reverse: the gradient leaving it on its right) from `first`
+ *          (h0 / dht, NULL = zero) in `out_in`, and the value pushed through all R shards (final
+ *          state / dh0) in `out_all` (NULL to skip).  Any K, V with K*V % 4 == 0.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  tops_chunk_problem pb;
+  int32_t reverse;
+  const void *x, *g, *y;
+  float* state_out; /* [B,H,K,V] */
+} tops_state_pack_params;
+size_t tops_b200_chunk_state_exchange_pack_workspace_bytes(const tops_state_pack_params* p);
+int tops_b200_chunk_state_exchange_pack(const tops_state_pack_params* p, void* workspace, size_t workspace_bytes,
+                                        void* stream);
+typedef struct {
+  int32_t R, rank, reverse;
+  int64_t BH;
+  int32_t K, V;
+  const float* first;
+  const float* P;
+  const float* S;
+  float* out_in;
+  float* out_all;
+} tops_state_apply_params;
+int tops_b200_chunk_state_exchange_apply(const tops_state_apply_params* p, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Gate activations — the step before the attention kernels.

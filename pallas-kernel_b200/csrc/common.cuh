@@ -29,9 +29,15 @@ struct KernelScope {
   cudaStream_t st;
 };
 
-inline int post_launch() {
+// The CUDA runtime error behind the most recent TOPS_E_CUDA (read back through tops_b200_last_cuda_error).
+void record_cuda_error(int code, const char* where);
+
+inline int post_launch(const char* where = "kernel launch") {
   count_launch();
-  return cudaGetLastError() == cudaSuccess ? TOPS_OK : TOPS_E_CUDA;
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return TOPS_OK;
+  record_cuda_error((int)e, where);
+  return TOPS_E_CUDA;
 }
 
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }

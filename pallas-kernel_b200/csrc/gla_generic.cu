@@ -760,5 +760,36 @@ int launch_sum_partials(const float* part, size_t stride, int n, float* out, siz
   return post_launch();
 }
 
+// State entering (forward) or state gradient leaving (reverse) time shard `rank` of `R`: the value at the
+// outer end pushed through the shards in between, h <- h * exp(P_s) + S_s, shard by shard in a fixed order.
+//   first [BH,K,V] or null (zero);  P [R,BH,K];  S [R,BH,K,V];  out_in, out_all [BH,K,V] (out_all may be null:
+//   the value pushed through every shard, i.e. the final state / the gradient of the initial state)
+__global__ void k_fold_shards(const float* __restrict__ first, const float* __restrict__ P, const float* __restrict__ S,
+                              float* __restrict__ out_in, float* __restrict__ out_all, int R, int rank, int reverse,
+                              size_t BH, int K, int V) {
+  const size_t n4 = BH * K * V / 4;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 4, bhk = e / V;
+    float4 cur = first ? *reinterpret_cast<const float4*>(first + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < R; ++t) {
+      const int s = reverse ? R - 1 - t : t;
+      if (s == rank) *reinterpret_cast<float4*>(out_in + e) = cur;
+      const float w = __expf(P[(size_t)s * BH * K + bhk]);
+      const float4 add = *reinterpret_cast<const float4*>(S + (size_t)s * BH * K * V + e);
+      cur = make_float4(fmaf(cur.x, w, add.x), fmaf(cur.y, w, add.y), fmaf(cur.z, w, add.z), fmaf(cur.w, w, add.w));
+    }
+    if (out_all) *reinterpret_cast<float4*>(out_all + e) = cur;
+  }
+}
+
+int launch_fold_shards(const float* first, const float* P, const float* S, float* out_in, float* out_all, int R, int rank,
+                       int reverse, size_t BH, int K, int V, cudaStream_t st) {
+  const size_t n4 = BH * K * V / 4;
+  const int grid = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  KernelScope ks("fold_shards", st);
+  k_fold_shards<<<grid, 256, 0, st>>>(first, P, S, out_in, out_all, R, rank, reverse, BH, K, V);
+  return post_launch();
+}
+
 }  // namespace generic
 }  // namespace tops

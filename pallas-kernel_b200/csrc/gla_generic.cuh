@@ -36,6 +36,8 @@ int launch_scan(const Problem& pb, bool bwd, const void* x, const void* y, const
 int launch_fwd_o(const Problem& pb, const void* q, const void* k, const void* v, const void* h, int h_f32,
                  void* o, float* A_out, int round_A, cudaStream_t st);
 int launch_bwd(const Problem& pb, const BwdBuffers& b, cudaStream_t st);
+int launch_fold_shards(const float* first, const float* P, const float* S, float* out_in, float* out_all, int R, int rank,
+                       int reverse, size_t BH, int K, int V, cudaStream_t st);
 int launch_sum_partials(const float* part, size_t stride, int n, float* out, size_t count, cudaStream_t st);
 }  // namespace generic
 }  // namespace tops

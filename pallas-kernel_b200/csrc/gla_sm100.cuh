@@ -13,6 +13,10 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t ws_bytes, cudaStr
 bool bwd_dtypes_ok(const tops_chunk_bwd_params& p);
 size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p);
 int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t ws_bytes, cudaStream_t st);
+// Shard summary for the state exchange of a time-sharded sequence (see tops_b200_chunk_state_exchange_pack).
+size_t summary_workspace_bytes(const tops_chunk_problem& pb);
+int state_summary(const tops_chunk_problem& pb, bool reverse, const void* x, const void* g, const void* y,
+                  float* state_out, void* ws, cudaStream_t st);
 // Reads the device error word (0 = no bounded wait has ever given up).
 int device_error(int* out);
 // Overwrites the device error word (0 clears it).

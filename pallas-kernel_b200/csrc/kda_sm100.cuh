@@ -8,6 +8,9 @@ namespace sm100 {
 // chunk 64, whole chunks, dense batch).
 bool kda_supported(const tops_chunk_kda_fwd_params& p);
 int kda_chunk_fwd(const tops_chunk_kda_fwd_params& p, cudaStream_t st);
+bool kda_bwd_supported(const tops_chunk_kda_bwd_params& p);
+size_t kda_chunk_bwd_workspace_bytes(const tops_chunk_kda_bwd_params& p);
+int kda_chunk_bwd(const tops_chunk_kda_bwd_params& p, void* ws, cudaStream_t st);
 // The error word of the bounded waits in the KDA kernels (same convention as device_error()).
 int kda_device_error(int* out);
 int kda_device_error_set(int code);

@@ -49,7 +49,12 @@ inline int cached_map(CUtensorMap* m, int kind, const void* ptr, uint64_t a, uin
   std::lock_guard<std::mutex> lk(g_map_mu);
   MapSlot& s = g_maps[(slot + (size_t)kind) % kMapSlots];
   if (!(s.used && s.key == key)) {
-    if (encode(&s.map) != CUDA_SUCCESS) { s.used = false; return TOPS_E_CUDA; }
+    const CUresult r = encode(&s.map);
+    if (r != CUDA_SUCCESS) {
+      s.used = false;
+      record_cuda_error(-(int)r, "cuTensorMapEncodeTiled (driver error code negated)");
+      return TOPS_E_CUDA;
+    }
     s.key = key;
     s.used = true;
   }
@@ -62,6 +67,18 @@ inline int act_map(CUtensorMap* m, const void* ptr, int BT, int H) {
   return cached_map(m, 0, ptr, (uint64_t)BT, (uint64_t)H, [&](CUtensorMap* out) {
     cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)H, (cuuint64_t)BT};
     cuuint64_t strides[2] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)H * kHeadDim * 2};
+    cuuint32_t box[3] = {64, 1, 64};
+    cuuint32_t es[3] = {1, 1, 1};
+    return encode_fn()(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
+}
+// [B*T, H, 64] bf16 per-chunk matrices (row i of a chunk at token i): box = 64 columns x 1 head x 64 tokens
+inline int mat_map(CUtensorMap* m, const void* ptr, int BT, int H) {
+  return cached_map(m, 2, ptr, (uint64_t)BT, (uint64_t)H, [&](CUtensorMap* out) {
+    cuuint64_t dims[3] = {64, (cuuint64_t)H, (cuuint64_t)BT};
+    cuuint64_t strides[2] = {64 * 2, (cuuint64_t)H * 64 * 2};
     cuuint32_t box[3] = {64, 1, 64};
     cuuint32_t es[3] = {1, 1, 1};
     return encode_fn()(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
@@ -106,8 +123,10 @@ inline bool device_is_sm100() { return device_info().sm100; }
 
 template <class F>
 inline int opt_in_smem(F f, size_t bytes) {
-  return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess ? TOPS_OK
-                                                                                                         : TOPS_E_CUDA;
+  const cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) return TOPS_OK;
+  record_cuda_error((int)e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+  return TOPS_E_CUDA;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

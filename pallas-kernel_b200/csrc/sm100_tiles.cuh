@@ -114,6 +114,40 @@ __device__ __forceinline__ void build_w_tile(uint8_t* tile) {
   }
 }
 
+// 4 x 4 transpose over the lanes l, l^1, l^2, l^3.  In: v[j] = value of this lane's channel at
+// time t0 + j.  Out: v[j] = value of channel (lane & ~3) + j at time t0 + (lane & 3), so that a
+// thread can store four neighbouring channels of one time step with one instruction.
+__device__ __forceinline__ void transpose4(float (&v)[4], int lane) {
+  const bool odd = lane & 1, hi = lane & 2;
+  const float r0 = __shfl_xor_sync(0xffffffffu, odd ? v[0] : v[1], 1);
+  const float r1 = __shfl_xor_sync(0xffffffffu, odd ? v[2] : v[3], 1);
+  const float a0 = odd ? r0 : v[0], a1 = odd ? v[1] : r0;   // time t0 + odd:     channels 2m, 2m + 1
+  const float b0 = odd ? r1 : v[2], b1 = odd ? v[3] : r1;   // time t0 + 2 + odd: channels 2m, 2m + 1
+  const float u0 = __shfl_xor_sync(0xffffffffu, hi ? a0 : b0, 2);
+  const float u1 = __shfl_xor_sync(0xffffffffu, hi ? a1 : b1, 2);
+  v[0] = hi ? u0 : a0; v[1] = hi ? u1 : a1; v[2] = hi ? b0 : u0; v[3] = hi ? b1 : u1;
+}
+// The same exchange followed by a store of the four neighbouring channels of time step
+// t0 + (lane & 3) at p[i]; the bf16 form rounds after the first stage and moves packed pairs.
+__device__ __forceinline__ void st_transposed4(float* p, size_t i, float (&v)[4], int lane) {
+  transpose4(v, lane);
+  __stcs(reinterpret_cast<float4*>(p + i), make_float4(v[0], v[1], v[2], v[3]));
+}
+__device__ __forceinline__ void st_transposed4(__nv_bfloat16* p, size_t i, const float (&v)[4], int lane) {
+  const bool odd = lane & 1, hi = lane & 2;
+  const float r0 = __shfl_xor_sync(0xffffffffu, odd ? v[0] : v[1], 1);
+  const float r1 = __shfl_xor_sync(0xffffffffu, odd ? v[2] : v[3], 1);
+  const uint32_t pa = odd ? pack_bf16(r0, v[1]) : pack_bf16(v[0], r0);
+  const uint32_t pb = odd ? pack_bf16(r1, v[3]) : pack_bf16(v[2], r1);
+  const uint32_t u = __shfl_xor_sync(0xffffffffu, hi ? pa : pb, 2);
+  __stcs(reinterpret_cast<uint2*>(p + i), hi ? make_uint2(u, pb) : make_uint2(pa, u));
+}
+// gradients are written once and not read again by these kernels: streaming stores
+__device__ __forceinline__ void st_out(float* p, size_t i, float x) { __stcs(p + i, x); }
+__device__ __forceinline__ void st_out(__nv_bfloat16* p, size_t i, float x) {
+  __stcs(reinterpret_cast<unsigned short*>(p) + i, __bfloat16_as_ushort(__float2bfloat16_rn(x)));
+}
+
 }  // namespace
 }  // namespace sm100
 }  // namespace tops

@@ -19,6 +19,13 @@ namespace tops {
 static std::atomic<int64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+static std::mutex g_err_mu;
+static char g_err_text[256] = "";
+void record_cuda_error(int code, const char* where) {
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  snprintf(g_err_text, sizeof g_err_text, "%s: %s (%d)", where, cudaGetErrorString((cudaError_t)code), code);
+}
+
 namespace {
 struct ProfRecord { const char* label; cudaEvent_t start, stop; };
 std::atomic<int> g_prof_on{0};
@@ -138,6 +145,13 @@ extern "C" const char* tops_b200_strerror(int code) {
 }
 
 extern "C" int64_t tops_b200_launch_count(void) { return g_launches.load(); }
+
+extern "C" int tops_b200_last_cuda_error(char* buf, size_t cap) {
+  if (!buf || cap == 0) return TOPS_E_NULL;
+  std::lock_guard<std::mutex> lk(g_err_mu);
+  snprintf(buf, cap, "%s", g_err_text);
+  return TOPS_OK;
+}
 
 extern "C" int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb) {
   if (!pb || check_problem(*pb)) return TOPS_IMPL_GENERIC;
@@ -441,6 +455,23 @@ extern "C" int tops_b200_chunk_kda_fwd(const tops_chunk_kda_fwd_params* p, void*
   return sm100::kda_chunk_fwd(*p, (cudaStream_t)stream);
 }
 
+extern "C" size_t tops_b200_chunk_kda_bwd_workspace_bytes(const tops_chunk_kda_bwd_params* p) {
+  if (!p || p->B < 1 || p->T < 1 || p->H < 1 || !sm100::kda_bwd_supported(*p)) return 0;
+  return sm100::kda_chunk_bwd_workspace_bytes(*p);
+}
+
+extern "C" int tops_b200_chunk_kda_bwd(const tops_chunk_kda_bwd_params* p, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->g || !p->beta || !p->do_ || !p->saved_h || !p->saved_vnew || !p->saved_T ||
+      !p->saved_R || !p->dq || !p->dk || !p->dv || !p->dg || !p->dbeta)
+    return TOPS_E_NULL;
+  if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1) return TOPS_E_BAD_SHAPE;
+  if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype) || !valid_dtype(p->grad_dtype)) return TOPS_E_BAD_DTYPE;
+  if (!sm100::kda_bwd_supported(*p)) return TOPS_E_UNSUPPORTED;
+  if (!workspace || workspace_bytes < sm100::kda_chunk_bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
+  return sm100::kda_chunk_bwd(*p, workspace, (cudaStream_t)stream);
+}
+
 extern "C" size_t tops_b200_kda_bwd_workspace_bytes(const tops_kda_bwd_params* p) {
   return p ? kda::bwd_workspace_bytes(*p) : 0;
 }
@@ -518,4 +549,31 @@ extern "C" int tops_b200_rmsnorm_gated_bwd(const tops_norm_params* p, void* work
   if (rc) return rc;
   if (!workspace || workspace_bytes < elementwise::rmsnorm_gated_bwd_workspace_bytes(*p)) return TOPS_E_WORKSPACE;
   return elementwise::rmsnorm_gated_bwd(*p, workspace, (cudaStream_t)stream);
+}
+
+// ---- state exchange of a time-sharded sequence -------------------------------------
+extern "C" size_t tops_b200_chunk_state_exchange_pack_workspace_bytes(const tops_state_pack_params* p) {
+  if (!p || check_problem(p->pb) || !sm100::supported(p->pb)) return 0;
+  return sm100::summary_workspace_bytes(p->pb);
+}
+
+extern "C" int tops_b200_chunk_state_exchange_pack(const tops_state_pack_params* p, void* workspace, size_t workspace_bytes,
+                                                   void* stream) {
+  if (!p || !p->x || !p->g || !p->y || !p->state_out) return TOPS_E_NULL;
+  int rc = check_problem(p->pb);
+  if (rc) return rc;
+  if (!sm100::supported(p->pb)) return TOPS_E_UNSUPPORTED;
+  if (!workspace || workspace_bytes < sm100::summary_workspace_bytes(p->pb)) return TOPS_E_WORKSPACE;
+  return sm100::state_summary(p->pb, p->reverse != 0, p->x, p->g, p->y, p->state_out, workspace, (cudaStream_t)stream);
+}
+
+extern "C" int tops_b200_chunk_state_exchange_apply(const tops_state_apply_params* p, void* stream) {
+  if (!p || !p->P || !p->S || !p->out_in) return TOPS_E_NULL;
+  if (p->R < 1 || p->rank < 0 || p->rank >= p->R || p->BH < 1 || p->K < 1 || p->V < 1 || (p->V % 4) != 0)
+    return TOPS_E_BAD_SHAPE;
+  const void* ptrs[] = {p->first, p->P, p->S, p->out_in, p->out_all};
+  for (const void* x : ptrs)
+    if (reinterpret_cast<uintptr_t>(x) & 15) return TOPS_E_ALIGN;
+  return generic::launch_fold_shards(p->first, p->P, p->S, p->out_in, p->out_all, p->R, p->rank, p->reverse,
+                                     (size_t)p->BH, p->K, p->V, (cudaStream_t)stream);
 }

@@ -96,7 +96,7 @@ class ChunkKdaFwdParams(C.Structure):
     _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("chunk", _i32), ("dtype", _i32),
                 ("gate_dtype", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("beta", _vp),
                 ("h0", _vp), ("o", _vp), ("ht", _vp), ("Aqk_out", _vp), ("Akk_out", _vp), ("saved_h", _vp),
-                ("saved_vnew", _vp), ("saved_T", _vp)]
+                ("saved_vnew", _vp), ("saved_T", _vp), ("saved_R", _vp)]
 
 
 _i64 = C.c_int64
@@ -116,6 +116,22 @@ class GateActBwdParams(C.Structure):
 class NormParams(C.Structure):
     _fields_ = [("rows", _i64), ("D", _i32), ("dtype", _i32), ("eps", _f32), ("x", _vp), ("gate", _vp), ("weight", _vp),
                 ("y", _vp), ("rstd", _vp), ("dy", _vp), ("dx", _vp), ("dgate", _vp), ("dweight", _vp)]
+
+
+class ChunkKdaBwdParams(C.Structure):
+    _fields_ = [("B", _i32), ("T", _i32), ("H", _i32), ("K", _i32), ("V", _i32), ("chunk", _i32), ("dtype", _i32),
+                ("gate_dtype", _i32), ("scale", _f32), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("beta", _vp),
+                ("do_", _vp), ("dht", _vp), ("saved_h", _vp), ("saved_vnew", _vp), ("saved_T", _vp), ("saved_R", _vp),
+                ("dq", _vp), ("dk", _vp), ("dg", _vp), ("dbeta", _vp), ("grad_dtype", _i32), ("dv", _vp), ("dh0", _vp)]
+
+
+class StatePackParams(C.Structure):
+    _fields_ = [("pb", ChunkProblem), ("reverse", _i32), ("x", _vp), ("g", _vp), ("y", _vp), ("state_out", _vp)]
+
+
+class StateApplyParams(C.Structure):
+    _fields_ = [("R", _i32), ("rank", _i32), ("reverse", _i32), ("BH", _i64), ("K", _i32), ("V", _i32), ("first", _vp),
+                ("P", _vp), ("S", _vp), ("out_in", _vp), ("out_all", _vp)]
 
 
 lib.tops_b200_strerror.restype = C.c_char_p
@@ -167,6 +183,16 @@ lib.tops_b200_gate_act_bwd_workspace_bytes.restype = _sz
 lib.tops_b200_gate_act_bwd_workspace_bytes.argtypes = [C.POINTER(GateActBwdParams)]
 lib.tops_b200_rmsnorm_gated_bwd_workspace_bytes.restype = _sz
 lib.tops_b200_rmsnorm_gated_bwd_workspace_bytes.argtypes = [C.POINTER(NormParams)]
+lib.tops_b200_chunk_kda_bwd.restype = C.c_int
+lib.tops_b200_chunk_kda_bwd.argtypes = [C.POINTER(ChunkKdaBwdParams), _vp, _sz, _vp]
+lib.tops_b200_chunk_kda_bwd_workspace_bytes.restype = _sz
+lib.tops_b200_chunk_kda_bwd_workspace_bytes.argtypes = [C.POINTER(ChunkKdaBwdParams)]
+lib.tops_b200_chunk_state_exchange_pack.restype = C.c_int
+lib.tops_b200_chunk_state_exchange_pack.argtypes = [C.POINTER(StatePackParams), _vp, _sz, _vp]
+lib.tops_b200_chunk_state_exchange_pack_workspace_bytes.restype = _sz
+lib.tops_b200_chunk_state_exchange_pack_workspace_bytes.argtypes = [C.POINTER(StatePackParams)]
+lib.tops_b200_chunk_state_exchange_apply.restype = C.c_int
+lib.tops_b200_chunk_state_exchange_apply.argtypes = [C.POINTER(StateApplyParams), _vp]
 lib.tops_b200_chunk_gla_fwd_static.restype = C.c_int
 lib.tops_b200_chunk_gla_fwd_static.argtypes = [C.POINTER(ChunkFwdParams), _vp]
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
@@ -186,9 +212,19 @@ class TopsError(RuntimeError):
     pass
 
 
+lib.tops_b200_last_cuda_error.restype = C.c_int
+lib.tops_b200_last_cuda_error.argtypes = [C.c_char_p, _sz]
+E_CUDA = -5
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
-        raise TopsError(f"{what}: {lib.tops_b200_strerror(rc).decode()} (code {rc})")
+        detail = ""
+        if rc == E_CUDA:
+            buf = C.create_string_buffer(256)
+            lib.tops_b200_last_cuda_error(buf, len(buf))
+            detail = f" [{buf.value.decode()}]"
+        raise TopsError(f"{what}: {lib.tops_b200_strerror(rc).decode()} (code {rc}){detail}")
 
 
 def ptr(t) -> int | None:

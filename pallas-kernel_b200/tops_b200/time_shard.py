@@ -39,11 +39,14 @@ class LocalOps:
     grad_start(q, do, g, scale) -> D [B,H,K,V] fp32: dh0 of the shard for dht = 0
     fwd(q, k, v, g, scale, h_in) -> (o, h_out)
     bwd(q, k, v, g, scale, h_in, do, dh_out) -> (dq, dk, dv, dg, dh_in)
+    fold(first, decays [R,...], states [R,B,H,K,V], rank, reverse) -> (value entering shard `rank`,
+         value pushed through all shards); None: the torch loops of fold_left / fold_right
     """
     end_state: Callable
     grad_start: Callable
     fwd: Callable
     bwd: Callable
+    fold: Optional[Callable] = None
 
 
 def _acc(t: torch.Tensor) -> torch.Tensor:
@@ -56,10 +59,12 @@ def shard_decay(g: torch.Tensor) -> torch.Tensor:
     return p[..., None, None] if p.ndim == 2 else p[..., None]
 
 
-def _gather(x: torch.Tensor, group) -> list:
+def _gather(x: torch.Tensor, group) -> torch.Tensor:
+    """All-gather into one [R, ...] tensor (one collective; every shard summary lands in local memory)."""
     world = dist.get_world_size(group)
-    out = [torch.empty_like(x) for _ in range(world)]
-    dist.all_gather(out, x.contiguous(), group=group)
+    x = x.contiguous()
+    out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    dist.all_gather(list(out.unbind(0)), x, group=group)   # the views receive in place
     return out
 
 
@@ -87,9 +92,12 @@ def forward(ops: LocalOps, q, k, v, g, scale, initial_state=None, group=None):
     P = shard_decay(g)
     S = _acc(ops.end_state(k, v, g))
     decays, states = _gather(P, group), _gather(S, group)
-    h_in = fold_left(decays, states, initial_state, rank)
+    if ops.fold is not None:
+        h_in, final = ops.fold(initial_state, decays, states, rank, False)
+    else:
+        h_in = fold_left(decays, states, initial_state, rank)
+        final = fold_left(decays, states, initial_state, len(states))
     o, _ = ops.fwd(q, k, v, g, scale, h_in)
-    final = fold_left(decays, states, initial_state, len(states))
     return o, final, h_in
 
 
@@ -101,15 +109,23 @@ def backward(ops: LocalOps, q, k, v, g, scale, h_in, do, dht=None, group=None):
     P = shard_decay(g)
     D = _acc(ops.grad_start(q, do, g, scale))
     decays, grads = _gather(P, group), _gather(D, group)
-    dh_out = fold_right(decays, grads, dht, rank)
+    if ops.fold is not None:
+        dh_out, dh0 = ops.fold(dht, decays, grads, rank, True)
+    else:
+        dh_out = fold_right(decays, grads, dht, rank)
+        dh0 = fold_right(decays, grads, dht, -1)
     dq, dk, dv, dg, _ = ops.bwd(q, k, v, g, scale, h_in, do, dh_out)
-    dh0 = fold_right(decays, grads, dht, -1)
     return dq, dk, dv, dg, dh0
 
 
 def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
     """LocalOps on the CUDA kernels of this package; `kind` is "simple_gla"
-    (g: [B,T,H]) or "gla" (g: [B,T,H,K])."""
+    (g: [B,T,H]) or "gla" (g: [B,T,H,K]).  Shards the tcgen05 kernels take (bf16 q/k/v and gate,
+    K = V = 128, chunk 64, whole chunks) get their summaries from the library's state-exchange entry
+    points (`tops_b200_chunk_state_exchange_pack` / `_apply`); other problems from the generic scans."""
+    import ctypes as C_
+
+    from . import _lib as L
     from .ops import common, gla, simple_gla
     C = chunk_size
 
@@ -117,14 +133,63 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
         gc = common.chunk_local_cumsum(g, C)
         return dict(g=gc) if g.ndim == 3 else dict(gk=gc)
 
+    def per_channel(g, K):
+        return g if g.ndim == 4 else g.unsqueeze(-1).expand(*g.shape, K).contiguous()
+
+    def pack_problem(x, y, g):
+        B, T, H, K = x.shape
+        pb = common.make_problem(B, T, H, K, y.shape[-1], C, L.dtype_code(x.dtype), L.dtype_code(g.dtype),
+                                 L.GATE_PER_CHANNEL, 1.0)
+        ok = (x.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
+              and L.lib.tops_b200_chunk_selected_impl(C_.byref(pb)) == L.IMPL_SM100)
+        return pb if ok else None
+
+    def pack(x, y, g, reverse, scale):
+        """Shard summary through the tcgen05 summary scan; None when the problem is not one it takes."""
+        with torch.cuda.device(x.device):
+            pb = pack_problem(x, y, g)
+            if pb is None:
+                return None
+            pb.scale = float(scale)
+            B, T, H, K = x.shape
+            x, y = x.contiguous(), y.contiguous()
+            gk = per_channel(g, K)
+            out = torch.empty(B, H, K, y.shape[-1], dtype=torch.float32, device=x.device)
+            p = L.StatePackParams()
+            p.pb, p.reverse, p.x, p.g, p.y, p.state_out = pb, int(reverse), L.ptr(x), L.ptr(gk), L.ptr(y), L.ptr(out)
+            ws = L.workspace(L.lib.tops_b200_chunk_state_exchange_pack_workspace_bytes(C_.byref(p)), x.device)
+            L.check(L.lib.tops_b200_chunk_state_exchange_pack(C_.byref(p), ws.data_ptr(), ws.numel(),
+                                                              L.stream_ptr(x.device)), "chunk_state_exchange_pack")
+            return out
+
     def end_state(k, v, g):
+        s = pack(k, v, g, False, 1.0)
+        if s is not None:
+            return s
         _, ht = common.chunk_fwd_h(k, v, **gates(g), output_final_state=True, states_in_fp32=True, chunk_size=C)
         return ht
 
     def grad_start(q, do, g, scale):
+        d = pack(q, do, g, True, scale)
+        if d is not None:
+            return d
         zero = torch.zeros(q.shape[0], q.shape[2], q.shape[3], do.shape[3], dtype=torch.float32, device=q.device)
         _, dh0 = common.chunk_bwd_dh(q, do, **gates(g), h0=zero, dht=None, scale=scale, chunk_size=C)
         return dh0
+
+    def fold(first, decays, states, rank, reverse):
+        R, B, H, K, V = states.shape
+        with torch.cuda.device(states.device):
+            P = decays.float().expand(R, B, H, K, 1).contiguous()
+            S = states.float().contiguous()
+            f = None if first is None else first.float().contiguous()
+            out_in, out_all = torch.empty_like(S[0]), torch.empty_like(S[0])
+            p = L.StateApplyParams()
+            p.R, p.rank, p.reverse, p.BH, p.K, p.V = R, rank, int(reverse), B * H, K, V
+            p.first, p.P, p.S, p.out_in, p.out_all = L.ptr(f), L.ptr(P), L.ptr(S), L.ptr(out_in), L.ptr(out_all)
+            L.check(L.lib.tops_b200_chunk_state_exchange_apply(C_.byref(p), L.stream_ptr(S.device)),
+                    "chunk_state_exchange_apply")
+        return out_in, out_all
 
     if kind == "simple_gla":
         def fwd(q, k, v, g, scale, h_in):
@@ -139,4 +204,4 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
 
         def bwd(q, k, v, g, scale, h_in, do, dh_out):
             return gla.chunk_gla_bwd(q, k, v, g, None, scale, h_in, None, None, do, dh_out, C)
-    return LocalOps(end_state, grad_start, fwd, bwd)
+    return LocalOps(end_state, grad_start, fwd, bwd, fold)

@@ -69,6 +69,8 @@ BWD_SHAPES = [
     (1, 192, 2, 128, 128, 64, torch.float32, True),
     (2, 256, 2, 128, 128, 64, torch.bfloat16, True),
     (1, 130, 2, 64, 96, 64, torch.bfloat16, False),
+    (2, 128, 2, 64, 64, 32, torch.float16, True),
+    (1, 192, 3, 128, 128, 64, torch.float16, False),
 ]
 
 
@@ -271,3 +273,24 @@ def test_bad_arguments_raise_before_launch():
         chunk_gla(x["q"], x["k"], x["v"], x["g"], initial_state=torch.zeros(2, 2, 16, 16, device="cuda"))
     with pytest.raises(AssertionError):
         chunk_gla(x["q"], x["k"], x["v"], x["g"], cu_seqlens=[0, 16, 16, 32])
+
+
+@pytest.mark.parametrize("chunk_size", [8, 128, 256])
+def test_chunk_sizes_beyond_the_kernel_tiles(chunk_size):
+    """Any power of two is a valid chunk_size (tops/ops/common/cumsum.py:506-508; the reference's tests use
+    128): the differentiable ops give the chunk-size independent result, computed with a length the kernels hold."""
+    from tops_b200.ops.gla import chunk_gla
+    from tops_b200.ops.simple_gla import chunk_simple_gla
+    B, T, H, K, V = 1, 256, 2, 64, 64
+    x = _inputs(9, B, T, H, K, V, torch.float32, with_h0=True)
+    c = to_cuda(x)
+    o, ht = chunk_gla(c["q"], c["k"], c["v"], c["g"], initial_state=c["h0"], output_final_state=True, chunk_size=chunk_size)
+    o_ref, ht_ref = O.chunk_gla(x["q"], x["k"], x["v"], x["g"], K ** -0.5, x["h0"], True, chunk_size=64)
+    assert_close("o", o, o_ref, torch.float32)
+    assert_close("ht", ht, ht_ref, torch.float32)
+    gs = c["g"].mean(-1)
+    o2, _ = chunk_simple_gla(c["q"], c["k"], c["v"], g=gs, initial_state=c["h0"], chunk_size=chunk_size)
+    o3, _ = chunk_simple_gla(c["q"], c["k"], c["v"], g=gs, initial_state=c["h0"], chunk_size=64)
+    assert_close("simple_gla o", o2, o3.cpu(), torch.float32)
+    with pytest.raises(AssertionError):
+        chunk_gla(c["q"], c["k"], c["v"], c["g"], chunk_size=48)

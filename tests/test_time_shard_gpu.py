@@ -27,8 +27,9 @@ def _worker(rank, world, port, out):
         from tops_b200 import time_shard as TS
         from tops_b200.synth import make_inputs
         B, T, H, K, V, C = 1, 1024 * world, 4, 128, 128, 64
-        x = make_inputs(61, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True,
-                        gate_dtype=torch.float32)
+        # bf16 gate: every local op (summaries through the state-exchange entry points, forward,
+        # backward) runs on the tcgen05 kernels
+        x = make_inputs(61, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
         scale = K ** -0.5
         sl = slice(rank * T // world, (rank + 1) * T // world)
         c = {n: (t[:, sl] if t.ndim >= 3 and t.shape[1] == T else t).cuda().contiguous() for n, t in x.items()}
@@ -36,6 +37,8 @@ def _worker(rank, world, port, out):
         o, final, h_in = TS.forward(ops, c["q"], c["k"], c["v"], c["g"], scale, c["h0"])
         dq, dk, dv, dg, dh0 = TS.backward(ops, c["q"], c["k"], c["v"], c["g"], scale, h_in, c["do"], c["dht"])
         torch.cuda.synchronize()
+        from tops_b200 import _lib as L
+        assert L.device_error() == 0
         o_ref, ht_ref = OS.chunk_simple_gla(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True, chunk_size=C)
         r = OS.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, x["h0"], x["do"], x["dht"], scale, chunk_size=C)
         errs = {"o": rel_l2(o, o_ref[:, sl]), "ht": rel_l2(final, ht_ref), "dh0": rel_l2(dh0, r[4])}
