@@ -59,5 +59,27 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return OUT
 
 
+def build_jax_shim() -> str | None:
+    """libtops_b200_jax.so: the XLA FFI handlers of jax_ffi/jax_ffi_shim.cc, compiled against
+    jax.ffi.include_dir().  Only where JAX is installed; returns None (and says so) otherwise."""
+    try:
+        import jax  # noqa: F401
+        inc = jax.ffi.include_dir()
+    except Exception as exc:
+        print(f"jax not found ({type(exc).__name__}: {exc}) - the jax.ffi shim is skipped")
+        return None
+    lib = build()
+    out = os.path.join(HERE, "tops_b200", "libtops_b200_jax.so")
+    cmd = [NVCC, "-std=c++17", "-O2", "-shared", "-Xcompiler", "-fPIC", "-I" + inc, "-I" + os.path.join(ROOT, "include"),
+           os.path.join(HERE, "jax_ffi", "jax_ffi_shim.cc"), "-o", out, "-L" + os.path.dirname(lib), "-l:libtops_b200.so",
+           "-Xlinker", "-rpath=$ORIGIN", "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"jax.ffi shim failed to build:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--jax" in sys.argv:
+        print(build_jax_shim())

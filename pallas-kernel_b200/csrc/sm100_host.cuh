@@ -49,6 +49,10 @@ inline int cached_map(CUtensorMap* m, int kind, const void* ptr, uint64_t a, uin
   std::lock_guard<std::mutex> lk(g_map_mu);
   MapSlot& s = g_maps[(slot + (size_t)kind) % kMapSlots];
   if (!(s.used && s.key == key)) {
+    // cuTensorMapEncodeTiled is a driver call and needs a current context on THIS thread; a thread that
+    // has only made context-free runtime calls so far (an autograd worker on its first backward) has none.
+    // Selecting the device it already has current binds the primary context without any other effect.
+    if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return TOPS_E_CUDA; }
     const CUresult r = encode(&s.map);
     if (r != CUDA_SUCCESS) {
       s.used = false;

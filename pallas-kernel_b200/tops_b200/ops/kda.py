@@ -36,15 +36,18 @@ def _check(q, k, v, g, beta, initial_state):
 
 
 @L.on_tensor_device
-def kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state):
-    """One call of tops_b200_kda_fwd.  Returns (o in q.dtype, final state fp32 or None)."""
+def kda_fwd(q, k, v, g, beta, scale, initial_state, output_final_state, state_out=None):
+    """One call of tops_b200_kda_fwd.  Returns (o in q.dtype, final state fp32 or None).  `state_out`
+    may be the initial state itself: every thread reads its part of the state before it writes it."""
     B, T, H, K, V = _check(q, k, v, g, beta, initial_state)
     dev = q.device
     q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
     beta = beta.to(q.dtype).contiguous()
     h0 = None if initial_state is None else initial_state.float().contiguous()
     o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
-    ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    ht = state_out
+    if ht is None and output_final_state:
+        ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
     p = L.KdaFwdParams()
     p.B, p.T, p.H, p.K, p.V = B, T, H, K, V
     p.dtype, p.gate_dtype, p.scale = L.dtype_code(q.dtype), L.dtype_code(g.dtype), float(scale)
@@ -225,6 +228,18 @@ def fused_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output
         scale = K ** -0.5
     o, ht = _KDA.apply(q, k, v, g, beta, initial_state, float(scale), bool(output_final_state), False)
     return o, (ht if output_final_state else None)
+
+
+def fused_recurrent_kda_decode_(q, k, v, g, beta, state, scale=None):
+    """Decode: the tokens of this call (usually one) update `state` `[B,H,K,V]` fp32 IN PLACE and the outputs
+    `[B,T,H,V]` come back in q.dtype (reference, functional form: `tops/cpu/ops/kda/fused_recurrent.py:71-209`)."""
+    B, T, H, K, V = _check(q, k, v, g, beta, state)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    if scale is None:
+        scale = K ** -0.5
+    with torch.no_grad():
+        o, _ = kda_fwd(q, k, v, g, beta, float(scale), state, True, state_out=state)
+    return o
 
 
 def chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False, cu_seqlens=None,

@@ -75,3 +75,22 @@ def test_kda_state_split():
     o2, s2 = fused_recurrent_kda(*bb, None, s1, True)
     assert_close("o", torch.cat([o1, o2], 1), o, torch.float32)
     assert_close("ht", s2, ht, torch.float32)
+
+
+def test_kda_decode_in_place():
+    """One token per call on a state updated in place == one pass of the oracle over the tokens."""
+    from oracle import kda as OK
+    from tops_b200.ops.kda import fused_recurrent_kda_decode_
+    from tops_b200.synth import make_inputs
+    B, T, H, K, V = 3, 24, 2, 128, 128
+    host = make_inputs(91, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_beta=True, l2norm_qk=True)
+    x = {n: t.cuda() for n, t in host.items()}
+    state = x["h0"].clone()
+    ptr = state.data_ptr()
+    outs = [fused_recurrent_kda_decode_(*(x[n][:, t:t + 1].contiguous() for n in ("q", "k", "v", "g", "beta")), state)
+            for t in range(T)]
+    assert state.data_ptr() == ptr
+    o_ref, ht_ref = OK.naive_recurrent_kda(host["q"], host["k"], host["v"], host["g"], host["beta"], None, host["h0"], True)
+    got = torch.cat(outs, 1)
+    assert ((got.float().cpu() - o_ref.float()).norm() / o_ref.float().norm()).item() <= 2e-2
+    assert ((state.cpu() - ht_ref).norm() / ht_ref.norm()).item() <= 2e-2
