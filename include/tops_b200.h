@@ -74,6 +74,11 @@ int tops_b200_device_error(int* out);
  * tests of the error reporting path; no kernel is involved).  Both synchronise with the device. */
 int tops_b200_device_error_reset(void);
 int tops_b200_device_error_set(int code);
+/* Test hook for the bounded waits themselves: the next tcgen05 state-scan launch of this process never
+ * issues the tile load of chunk `chunk` (>= 3) of each block, so the wait for that tile runs out after its
+ * limit (tens of milliseconds), the kernel records code 1, poisons its outputs and returns on its own; the
+ * hook clears itself after that one launch.  Nothing traps or faults.  No counterpart in the reference. */
+int tops_b200_test_skip_load(int chunk);
 
 /* Per-kernel device timing (no counterpart behind the reference's op API; its
  * benchmarks wrap timed loops in jax.profiler traces, `benchmarks/utils.py:71-83`).

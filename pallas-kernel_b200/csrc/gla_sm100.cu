@@ -35,6 +35,7 @@
 // a warp may only touch the 32 tensor-memory lanes (warp & 3) * 32 .. + 31, so
 // the thread owns accumulator row `col` and splits the accumulator columns
 // with the three other warps of its lane quarter by `seg`.
+#include <atomic>
 #include <mutex>
 
 #include "gla_sm100.cuh"
@@ -60,6 +61,8 @@ struct ScanParams {
   int T, H, NT;            // T: tokens per sequence; NT: chunks per block (T / 64 / nseg)
   int nseg;                // time segments per sequence, one block each
   float scale;
+  int skip_xy;             // test hook: the x/y tile load of this chunk is never issued (-1: none), so that the
+                           // bounded wait for it runs out and the kernel leaves through its error path
 };
 
 // One block per (batch, head): 16 compute warps and one driver warp.  The whole K x V state lives in
@@ -235,7 +238,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
         if (pp + 4 < NT) issue_g(pp + 4);          // the stage of chunk pp+1, whose exponent product is complete
         if (pp + 3 < NT) {                         // the x/y stage of chunk pp is free once its state product is done
           if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
-          issue_xy(pp + 3);
+          if (pp + 3 != p.skip_xy) issue_xy(pp + 3);
         }
       }
       __syncwarp();
@@ -1154,6 +1157,8 @@ constexpr size_t BWD_SMEM = 7 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 +
 // instead of a state scan followed by a chunk-parallel output kernel
 constexpr int kFusedMinBlocks = 48;
 
+std::atomic<int> g_test_skip_load{-1};
+
 // One launch of the scan kernel over `nseg` time segments per (batch, head).  states == nullptr keeps
 // no chunk-start states (a summary pass: end states and summed gates only).
 int run_scan(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, const void* g, const void* y,
@@ -1166,6 +1171,7 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, co
   if (states && (rc = state_map(&sp.mst, states, (size_t)pb.B * (pb.T / C) * pb.H * D))) return rc;
   sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final; sp.gsum = gsum;
   sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C / nseg; sp.nseg = nseg; sp.scale = pb.scale;
+  sp.skip_xy = g_test_skip_load.exchange(-1);   // one launch only
   dim3 grid(pb.B * pb.H * nseg);
   if (bwd) {
     if ((rc = opt_in_smem(k_scan<true>, SCAN_SMEM))) return rc;
@@ -1383,6 +1389,8 @@ int device_error(int* out) {
   *out = v;
   return TOPS_OK;
 }
+
+void test_skip_load(int chunk) { g_test_skip_load.store(chunk); }
 
 int device_error_set(int code) {
   return cudaMemcpyToSymbol(g_error, &code, sizeof(int)) == cudaSuccess ? TOPS_OK : TOPS_E_CUDA;

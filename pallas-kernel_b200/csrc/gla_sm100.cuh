@@ -19,6 +19,8 @@ int state_summary(const tops_chunk_problem& pb, bool reverse, const void* x, con
                   float* state_out, void* ws, cudaStream_t st);
 // Reads the device error word (0 = no bounded wait has ever given up).
 int device_error(int* out);
+// Test hook: the next state-scan launch never issues the x/y tile load of chunk `chunk` of each block.
+void test_skip_load(int chunk);
 // Overwrites the device error word (0 clears it).
 int device_error_set(int code);
 }  // namespace sm100

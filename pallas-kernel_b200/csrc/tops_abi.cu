@@ -174,6 +174,11 @@ extern "C" int tops_b200_device_error_set(int code) {
 
 extern "C" int tops_b200_device_error_reset(void) { return tops_b200_device_error_set(0); }
 
+extern "C" int tops_b200_test_skip_load(int chunk) {
+  sm100::test_skip_load(chunk);
+  return TOPS_OK;
+}
+
 extern "C" int tops_b200_profile_enable(int on) {
   g_prof_on.store(on ? 1 : 0);
   return TOPS_OK;

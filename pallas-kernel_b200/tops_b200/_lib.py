@@ -146,6 +146,8 @@ lib.tops_b200_device_error_reset.restype = C.c_int
 lib.tops_b200_device_error_reset.argtypes = []
 lib.tops_b200_device_error_set.restype = C.c_int
 lib.tops_b200_device_error_set.argtypes = [C.c_int]
+lib.tops_b200_test_skip_load.restype = C.c_int
+lib.tops_b200_test_skip_load.argtypes = [C.c_int]
 lib.tops_b200_profile_enable.restype = C.c_int
 lib.tops_b200_profile_enable.argtypes = [C.c_int]
 lib.tops_b200_profile_read.restype = C.c_int

@@ -128,3 +128,33 @@ def test_device_error_word_raises_and_clears():
         L.raise_on_device_error("test")
     assert L.device_error() == 0
     L.raise_on_device_error("test")   # clean word: no exception
+
+
+def test_bounded_wait_runs_out_and_the_kernel_returns_by_itself():
+    """A tile load that is never issued: the state scan's wait for it gives up after its limit, the kernel
+    leaves through its error path (every thread of the block takes the same exit at the same barrier, tensor
+    memory is freed), the error word and a NaN in the final state report it, and the next call is correct."""
+    from tops_b200 import _lib as L
+    from tops_b200.ops._chunk import chunk_fwd_call
+    from tops_b200.synth import make_inputs
+    B, T, H = 1, 256, 1          # one block, four chunks: the scan + chunk-output form of the forward
+    x = to_cuda(make_inputs(31, B, T, H, 128, 128, dtype=torch.bfloat16, with_h0=True))
+    scale = 128 ** -0.5
+    assert L.device_error() == 0
+    L.check(L.lib.tops_b200_test_skip_load(3), "test_skip_load")
+    o, ht, _, _, _ = chunk_fwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, scale, x["h0"], True, 64,
+                                    impl=L.IMPL_SM100)
+    torch.cuda.synchronize()
+    assert L.device_error() == 1
+    assert torch.isnan(ht).any()
+    with pytest.raises(L.TopsError):
+        L.raise_on_device_error("test")
+    assert L.device_error() == 0
+    o2, ht2, _, _, _ = chunk_fwd_call(x["q"], x["k"], x["v"], x["g"], L.GATE_PER_CHANNEL, scale, x["h0"], True, 64,
+                                      impl=L.IMPL_SM100)
+    torch.cuda.synchronize()
+    cpu = {k: v.cpu() for k, v in x.items()}
+    o_ref, ht_ref = O.chunk_gla(cpu["q"], cpu["k"], cpu["v"], cpu["g"], scale, cpu["h0"], True, chunk_size=64)
+    assert_close("o", o2.cpu(), o_ref, torch.bfloat16)
+    assert_close("ht", ht2.cpu(), ht_ref, torch.bfloat16)
+    assert L.device_error() == 0
