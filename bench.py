@@ -522,6 +522,7 @@ def run_b200(args):
                 r = secondary(name, steps=args.steps, seq=0)
                 extra[name] = {"ms": r["ms_per_step"], "value": r["value"], "unit": r["unit"],
                                "algorithmic_bytes": r["algorithmic_bytes"], "frac": r["frac"],
+                               "kernels_ms_per_launch": r["kernels_ms_per_launch"],
                                "workload": r["config"]["workload"]}
             except Exception as exc:
                 extra[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
@@ -627,6 +628,7 @@ def secondary(name, steps, seq):
 
     hbm_peak, _, peak_kind = measured_peaks()
     n0 = L.launch_count()
+    L.lib.tops_b200_profile_enable(1)
     if name == "decode":
         from tops_b200.ops.gla import fused_recurrent_gla_decode_
         B, H, K, V = 128, 32, 128, 128
@@ -670,6 +672,11 @@ def secondary(name, steps, seq):
                "config": {"workload": f"KDA fwd+bwd B=4 T={T} H=32 K=V=128 chunk 64 bf16, one GPU (BASELINE configs[4])"}}
     else:
         raise ValueError(name)
+    L.lib.tops_b200_profile_enable(0)
+    buf = ctypes.create_string_buffer(1 << 16)
+    L.lib.tops_b200_profile_read(buf, len(buf))
+    out["kernels_ms_per_launch"] = {ln.split()[0]: float(ln.split()[2]) / int(ln.split()[1])
+                                    for ln in buf.value.decode().splitlines()}
     out["ms_per_step"] = ms
     out["algorithmic_bytes"] = nbytes
     out["frac"] = nbytes / (ms * 1e-3) / 1e9 / hbm_peak

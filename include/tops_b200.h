@@ -254,6 +254,11 @@ typedef struct {
    * `tops/cpu/ops/gla/chunk.py:551-561`). */
   const void* h_saved;
   int32_t dg_dtype; /* TOPS_F32 (0) or TOPS_BF16, see above */
+  /* tcgen05 path only (TOPS_E_UNSUPPORTED elsewhere): the per-channel gate `[B,T,H,K]` is a scalar gate
+   * `[B,T,H]` replicated over K (simple_gla on the per-channel kernels); dg is then summed over K inside
+   * the kernel and written as fp32 `[B,T,H]` — the scalar gate's gradient
+   * (`tops/cpu/ops/simple_gla/chunk.py:348-412`). */
+  int32_t dg_sum_k;
 } tops_chunk_bwd_params;
 size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);
 int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,

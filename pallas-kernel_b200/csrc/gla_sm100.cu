@@ -320,8 +320,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
 template <bool REVERSE>
 __global__ void k_join_segments(const float* first, const float* P, const float* S, float* start, float* last,
                                 int nseg) {
+  // grid (batch x head, slices): a block chains one slice of the K x V elements of one (batch, head)
   const int bh = blockIdx.x;
-  for (int e = threadIdx.x * 4; e < D * D; e += blockDim.x * 4) {
+  const int span = D * D / gridDim.y;
+  for (int e = blockIdx.y * span + threadIdx.x * 4; e < (blockIdx.y + 1) * span; e += blockDim.x * 4) {
     const int k = e / D;
     float4 cur = first ? *reinterpret_cast<const float4*>(first + (size_t)bh * D * D + e) : make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = 0; i < nseg; ++i) {
@@ -778,8 +780,9 @@ struct BwdParams {
 constexpr int BWD_THREADS = 704;
 constexpr int BWD_EPI_THREADS = 512, BWD_GATE_THREADS = 128;
 
-// TG: type of dq and dk; TD: type of dg
-template <typename TG, typename TD>
+// TG: type of dq and dk; TD: type of dg; SUMK: dg is summed over the key channels inside the kernel and
+// written as fp32 [B,T,H] (a scalar gate replicated over K: its gradient is the sum of the channels')
+template <typename TG, typename TD, bool SUMK>
 __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -801,6 +804,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums
   __shared__ float tails[2][4][D];    // per-segment sum_i dk_inter k
   __shared__ float hdh_s[2][D];       // sum_v h' dh'
+  __shared__ float dgk_s[2][C];       // SUMK: dg of a chunk summed over the channels
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // tensor-memory columns: the exponent tile E_mid is consumed by the gating before A and dA take its place
@@ -837,6 +841,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
     fence_barrier_init();
     abort_flag = 0;
   }
+  if (tid < 2 * C) dgk_s[tid >> 6][tid & 63] = 0.f;
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
   build_tri_tile(mtm, 128, TRI_MID);
   fence_async_smem();
@@ -933,7 +938,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
                         hdh_s[sl][col] / p.scale;
       // (exp(G_n) sum_v h dh = sum_v h' dh' / scale)
       mbar_arrive(&e_done[sl]);   // tensor memory, the q~ / k~ tiles and hdh_s of this chunk are free
-      if (p.dg) {
+      if constexpr (SUMK) {
+        // sum over the 128 channels: the lanes of a warp by shuffles (lane t keeps the total of time step t),
+        // then the four warps that share this segment through shared memory
+        float mine = 0.f;
+#pragma unroll
+        for (int t = 0; t < SEG; ++t) {
+          float w = dgl[t] + cst;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+          if (lane == t) mine = w;
+        }
+        if (lane < SEG) atomicAdd(&dgk_s[sl][seg * SEG + lane], mine);
+        asm volatile("bar.sync 1, %0;" ::"n"(BWD_EPI_THREADS) : "memory");
+        if (tid < C) {
+          reinterpret_cast<float*>(p.dg)[(size_t)(row + tid) * p.H + h] = dgk_s[sl][tid];
+          dgk_s[sl][tid] = 0.f;   // (this slot is used again two chunks on, two barriers later)
+        }
+      } else if (p.dg) {
         // after the accumulators are released: four time steps x four channels change hands inside each
         // group of four lanes, so that every store writes four neighbouring channels of one time step
 #pragma unroll
@@ -1216,8 +1238,9 @@ int segment_starts(bool bwd, const tops_chunk_problem& pb, int nseg, const void*
   int rc = run_scan(bwd, pb, nseg, x, g, y, nullptr, nullptr, sc.ends, sc.gsum, st);
   if (rc) return rc;
   KernelScope ks("sm100_join_segments", st);
-  if (bwd) k_join_segments<true><<<pb.B * pb.H, 512, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
-  else k_join_segments<false><<<pb.B * pb.H, 512, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
+  const dim3 grid(pb.B * pb.H, 16);   // 16 slices of 1024 elements: 256 threads x float4
+  if (bwd) k_join_segments<true><<<grid, 256, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
+  else k_join_segments<false><<<grid, 256, 0, st>>>(first, sc.gsum, sc.ends, sc.starts, last, nseg);
   return post_launch();
 }
 
@@ -1308,13 +1331,13 @@ bool bwd_dtypes_ok(const tops_chunk_bwd_params& p) {
          (p.grad_dtype == TOPS_BF16 && (p.dg_dtype == TOPS_F32 || p.dg_dtype == TOPS_BF16));
 }
 
-template <typename TG, typename TD>
+template <typename TG, typename TD, bool SUMK = false>
 int launch_bwd_main(const BwdParams& bp, cudaStream_t st) {
-  int rc = opt_in_smem(k_bwd_main<TG, TD>, BWD_SMEM);
+  int rc = opt_in_smem(k_bwd_main<TG, TD, SUMK>, BWD_SMEM);
   if (rc) return rc;
   const int grid = bp.total < sm_count() ? bp.total : sm_count();
   KernelScope ks("sm100_bwd_main", st);
-  k_bwd_main<TG, TD><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
+  k_bwd_main<TG, TD, SUMK><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
   return post_launch();
 }
 
@@ -1362,6 +1385,11 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   bp.dq = p.dq; bp.dk = p.dk; bp.dg = p.dg;
   bp.dv = reinterpret_cast<__nv_bfloat16*>(p.dv); bp.T = pb.T; bp.H = pb.H; bp.NT = NT; bp.scale = pb.scale;
   bp.total = NT * pb.B * pb.H;
+  if (p.dg_sum_k) {
+    if (!p.dg || p.dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;
+    return p.grad_dtype == TOPS_F32 ? launch_bwd_main<float, float, true>(bp, st)
+                                    : launch_bwd_main<__nv_bfloat16, float, true>(bp, st);
+  }
   if (p.grad_dtype == TOPS_F32) return launch_bwd_main<float, float>(bp, st);
   if (p.dg_dtype == TOPS_F32) return launch_bwd_main<__nv_bfloat16, float>(bp, st);
   return launch_bwd_main<__nv_bfloat16, __nv_bfloat16>(bp, st);

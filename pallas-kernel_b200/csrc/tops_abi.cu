@@ -386,7 +386,7 @@ extern "C" int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* wor
   if (!workspace || workspace_bytes < tops_b200_chunk_bwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   if (use_sm100(p->pb) && sm100::bwd_dtypes_ok(*p)) return sm100::chunk_bwd(*p, workspace, workspace_bytes, st);
-  if (p->dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;   // the generic kernels write dg in fp32 only
+  if (p->dg_dtype != TOPS_F32 || p->dg_sum_k) return TOPS_E_UNSUPPORTED;   // the generic kernels write fp32 dg per gate element
 
   Problem pb;
   BwdLayout L;

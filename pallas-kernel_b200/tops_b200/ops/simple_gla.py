@@ -67,11 +67,13 @@ def _expand_gate(g, K):
 def _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, want_saved):
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
+    gate_k = None
     if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-        gate, kind = _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL
+        gate = gate_k = _expand_gate(g, q.shape[-1])
+        kind = L.GATE_PER_CHANNEL
     o, ht, _, _, saved = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
                                         _cu(cu_seqlens), want_saved=want_saved)
-    return o, ht, (saved if want_saved else None)
+    return o, ht, ((saved, gate_k) if want_saved else None)
 
 
 def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
@@ -83,19 +85,19 @@ def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final
 
 
 def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chunk_size=64, cu_seqlens=None,
-                         h_saved=None):
+                         h_saved=None, gate_k=None):
     """Backward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:668-788`).
     Returns (dq, dk in the input dtype, dv in do.dtype, dg fp32 `[B,T,H]` or
     None, dh0 fp32 or None).  `h_saved`: the chunk-start states the tcgen05
-    forward kept (None recomputes them, as the reference does)."""
+    forward kept (None recomputes them, as the reference does); `gate_k`: the gate replicated over K
+    that forward made (None makes it again)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
     if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-        # dq, dk leave the kernel in bf16; the per-channel gate gradient stays fp32 for the sum over K
-        dq, dk, dv, dgk, dh0 = chunk_bwd_call(q, k, v, _expand_gate(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale,
-                                              initial_state, do, dht, chunk_size, q.dtype, True,
-                                              initial_state is not None, h_saved=h_saved)
-        return dq, dk, dv, dgk.sum(-1), dh0
+        # dq, dk leave the kernel in bf16; the gate gradient is summed over K inside the kernel (fp32 [B,T,H])
+        gk = _expand_gate(g, q.shape[-1]) if gate_k is None else gate_k
+        return chunk_bwd_call(q, k, v, gk, L.GATE_PER_CHANNEL, scale, initial_state, do, dht, chunk_size, q.dtype, True,
+                              initial_state is not None, h_saved=h_saved, dg_sum_k=True)
     return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
                           g is not None, initial_state is not None, _cu(cu_seqlens))
 
@@ -104,16 +106,17 @@ class _ChunkSimpleGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, g_gamma, initial_state, scale, output_final_state, cu, chunk_size):
         keep = any(t is not None and t.requires_grad for t in (q, k, v, g, initial_state))
-        o, ht, hs = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu, keep)
-        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state, hs)
+        o, ht, kept = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu, keep)
+        hs, gate_k = kept if kept is not None else (None, None)
+        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state, hs, gate_k)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, g_gamma, h0, hs = ctx.saved_tensors
+        q, k, v, g, g_gamma, h0, hs, gate_k = ctx.saved_tensors
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(q, k, v, g, g_gamma, h0, do.to(q.dtype), dht, ctx.scale, ctx.chunk,
-                                                   ctx.cu, h_saved=hs)
+                                                   ctx.cu, h_saved=hs, gate_k=gate_k)
         # a constant decay gets a zero cotangent, as in the reference (tops/ops/simple_gla/chunk.py:764)
         if L.CHECK_DEVICE:
             L.raise_on_device_error("chunk_simple_gla backward")
