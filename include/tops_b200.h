@@ -182,6 +182,10 @@ typedef struct {
    * hand it to tops_b200_chunk_gla_bwd as `h_saved` only when
    * tops_b200_chunk_selected_impl reports TOPS_IMPL_SM100 for the problem. */
   void* saved_out;
+  /* Optional (tcgen05 path, few (batch, head) pairs): the workspace a `tops_b200_chunk_state_exchange_pack`
+   * call (reverse = 0) on this same problem left behind.  It holds the time segments' summaries, so the
+   * forward skips its own summary scan and only chains the segments from `h0`.  NULL otherwise. */
+  void* segments;
 } tops_chunk_fwd_params;
 /* Which kernel family TOPS_IMPL_AUTO resolves to for this problem on the current device. */
 int tops_b200_chunk_selected_impl(const tops_chunk_problem* pb);
@@ -259,6 +263,9 @@ typedef struct {
    * the kernel and written as fp32 `[B,T,H]` — the scalar gate's gradient
    * (`tops/cpu/ops/simple_gla/chunk.py:348-412`). */
   int32_t dg_sum_k;
+  /* The same for the reverse scan: the workspace of a `tops_b200_chunk_state_exchange_pack` call with
+   * reverse = 1 (x = q, y = do, the same scale) on this problem.  NULL otherwise. */
+  void* rev_segments;
 } tops_chunk_bwd_params;
 size_t tops_b200_chunk_bwd_workspace_bytes(const tops_chunk_bwd_params* p);
 int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* workspace, size_t workspace_bytes,
@@ -426,6 +433,9 @@ int tops_b200_kda_bwd(const tops_kda_bwd_params* p, void* workspace, size_t work
  *          (reverse = 1: x = q, y = do; x is scaled by pb.scale).  tcgen05 problems only (bf16,
  *          K = V = 128, chunk 64, per-channel gate `[B,T,H,K]`): TOPS_E_UNSUPPORTED otherwise.
  *          P, the summed log-gates of the shard `[B,H,K]`, is a plain sum the caller makes.
+ *          The workspace keeps the summaries of the time segments the scan was cut into: handed to the
+ *          forward (`segments`) / backward (`rev_segments`) call of the same shard it saves their own
+ *          summary scan, so a shard is scanned twice per direction, as on a single GPU.
  *   apply  after the ranks have all-gathered P `[R,B*H,K]` and S `[R,B*H,K,V]` (fp32): the state
  *          entering shard `rank` (reverse: the gradient leaving it on its right) from `first`
  *          (h0 / dht, NULL = zero) in `out_in`, and the value pushed through all R shards (final

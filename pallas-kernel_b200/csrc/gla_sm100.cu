@@ -1233,9 +1233,11 @@ struct SegmentScratch {
 };
 // summary pass + join: leaves the state entering every segment in sc.starts and the state after the last
 // (forward) / before the first (reverse) segment in `last` (may be null)
+// With `have_summary` the scratch already holds the segments' end states and summed gates (a shard summary
+// made by state_summary() for the same problem) and only the join runs.
 int segment_starts(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, const void* g, const void* y,
-                   const float* first, float* last, const SegmentScratch& sc, cudaStream_t st) {
-  int rc = run_scan(bwd, pb, nseg, x, g, y, nullptr, nullptr, sc.ends, sc.gsum, st);
+                   const float* first, float* last, const SegmentScratch& sc, cudaStream_t st, bool have_summary = false) {
+  int rc = have_summary ? TOPS_OK : run_scan(bwd, pb, nseg, x, g, y, nullptr, nullptr, sc.ends, sc.gsum, st);
   if (rc) return rc;
   KernelScope ks("sm100_join_segments", st);
   const dim3 grid(pb.B * pb.H, 16);   // 16 slices of 1024 elements: 256 threads x float4
@@ -1281,12 +1283,15 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
   char* wsp = reinterpret_cast<char*>(ws);
   void* h = p.saved_out ? p.saved_out : wsp;
   const bool fused = fwd_is_fused(pb, nseg);
-  const SegmentScratch sc(reinterpret_cast<float*>(wsp + ((p.saved_out || fused) ? 0 : state_bytes(pb))), pb, nseg);
+  if (!aligned16(p.segments)) return TOPS_E_ALIGN;
+  const SegmentScratch sc(p.segments ? reinterpret_cast<float*>(p.segments)
+                                     : reinterpret_cast<float*>(wsp + ((p.saved_out || fused) ? 0 : state_bytes(pb))),
+                          pb, nseg);
   int rc;
   const float* start = p.h0;
   float* last = p.ht;
   if (nseg > 1) {
-    if ((rc = segment_starts(false, pb, nseg, p.k, p.g, p.v, p.h0, p.ht, sc, st))) return rc;
+    if ((rc = segment_starts(false, pb, nseg, p.k, p.g, p.v, p.h0, p.ht, sc, st, p.segments != nullptr))) return rc;
     start = sc.starts;
     last = nullptr;   // the join kernel has written the final state
   }
@@ -1346,7 +1351,7 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   if (!bwd_dtypes_ok(p)) return TOPS_E_UNSUPPORTED;
   if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.g) || !aligned16(p.do_) ||
       !aligned16(p.h0) || !aligned16(p.dht) || !aligned16(p.dh0) || !aligned16(p.dq) || !aligned16(p.dk) ||
-      !aligned16(p.dv) || !aligned16(p.dg) || !aligned16(p.h_saved) || !aligned16(ws))
+      !aligned16(p.dv) || !aligned16(p.dg) || !aligned16(p.h_saved) || !aligned16(p.rev_segments) || !aligned16(ws))
     return TOPS_E_ALIGN;
   // workspace: [dh'] [h' unless the forward kept it] [segment scratch]
   const int nseg = pick_segments(pb);
@@ -1368,8 +1373,9 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
     const float* start = p.dht;
     float* last = p.dh0;
     if (nseg > 1) {
-      if ((rc = segment_starts(true, pb, nseg, p.q, p.g, p.do_, p.dht, p.dh0, sc, st))) return rc;
-      start = sc.starts;
+      const SegmentScratch rsc(p.rev_segments ? reinterpret_cast<float*>(p.rev_segments) : sc.ends, pb, nseg);
+      if ((rc = segment_starts(true, pb, nseg, p.q, p.g, p.do_, p.dht, p.dh0, rsc, st, p.rev_segments != nullptr))) return rc;
+      start = rsc.starts;
       last = nullptr;   // the join kernel has written dh0
     }
     if ((rc = run_scan(true, pb, nseg, p.q, p.g, p.do_, start, dh, last, nullptr, st))) return rc;

@@ -12,11 +12,12 @@ from .common import make_problem, total_chunks
 
 @L.on_tensor_device
 def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqlens=None,
-                   want_gcum=False, want_A=False, want_h=False, impl=L.IMPL_AUTO, want_saved=False):
+                   want_gcum=False, want_A=False, want_h=False, impl=L.IMPL_AUTO, want_saved=False, segments=None):
     """Run tops_b200_chunk_gla_fwd.  Returns (o, ht, g_cumsum, A, h); the last
     three are None unless asked for.  With `want_saved` the fifth value is
     instead the opaque scratch the tcgen05 forward keeps for its backward
-    (None when another kernel family runs): pass it to chunk_bwd_call as `h_saved`."""
+    (None when another kernel family runs): pass it to chunk_bwd_call as `h_saved`.  `segments`: the
+    workspace of a state-exchange pack call on the same problem (time sharding), see the C header."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     dev = q.device
@@ -45,6 +46,8 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
             and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100:
         hs = torch.empty(B, nch // B, H, K, V, dtype=k.dtype, device=dev)
         p.saved_out = L.ptr(hs)
+    if segments is not None and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100:
+        p.segments = L.ptr(segments)
     ws = L.workspace(L.lib.tops_b200_chunk_fwd_workspace_bytes(C.byref(p)), dev)
     L.check(L.lib.tops_b200_chunk_gla_fwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)),
             "chunk_gla_fwd")
@@ -53,7 +56,8 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
 
 @L.on_tensor_device
 def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dtype, want_dg, want_dh0,
-                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False, dg_sum_k=False):
+                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False, dg_sum_k=False,
+                   rev_segments=None):
     """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0).  `h_saved`
     is the scratch returned by chunk_fwd_call(want_saved=True) on the same inputs.
     With `primal_dtypes` the gradients come back in the dtypes of their primals
@@ -101,6 +105,8 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
     if h_saved is not None:
         assert h_saved.dtype == q.dtype and h_saved.shape[-3:] == (H, K, V)
         p.h_saved = L.ptr(h_saved)
+    if rev_segments is not None and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100:
+        p.rev_segments = L.ptr(rev_segments)
     ws = L.workspace(L.lib.tops_b200_chunk_bwd_workspace_bytes(C.byref(p)), dev)
     L.check(L.lib.tops_b200_chunk_gla_bwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)),
             "chunk_gla_bwd")

@@ -126,7 +126,7 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
     import ctypes as C_
 
     from . import _lib as L
-    from .ops import common, gla, simple_gla
+    from .ops import _chunk, common, gla, simple_gla
     C = chunk_size
 
     def gates(g):
@@ -144,6 +144,19 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
               and L.lib.tops_b200_chunk_selected_impl(C_.byref(pb)) == L.IMPL_SM100)
         return pb if ok else None
 
+    # What one shard's calls share: the gate replicated over K (scalar gates) and the workspaces the two
+    # pack calls leave behind (the time segments' summaries), which the forward / backward of the same
+    # shard take back so that they do not scan the shard a third time.
+    kept = {}
+
+    def gate_k(g, K):
+        if g.ndim == 4:
+            return g
+        if kept.get("g") is not g:
+            kept.clear()
+            kept["g"], kept["gk"] = g, per_channel(g, K)
+        return kept["gk"]
+
     def pack(x, y, g, reverse, scale):
         """Shard summary through the tcgen05 summary scan; None when the problem is not one it takes."""
         with torch.cuda.device(x.device):
@@ -153,14 +166,19 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
             pb.scale = float(scale)
             B, T, H, K = x.shape
             x, y = x.contiguous(), y.contiguous()
-            gk = per_channel(g, K)
+            gk = gate_k(g, K)
             out = torch.empty(B, H, K, y.shape[-1], dtype=torch.float32, device=x.device)
             p = L.StatePackParams()
             p.pb, p.reverse, p.x, p.g, p.y, p.state_out = pb, int(reverse), L.ptr(x), L.ptr(gk), L.ptr(y), L.ptr(out)
             ws = L.workspace(L.lib.tops_b200_chunk_state_exchange_pack_workspace_bytes(C_.byref(p)), x.device)
             L.check(L.lib.tops_b200_chunk_state_exchange_pack(C_.byref(p), ws.data_ptr(), ws.numel(),
                                                               L.stream_ptr(x.device)), "chunk_state_exchange_pack")
+            kept["rev" if reverse else "fwd"] = (x.data_ptr(), ws)
             return out
+
+    def segments(which, x):
+        ent = kept.get(which)
+        return ent[1] if ent is not None and ent[0] == x.data_ptr() else None
 
     def end_state(k, v, g):
         s = pack(k, v, g, False, 1.0)
@@ -191,17 +209,41 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
                     "chunk_state_exchange_apply")
         return out_in, out_all
 
+    def fast(q, v, g):
+        return pack_problem(q, v, g) is not None
+
     if kind == "simple_gla":
         def fwd(q, k, v, g, scale, h_in):
+            if fast(q, v, g):   # the per-channel tcgen05 kernels on the replicated gate, segment summaries reused
+                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, gate_k(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale, h_in,
+                                                        True, C, want_saved=True, segments=segments("fwd", k))
+                kept["hs"] = (q.data_ptr(), hs)
+                return o, ht
             return simple_gla.chunk_simple_gla_fwd(q, k, v, g, None, scale, h_in, True, C)
 
         def bwd(q, k, v, g, scale, h_in, do, dh_out):
+            if fast(q, v, g):
+                hs = kept.get("hs")
+                hs = hs[1] if hs is not None and hs[0] == q.data_ptr() else None
+                return _chunk.chunk_bwd_call(q, k, v, gate_k(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale, h_in, do, dh_out,
+                                             C, q.dtype, True, True, h_saved=hs, dg_sum_k=True,
+                                             rev_segments=segments("rev", q))
             return simple_gla.chunk_simple_gla_bwd(q, k, v, g, None, h_in, do, dh_out, scale, C)
     else:
         def fwd(q, k, v, g, scale, h_in):
+            if fast(q, v, g):
+                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, g, L.GATE_PER_CHANNEL, scale, h_in, True, C,
+                                                        want_saved=True, segments=segments("fwd", k))
+                kept["hs"] = (q.data_ptr(), hs)
+                return o, ht
             o, ht = gla.chunk_gla(q, k, v, g, scale=scale, initial_state=h_in, output_final_state=True, chunk_size=C)
             return o, ht
 
         def bwd(q, k, v, g, scale, h_in, do, dh_out):
+            if fast(q, v, g):
+                hs = kept.get("hs")
+                hs = hs[1] if hs is not None and hs[0] == q.data_ptr() else None
+                return _chunk.chunk_bwd_call(q, k, v, g, L.GATE_PER_CHANNEL, scale, h_in, do, dh_out, C, torch.float32,
+                                             True, True, h_saved=hs, rev_segments=segments("rev", q))
             return gla.chunk_gla_bwd(q, k, v, g, None, scale, h_in, None, None, do, dh_out, C)
     return LocalOps(end_state, grad_start, fwd, bwd, fold)
