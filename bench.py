@@ -608,6 +608,14 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def simple_gla_bytes(B, T, H, K, V):
+    """Every API tensor of a simple_gla forward + backward once (bf16 activations, bf16 scalar gate, fp32 gate
+    gradient, fp32 states): q, k, v, g in, o out; q, k, v, g, do in, dq, dk, dv, dg out; h0, ht, dht, dh0.
+    Scratch (chunk-start states, segment summaries) is not counted."""
+    per_token_head = (2 * 2 * K + 2 * V + 2 + 2 * V) + (2 * 2 * K + 2 * 2 * V + 2 + 2 * 2 * K + 2 * V + 4)
+    return B * T * H * per_token_head + 4 * B * H * K * V * 4
+
+
 def secondary(name, steps, seq):
     """One secondary workload (BASELINE configs[2..4]) on the current GPU, device-resident, through
     the public ops.  Returns a dict with ms_per_step, value, unit, algorithmic_bytes, frac, config."""
@@ -651,7 +659,7 @@ def secondary(name, steps, seq):
                                      chunk_size=64)
             return torch.autograd.grad((o, ht), leaves, (x["do"], x["dht"]))
         ms = timed(step, max(3, min(steps, 10)), 3)
-        nbytes = B * T * H * 3080
+        nbytes = simple_gla_bytes(B, T, H, K, V)
         out = {"metric": "simple_gla chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s",
                "config": {"workload": f"simple_gla fwd+bwd B=1 T={T} H=32 K=V=128 chunk 64 bf16, scalar bf16 gate, one GPU "
                                       "(BASELINE configs[3] without the time sharding)"}}
@@ -667,7 +675,9 @@ def secondary(name, steps, seq):
                               chunk_size=64)
             return torch.autograd.grad((o, ht), leaves, (x["do"], x["dht"]))
         ms = timed(step, max(2, min(steps, 5)), 2)
-        nbytes = B * T * H * 4360
+        # q, k, v, g, beta in, o out; q, k, v, g, beta, do in, dq, dk, dv, dg, dbeta out; h0, ht, dht, dh0
+        nbytes = B * T * H * (4 * 2 * K + 2 + 2 * V) + B * T * H * (4 * 2 * K + 2 + 2 * V + 3 * 2 * K + 2 * V + 2) \
+            + 4 * B * H * K * V * 4
         out = {"metric": "KDA chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s",
                "config": {"workload": f"KDA fwd+bwd B=4 T={T} H=32 K=V=128 chunk 64 bf16, one GPU (BASELINE configs[4])"}}
     else:
@@ -751,7 +761,7 @@ def run_time_shard(args):
     err = L.device_error()
     assert err == 0, f"a kernel gave up on a bounded wait (code {err})"
     hbm_peak, _, peak_kind = measured_peaks()
-    nbytes = B * T * H * 3080
+    nbytes = simple_gla_bytes(B, T, H, K, V)
     if rank == 0:
         print(json.dumps({
             "metric": "simple_gla chunk fwd+bwd tokens/s, one sequence sharded over time", "value": B * T / (ms * 1e-3),

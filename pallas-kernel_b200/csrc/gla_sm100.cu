@@ -61,6 +61,7 @@ struct ScanParams {
   int T, H, NT;            // T: tokens per sequence; NT: chunks per block (T / 64 / nseg)
   int nseg;                // time segments per sequence, one block each
   float scale;
+  const __nv_bfloat16* gscalar;   // scalar gates [B,T,H] (SCALAR kernels; mg is unused then)
   int skip_xy;             // test hook: the x/y tile load of this chunk is never issued (-1: none), so that the
                            // bounded wait for it runs out and the kernel leaves through its error path
 };
@@ -84,7 +85,10 @@ struct ScanShared {
   float gn[2][D], e0[2][D];   // row 63 (G_n) and row 0 of the exponent tile, per channel
 };
 
-template <bool BWD>
+// SCALAR: one gate per head and time step (simple_gla).  No gate tile is fetched and no exponent product is
+// issued: every compute warp keeps the 64 gates of the next chunk in registers and cumulates them with
+// shuffles (warp_cumulate), so a thread gates its 16 channels of x with one factor.
+template <bool BWD, bool SCALAR>
 __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ ScanParams p) {
   // every shared object is carved from the dynamic allocation, whose start is 1024-byte aligned when the
   // kernel has no static shared memory (checked below: the swizzled tiles need that alignment)
@@ -130,14 +134,30 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     for (int i = 0; i < 3; ++i) { mbar_init(&sh.fullg[i], 1); mbar_init(&sh.fullxy[i], 1); }
     mbar_init(&sh.ebar[0], 1); mbar_init(&sh.ebar[1], 1); mbar_init(&sh.sbar[0], 1); mbar_init(&sh.sbar[1], 1);
     fence_barrier_init();
-    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.my);
+    tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.my);
+    if (!SCALAR) tma_prefetch_desc(&p.mg);
     if (p.states) tma_prefetch_desc(&p.mst);
     sh.abort_flag = 0;
-    for (int c = 0; c < 3 && c < NT; ++c) { issue_g(c); issue_xy(c); }
+    for (int c = 0; c < 3 && c < NT; ++c) {
+      if (!SCALAR) issue_g(c);
+      issue_xy(c);
+    }
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
-  build_tri_tile(mt, 128, BWD ? TRI_INCL : TRI_REVN);
+  // SCALAR: the gates of time steps lane and lane + 32 of the next chunk to be gated
+  // (kept as loaded: the conversion, the first use of the loaded value, comes a chunk later)
+  __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
+  auto load_gates = [&](int c) {
+    const __nv_bfloat16* src = p.gscalar + (size_t)(chunk_row(c) + lane) * p.H + h;
+    greg_lo = src[0];
+    greg_hi = src[(size_t)32 * p.H];
+  };
+  if (SCALAR) {
+    if (!driver) load_gates(0);
+  } else {
+    build_tri_tile(mt, 128, BWD ? TRI_INCL : TRI_REVN);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -147,9 +167,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
 
   // exponents E = pattern . g of chunk pp: [time (repeated to 128 lanes)][channel]; row 63 is G_n
   auto issue_gate_mma = [&](int pp) {
+    if (SCALAR) return;
     if (!mbar_wait(&sh.fullg[pp % 3], (pp / 3) & 1)) { *abort_flag = 1; fail(1); }
     tc_fence_after();
-    const uint32_t ga = smem_u32(gs + (pp % 3) * TILE64), ma = smem_u32(mt);
+    const uint32_t ga = smem_u32(gs + (pp % 3) * TILE64);
+    const uint32_t ma = smem_u32(mt);
 #pragma unroll
     for (int j0 = 0; j0 < C; j0 += 16)
       umma_bf16(tm + cE + (pp & 1) * 128, desc_kmajor(ma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0),
@@ -166,14 +188,33 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     umma_commit(&sh.sbar[pp & 1]);
   };
   // gate x of chunk pp in place and publish G_n (and G_n - G_0, or G_0) of its channels
+  // (SCALAR: they are the same for every channel and stay in the registers gn_next, e0_next of every thread)
+  float gn_next = 0.f, e0_next = 0.f;
   auto gate_chunk = [&](int pp) {
-    if (!mbar_wait(&sh.ebar[pp & 1], (pp >> 1) & 1) || !mbar_wait(&sh.fullxy[pp % 3], (pp / 3) & 1)) {
+    if ((!SCALAR && !mbar_wait(&sh.ebar[pp & 1], (pp >> 1) & 1)) || !mbar_wait(&sh.fullxy[pp % 3], (pp / 3) & 1)) {
       *abort_flag = 1;
       fail(1);
     }
     tc_fence_after();
     const int i = (q4 * 32 + lane) & 63;          // time row of this thread
     const int cg = (q4 >> 1) * 4 + seg;           // its 16 channels
+    if (SCALAR) {
+      const WarpGates w = warp_cumulate(__bfloat162float(greg_lo), __bfloat162float(greg_hi), lane);
+      const float Gi = (q4 & 1) ? w.hi : w.lo;
+      gn_next = w.gn;
+      e0_next = BWD ? w.g0 : w.gn - w.g0;
+      const float f = BWD ? fast_exp(Gi) * p.scale : fast_exp(w.gn - Gi);
+      uint8_t* xt = xs + (pp % 3) * TILE64;
+      const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+        *reinterpret_cast<uint4*>(xt + off) = scale8_by(*reinterpret_cast<const uint4*>(xt + off), f);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      return;
+    }
     float e[16];
     tmem_ld16(tmem_addr(tm, lane_base, cE + (pp & 1) * 128 + cg * 16), e);
     if (i == 63) {
@@ -202,8 +243,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
   };
   // forward states are stored as h * exp(mid) * scale, mid = (G_0 + G_n) / 2 = G_n - (G_n - G_0) / 2;
   // reverse states as dh * exp(G_n - mid) = dh * exp((G_n - G_0) / 2)
+  auto gn_of = [&](int pp) { return SCALAR ? gn_next : sh.gn[pp & 1][col]; };   // (SCALAR: of the chunk gated last)
   auto state_scale = [&](int pp) {
-    const float gnv = sh.gn[pp & 1][col], e0 = sh.e0[pp & 1][col];
+    const float gnv = gn_of(pp), e0 = SCALAR ? e0_next : sh.e0[pp & 1][col];
     return BWD ? fast_exp(0.5f * (gnv - e0)) : fast_exp(gnv - 0.5f * e0) * p.scale;
   };
 
@@ -217,7 +259,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     if (ok && lane == 0) {
       issue_state_mma(0);
       if (NT > 2) issue_gate_mma(2);
-      if (NT > 3) issue_g(3);    // into the stage of chunk 0, whose exponent product is complete
+      if (!SCALAR && NT > 3) issue_g(3);    // into the stage of chunk 0, whose exponent product is complete
     }
     for (int pp = 0; ok && pp < NT; ++pp) {
       // the store of chunk pp-1 has read its staging tile: after the barrier the compute warps may
@@ -235,7 +277,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
           tma_store_commit();
         }
         if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
-        if (pp + 4 < NT) issue_g(pp + 4);          // the stage of chunk pp+1, whose exponent product is complete
+        if (!SCALAR && pp + 4 < NT) issue_g(pp + 4);   // the stage of chunk pp+1, whose exponent product is complete
         if (pp + 3 < NT) {                         // the x/y stage of chunk pp is free once its state product is done
           if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
           if (pp + 3 != p.skip_xy) issue_xy(pp + 3);
@@ -258,16 +300,18 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     }
     float gtot = 0.f;   // summed log-gates of this thread's channel over the block's chunks
     gate_chunk(0);
+    if (SCALAR && NT > 1) load_gates(1);
     bool ok = !__syncthreads_or(*abort_flag);
-    float decay = 1.f, hscale = 1.f;
+    float decay = 1.f, hscale = 1.f, gn_cur = 0.f;   // of the chunk whose state product comes next
     if (ok) {
-      decay = fast_exp(sh.gn[0][col]);
+      gn_cur = gn_of(0);
+      decay = fast_exp(gn_cur);
       hscale = state_scale(0);
     }
     for (int pp = 0; ok && pp < NT; ++pp) {
       // the state this chunk starts from (bf16), in the form its consumers use: staged in shared
       // memory in the tile format of the states tensor map and written out by a TMA store
-      gtot += sh.gn[pp & 1][col];   // (published by the gating of this chunk, one iteration ago)
+      gtot += gn_cur;   // (published by the gating of this chunk, one iteration ago)
       if (keep_states) {
         uint8_t* tile = hst + (pp & 1) * TILE128;
 #pragma unroll
@@ -279,11 +323,14 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       }
       if (pp + 1 < NT) gate_chunk(pp + 1);
       if (__syncthreads_or(*abort_flag)) { ok = false; break; }
-      float decay_n = 1.f, hscale_n = 1.f;
+      float decay_n = 1.f, hscale_n = 1.f, gn_n = 0.f;
       if (pp + 1 < NT) {
-        decay_n = fast_exp(sh.gn[(pp + 1) & 1][col]);
+        gn_n = gn_of(pp + 1);
+        decay_n = fast_exp(gn_n);
         hscale_n = state_scale(pp + 1);
       }
+      // (the gates of the chunk gated in the next iteration: fetched where the thread waits anyway)
+      if (SCALAR && pp + 2 < NT) load_gates(pp + 2);
       if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
       tc_fence_after();
       {
@@ -295,6 +342,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       tc_fence_before();
       decay = decay_n;
       hscale = hscale_n;
+      gn_cur = gn_n;
     }
     if (ok && p.s_final) {
       float* dst = p.s_final + ((size_t)blk * D + col) * D + seg * 32;
@@ -343,11 +391,14 @@ __global__ void k_join_segments(const float* first, const float* P, const float*
 // ===========================================================================
 struct FwdOParams {
   CUtensorMap mq, mk, mg, mv, mh;
+  const __nv_bfloat16* gscalar;   // scalar gates [B,T,H] (SCALAR kernel; mg is unused then)
   __nv_bfloat16* o;
   int T, H, NT;
   float scale;
 };
 
+// SCALAR: no gate tile and no exponent product; every warp cumulates the chunk's 64 gates in registers.
+template <bool SCALAR>
 __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ FwdOParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -370,8 +421,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   if (tid == 0) {
     mbar_init(&bar_load, 1); mbar_init(&bar_e, 1); mbar_init(&bar_a, 1); mbar_init(&bar_o, 1);
     fence_barrier_init();
-    mbar_expect_tx(&bar_load, 4 * TILE64 + TILE128);
-    tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row);
+    mbar_expect_tx(&bar_load, (SCALAR ? 3 : 4) * TILE64 + TILE128);
+    if (!SCALAR) { tma_load_3d(gs, &p.mg, &bar_load, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_load, 64, h, row); }
     tma_load_3d(qs, &p.mq, &bar_load, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_load, 64, h, row);
     tma_load_3d(ks, &p.mk, &bar_load, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_load, 64, h, row);
     tma_load_3d(vs, &p.mv, &bar_load, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &bar_load, 64, h, row);
@@ -380,7 +431,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
-  build_tri_tile(mt, 64, TRI_MID);
+  __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;   // SCALAR: the gates of time steps lane and lane + 32
+  if (SCALAR) {
+    const __nv_bfloat16* src = p.gscalar + (size_t)(row + lane) * p.H + h;
+    greg_lo = src[0];
+    greg_hi = src[(size_t)32 * p.H];
+  } else {
+    build_tri_tile(mt, 64, TRI_MID);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -389,7 +447,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   const uint32_t lane_base = q4 * 32;
   bool ok = __syncthreads_and(mbar_wait(&bar_load, 0));
   if (!ok) fail(3);
-  if (ok && tid == 0) {
+  if (!SCALAR && ok && tid == 0) {
     tc_fence_after();
     const uint32_t ga = smem_u32(gs), ma = smem_u32(mt);
 #pragma unroll
@@ -398,11 +456,30 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
     umma_commit(&bar_e);
   }
   __syncwarp();
-  if (ok) {
+  if (!SCALAR && ok) {
     ok = __syncthreads_and(mbar_wait(&bar_e, 0));
     if (!ok) fail(9);
   }
-  if (ok) {
+  if (SCALAR && ok) {
+    // thread (q4, lane < 16, seg) gates 32 channels of time row 16 q4 + lane, whose cumulative gate sits in
+    // lane (16 q4 + lane) mod 32 of the warp
+    const WarpGates w = warp_cumulate(__bfloat162float(greg_lo), __bfloat162float(greg_hi), lane);
+    const int i = 16 * q4 + (lane & 15);
+    const float E = __shfl_sync(0xffffffffu, (q4 >> 1) ? w.hi : w.lo, i & 31) - w.mid();
+    const float f = fast_exp(E), r = fast_exp(-E);
+    if (lane < 16) {
+      const uint32_t rowoff = (uint32_t)(seg >> 1) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t off = rowoff + (((uint32_t)((seg & 1) * 4 + u) ^ (uint32_t)i) & 7u) * 16u;
+        *reinterpret_cast<uint4*>(qs + off) = scale8_by(*reinterpret_cast<const uint4*>(qs + off), f);
+        *reinterpret_cast<uint4*>(ks + off) = scale8_by(*reinterpret_cast<const uint4*>(ks + off), r);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+  }
+  if (!SCALAR && ok) {
     tc_fence_after();
     float e[32];
     tmem_ld32(tmem_addr(tm, lane_base, cE + seg * 32), e);
@@ -502,6 +579,7 @@ struct FusedParams {
   __nv_bfloat16* states;   // h' [B,T/64,H,K,V] or null
   float* s_final;          // state each block ends with: [B,H,nseg,K,V] or null
   __nv_bfloat16* o;        // [B,T,H,V]
+  const __nv_bfloat16* gscalar;   // scalar gates [B,T,H] (SCALAR kernel; mg is unused then)
   int T, H, NT;            // T: tokens per sequence; NT: chunks per block (T / 64 / nseg)
   int nseg;                // time segments per sequence, one block each
   float scale;
@@ -514,6 +592,9 @@ struct FusedShared {
 constexpr uint32_t FUSED_STAGE = 4 * TILE64;   // q, k, g, v
 constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 + TILE64 + sizeof(FusedShared);
 
+// SCALAR: no gate tile is fetched and no exponent product issued; every compute warp cumulates the chunk's 64
+// gates in registers (warp_cumulate), which gives its threads E of their time row, G_n and mid directly.
+template <bool SCALAR>
 __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constant__ FusedParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* in = smem;                         // 2 stages x (q, k, g, v)
@@ -539,8 +620,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
     uint8_t *ks = qs + TILE64, *gs = ks + TILE64, *vs = gs + TILE64;
     uint64_t* bar = &sh.fullin[pp & 1];
     const int row = b * p.T + (c0 + pp) * C;
-    mbar_expect_tx(bar, FUSED_STAGE);
-    tma_load_3d(gs, &p.mg, bar, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, bar, 64, h, row);
+    mbar_expect_tx(bar, SCALAR ? 3 * TILE64 : FUSED_STAGE);
+    if (!SCALAR) { tma_load_3d(gs, &p.mg, bar, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, bar, 64, h, row); }
     tma_load_3d(qs, &p.mq, bar, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, bar, 64, h, row);
     tma_load_3d(ks, &p.mk, bar, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, bar, 64, h, row);
     tma_load_3d(vs, &p.mv, bar, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, bar, 64, h, row);
@@ -549,15 +630,28 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
     mbar_init(&sh.fullin[0], 1); mbar_init(&sh.fullin[1], 1);
     mbar_init(&sh.ebar, 1); mbar_init(&sh.abar, 1); mbar_init(&sh.sbar, 1); mbar_init(&sh.obar, 1);
     fence_barrier_init();
-    tma_prefetch_desc(&p.mq); tma_prefetch_desc(&p.mk); tma_prefetch_desc(&p.mg); tma_prefetch_desc(&p.mv);
+    tma_prefetch_desc(&p.mq); tma_prefetch_desc(&p.mk); tma_prefetch_desc(&p.mv);
+    if (!SCALAR) tma_prefetch_desc(&p.mg);
     sh.abort_flag = 0;
     issue_load(0);
     if (NT > 1) issue_load(1);
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
-  build_tri_tile(mt, 128, TRI_MID);
-  build_w_tile(wt);
+  // SCALAR: the gates of time steps lane and lane + 32 of the next chunk
+  // (kept as loaded: the conversion, the first use of the loaded value, comes a chunk later)
+  __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
+  auto load_gates = [&](int c) {
+    const __nv_bfloat16* src = p.gscalar + (size_t)(b * p.T + (c0 + c) * C + lane) * p.H + h;
+    greg_lo = src[0];
+    greg_hi = src[(size_t)32 * p.H];
+  };
+  if (SCALAR) {
+    if (!driver) load_gates(0);
+  } else {
+    build_tri_tile(mt, 128, TRI_MID);
+    build_w_tile(wt);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -568,6 +662,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
   if (driver) {
     // ------------------------------------------------------------------ products and copies
     auto issue_exponents = [&](int pp) {
+      if (SCALAR) return;
       if (!mbar_wait(&sh.fullin[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(3); }
       tc_fence_after();
       const uint32_t ga = smem_u32(in + (pp & 1) * FUSED_STAGE + 2 * TILE64), ma = smem_u32(mt), wa = smem_u32(wt);
@@ -663,13 +758,22 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       uint8_t* qs = in + (pp & 1) * FUSED_STAGE;
       uint8_t *ks = qs + TILE64, *gs = ks + TILE64;
       uint8_t* ht = hst + (pp & 1) * TILE128;
-      if (!mbar_wait(&sh.fullin[pp & 1], (pp >> 1) & 1) || !mbar_wait(&sh.ebar, ph)) { *abort_flag = 1; fail(9); }
+      if (!mbar_wait(&sh.fullin[pp & 1], (pp >> 1) & 1) || (!SCALAR && !mbar_wait(&sh.ebar, ph))) { *abort_flag = 1; fail(9); }
       tc_fence_after();
+      WarpGates wg;
+      if (SCALAR) {
+        wg = warp_cumulate(__bfloat162float(greg_lo), __bfloat162float(greg_hi), lane);
+      }
       // per-channel factors of this thread's state row
       float decay, c2;
       {
         float w[8];
-        tmem_ld8(tmem_addr(tm, lane_base, cW), w);
+        if (SCALAR) {
+          w[0] = wg.gn;
+          w[1] = wg.gn - wg.mid();
+        } else {
+          tmem_ld8(tmem_addr(tm, lane_base, cW), w);
+        }
         decay = fast_exp(w[0]);                    // exp(G_n)
         c2 = fast_exp(w[1]);                       // exp(G_n - mid)
         const float hscale = fast_exp(w[0] - w[1]) * p.scale;   // exp(mid) scale
@@ -680,7 +784,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
                          pack_bf16(S[j + 4] * hscale, S[j + 5] * hscale), pack_bf16(S[j + 6] * hscale, S[j + 7] * hscale));
       }
       // gate q, k: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
-      {
+      if (SCALAR) {
+        const int i = (q4 * 32 + lane) & 63;
+        const int cg = (q4 >> 1) * 4 + seg;
+        const float E = ((q4 & 1) ? wg.hi : wg.lo) - wg.mid();
+        const float f = fast_exp(E), r = fast_exp(-E);
+        const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+          *reinterpret_cast<uint4*>(qs + off) = scale8_by(*reinterpret_cast<const uint4*>(qs + off), f);
+          *reinterpret_cast<uint4*>(ks + off) = scale8_by(*reinterpret_cast<const uint4*>(ks + off), r);
+        }
+      } else {
         const int i = (q4 * 32 + lane) & 63;
         const int cg = (q4 >> 1) * 4 + seg;
         float em[16];
@@ -703,6 +819,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       tc_fence_before();
       if (__syncthreads_or(*abort_flag)) { ok = false; break; }   // B1
       if (pp > 0) copy_out(pp - 1);   // staged before the barrier; the products of this chunk run meanwhile
+      if (SCALAR && pp + 1 < NT) load_gates(pp + 1);   // the next chunk's gates, fetched where the thread waits anyway
       // tril(A) scale -> bf16 operand in the (dead) gate tile
       if (!mbar_wait(&sh.abar, ph)) { *abort_flag = 1; fail(4); }
       tc_fence_after();
@@ -766,6 +883,7 @@ struct BwdParams {
   CUtensorMap mq, mk, mg, mv, mdo, mh, mdh;
   void *dq, *dk, *dg;    // [B,T,H,K] fp32 or bf16 (dg may be null)
   __nv_bfloat16* dv;     // [B,T,H,V]
+  const __nv_bfloat16* gscalar;   // scalar gates [B,T,H] (SCALAR kernels; mg is unused then)
   int T, H, NT, total;   // total = B * H * NT chunks
   float scale;
 };
@@ -781,8 +899,11 @@ constexpr int BWD_THREADS = 704;
 constexpr int BWD_EPI_THREADS = 512, BWD_GATE_THREADS = 128;
 
 // TG: type of dq and dk; TD: type of dg; SUMK: dg is summed over the key channels inside the kernel and
-// written as fp32 [B,T,H] (a scalar gate replicated over K: its gradient is the sum of the channels')
-template <typename TG, typename TD, bool SUMK>
+// written as fp32 [B,T,H] (a scalar gate replicated over K: its gradient is the sum of the channels').
+// SCALAR (with SUMK): the gate is one value per head and time step; no gate tile is fetched and no exponent
+// product issued: every write-out warp cumulates the 64 gates of a chunk in registers (warp_cumulate) and
+// hands the factors exp(+-(G - mid)) of the time steps around by shuffles.
+template <typename TG, typename TD, bool SUMK, bool SCALAR>
 __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -832,7 +953,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   };
 
   if (tid == 0) {
-    mbar_init(&full_g, 1); mbar_init(&full_qk[0], 1); mbar_init(&full_qk[1], 1); mbar_init(&full_hdo, 1);
+    mbar_init(&full_g, 1);
+    mbar_init(&full_qk[0], 1); mbar_init(&full_qk[1], 1); mbar_init(&full_hdo, 1);
     mbar_init(&full_dhv, 1); mbar_init(&bar_gate, 1); mbar_init(&bar_A, 1); mbar_init(&bar_r1, 1); mbar_init(&bar_r2, 1);
     mbar_init(&bar_main, 1);
     mbar_init(&gated, BWD_EPI_THREADS); mbar_init(&conv_done, BWD_GATE_THREADS);
@@ -843,7 +965,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   }
   if (tid < 2 * C) dgk_s[tid >> 6][tid & 63] = 0.f;
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
-  build_tri_tile(mtm, 128, TRI_MID);
+  if (!SCALAR) build_tri_tile(mtm, 128, TRI_MID);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -861,12 +983,46 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
     TD* const dg_out = reinterpret_cast<TD*>(p.dg);
     // q -> q exp(G - mid), k -> k exp(mid - G) in place: thread (q4, lane, seg) owns time row
     // (32 q4 + lane) mod 64 and 16 channels
+    // SCALAR: the gates of time steps lane and lane + 32 of the next chunk to be gated, and the factors
+    // exp(G - mid), exp(mid - G) of time step (16 seg + lane) mod 32 + 32 (seg / 2) of the chunk gated last
+    __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
+    float fw_next = 1.f, rw_next = 1.f;
+    auto load_gates = [&](int it) {
+      int h, row, hrow;
+      chunk_rows(it, h, row, hrow);
+      const __nv_bfloat16* src = p.gscalar + (size_t)(row + lane) * p.H + h;
+      greg_lo = src[0];
+      greg_hi = src[(size_t)32 * p.H];
+    };
+    if (SCALAR && nit > 0) load_gates(0);
     auto gate_chunk = [&](int it) -> bool {
       const int sl = it & 1;
-      if (!wait(&bar_gate, it & 1, 9) || !wait(&full_qk[sl], (it >> 1) & 1, 6)) return false;
+      bool landed = (SCALAR || wait(&bar_gate, it & 1, 9)) && wait(&full_qk[sl], (it >> 1) & 1, 6);
+      if (SCALAR) landed = __all_sync(0xffffffffu, landed);   // (shuffles follow: the whole warp takes one path)
+      if (!landed) return false;
       tc_fence_after();
       const int i = (q4 * 32 + lane) & 63;
       const int cg = (q4 >> 1) * 4 + seg;
+      if (SCALAR) {
+        const WarpGates w = warp_cumulate(__bfloat162float(greg_lo), __bfloat162float(greg_hi), lane);
+        const float mid = w.mid();
+        const float f_lo = fast_exp(w.lo - mid), r_lo = fast_exp(mid - w.lo);
+        const float f_hi = fast_exp(w.hi - mid), r_hi = fast_exp(mid - w.hi);
+        fw_next = (seg >> 1) ? f_hi : f_lo;
+        rw_next = (seg >> 1) ? r_hi : r_lo;
+        const float f = (q4 & 1) ? f_hi : f_lo, r = (q4 & 1) ? r_hi : r_lo;
+        const uint32_t rowoff = (uint32_t)sl * TILE64 + (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+          *reinterpret_cast<uint4*>(qs + off) = scale8_by(*reinterpret_cast<const uint4*>(qs + off), f);
+          *reinterpret_cast<uint4*>(ks + off) = scale8_by(*reinterpret_cast<const uint4*>(ks + off), r);
+        }
+        fence_async_smem();
+        tc_fence_before();
+        mbar_arrive(&gated);
+        return true;
+      }
       float em[16];
       tmem_ld16(tmem_addr(tm, lane_base, cEm + cg * 16), em);
       const uint32_t rowoff = (uint32_t)sl * TILE64 + (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
@@ -887,14 +1043,19 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       mbar_arrive(&gated);
       return true;
     };
-    bool live = gate_chunk(0);
+    bool live = nit > 0 && gate_chunk(0);
+    if (SCALAR && nit > 1) load_gates(1);
     for (int it = 0; live && it < nit; ++it) {
       const int sl = it & 1;
       int h, row, hrow;
       chunk_rows(it, h, row, hrow);
+      const float fw = fw_next, rw = rw_next;   // (SCALAR) of this chunk
       // the next chunk's gating runs while the tensor core works on this chunk's gradient products
       if (it + 1 < nit && !gate_chunk(it + 1)) break;
-      if (!wait(&bar_main, it & 1, 8) || !wait(&hdh_done[sl], (it >> 1) & 1, 11)) break;
+      if (SCALAR && it + 2 < nit) load_gates(it + 2);   // fetched where the thread waits anyway
+      bool done = wait(&bar_main, it & 1, 8) && wait(&hdh_done[sl], (it >> 1) & 1, 11);
+      if (SUMK) done = __all_sync(0xffffffffu, done);   // (shuffles follow: the whole warp takes one path)
+      if (!done) break;
       tc_fence_after();
       const uint8_t* qt = qs + sl * TILE64;
       const uint8_t* kt = ks + sl * TILE64;
@@ -904,9 +1065,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       float run = 0.f, tail = 0.f;
 #pragma unroll
       for (int blk = 1; blk >= 0; --blk) {
-        float et[8], dq[8], dk1[8], dk2[8], dv[8];
+        float et[8] = {}, dq[8], dk1[8], dk2[8], dv[8];
         const uint32_t c0 = seg * SEG + blk * 8;
-        tmem_ld8(tmem_addr(tm, lane_base, cET + 64 * sl + c0), et);
+        if (!SCALAR) tmem_ld8(tmem_addr(tm, lane_base, cET + 64 * sl + c0), et);
         tmem_ld8(tmem_addr(tm, lane_base, cdq + c0), dq);
         tmem_ld8(tmem_addr(tm, lane_base, cdk1 + c0), dk1);
         tmem_ld8(tmem_addr(tm, lane_base, cdk2 + c0), dk2);
@@ -916,7 +1077,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
           const int t = blk * 8 + u;
           const uint32_t off = ca.at(seg * SEG + t);
           const float qv = ld_bf16(qt, off), kv = ld_bf16(kt, off);   // q~, k~
-          const float e = fast_exp(et[u]), r = fast_exp(-et[u]);
+          // exp(G - mid), exp(mid - G) of time step 16 seg + t
+          const float e = SCALAR ? __shfl_sync(0xffffffffu, fw, (seg * SEG + t) & 31) : fast_exp(et[u]);
+          const float r = SCALAR ? __shfl_sync(0xffffffffu, rw, (seg * SEG + t) & 31) : fast_exp(-et[u]);
           const float dqs = dq[u];                        // dq exp(mid - G)
           const float dki = dk2[u];                       // dk_inter exp(G - mid)
           const float dks = dk1[u] + dki;                 // dk exp(G - mid)
@@ -952,7 +1115,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         if (lane < SEG) atomicAdd(&dgk_s[sl][seg * SEG + lane], mine);
         asm volatile("bar.sync 1, %0;" ::"n"(BWD_EPI_THREADS) : "memory");
         if (tid < C) {
-          reinterpret_cast<float*>(p.dg)[(size_t)(row + tid) * p.H + h] = dgk_s[sl][tid];
+          if (p.dg) reinterpret_cast<float*>(p.dg)[(size_t)(row + tid) * p.H + h] = dgk_s[sl][tid];
           dgk_s[sl][tid] = 0.f;   // (this slot is used again two chunks on, two barriers later)
         }
       } else if (p.dg) {
@@ -1064,10 +1227,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
           umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
         umma_commit(&bar_main);
       };
-      bool ok = wait(&full_g, 0, 6);
+      bool ok = SCALAR || wait(&full_g, 0, 6);
       if (ok) {
         tc_fence_after();
-        issue_gate(0);
+        if (!SCALAR) issue_gate(0);
         ok = wait(&gated, 0, 12);
       }
       if (ok) {
@@ -1084,7 +1247,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         if (!wait(&conv_done, it & 1, 13)) break;   // A and dA of this chunk are in shared memory
         tc_fence_after();
         const bool more = it + 1 < nit;
-        if (more) {   // the next chunk's exponents take the place of A and dA in tensor memory
+        if (more && !SCALAR) {   // the next chunk's exponents take the place of A and dA in tensor memory
           if (!wait(&full_g, (it + 1) & 1, 6)) break;
           issue_gate(it + 1);
         }
@@ -1131,15 +1294,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         tma_load_3d(vs, &p.mv, &full_dhv, 0, h, row); tma_load_3d(vs + SLAB64, &p.mv, &full_dhv, 64, h, row);
         tma_load_2d(dhs, &p.mdh, &full_dhv, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &full_dhv, 64, hrow);
       };
-      load_g(0);
+      if (!SCALAR) load_g(0);
       load_qk(0);
       load_hdo(0);
       load_dhv(0);
       bool ok = true;
       if (nit > 1) {
         load_qk(1);
-        ok = wait(&bar_gate, 0, 9);   // the exponent products of chunk 0 have read its gates
-        if (ok) load_g(1);
+        if (!SCALAR) {
+          ok = wait(&bar_gate, 0, 9);   // the exponent products of chunk 0 have read its gates
+          if (ok) load_g(1);
+        }
       }
       for (int it = 0; ok && it + 1 < nit; ++it) {
         // dh' and v are dead after the first group of products (and the h' dh' reduction), h' and do
@@ -1151,8 +1316,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
         if (it + 2 < nit) {
           if (!wait(&e_done[it & 1], (it >> 1) & 1, 14)) break;
           load_qk(it + 2);
-          if (!wait(&bar_gate, (it + 1) & 1, 9)) break;
-          load_g(it + 2);
+          if (!SCALAR) {
+            if (!wait(&bar_gate, (it + 1) & 1, 9)) break;
+            load_g(it + 2);
+          }
         }
       }
     }
@@ -1187,24 +1354,28 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, co
              const float* s0, void* states, float* s_final, float* gsum, cudaStream_t st) {
   ScanParams sp;
   const int BT = pb.B * pb.T;
+  const bool scalar = pb.gate_kind == TOPS_GATE_SCALAR;
   int rc;
-  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.mg, g, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H)))
-    return rc;
+  if ((rc = act_map(&sp.mx, x, BT, pb.H)) || (rc = act_map(&sp.my, y, BT, pb.H))) return rc;
+  if (!scalar && (rc = act_map(&sp.mg, g, BT, pb.H))) return rc;
+  sp.gscalar = reinterpret_cast<const __nv_bfloat16*>(g);
   if (states && (rc = state_map(&sp.mst, states, (size_t)pb.B * (pb.T / C) * pb.H * D))) return rc;
   sp.s0 = s0; sp.states = reinterpret_cast<__nv_bfloat16*>(states); sp.s_final = s_final; sp.gsum = gsum;
   sp.T = pb.T; sp.H = pb.H; sp.NT = pb.T / C / nseg; sp.nseg = nseg; sp.scale = pb.scale;
   sp.skip_xy = g_test_skip_load.exchange(-1);   // one launch only
   dim3 grid(pb.B * pb.H * nseg);
-  if (bwd) {
-    if ((rc = opt_in_smem(k_scan<true>, SCAN_SMEM))) return rc;
-    KernelScope ks(states ? "sm100_bwd_dh" : "sm100_bwd_dh_summary", st);
-    k_scan<true><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
+  auto launch = [&](auto kernel, const char* label) {
+    if ((rc = opt_in_smem(kernel, SCAN_SMEM))) return rc;
+    KernelScope ks(label, st);
+    kernel<<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
     return post_launch();
+  };
+  if (bwd) {
+    const char* label = states ? "sm100_bwd_dh" : "sm100_bwd_dh_summary";
+    return scalar ? launch(k_scan<true, true>, label) : launch(k_scan<true, false>, label);
   }
-  if ((rc = opt_in_smem(k_scan<false>, SCAN_SMEM))) return rc;
-  KernelScope ks(states ? "sm100_fwd_h" : "sm100_fwd_h_summary", st);
-  k_scan<false><<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
-  return post_launch();
+  const char* label = states ? "sm100_fwd_h" : "sm100_fwd_h_summary";
+  return scalar ? launch(k_scan<false, true>, label) : launch(k_scan<false, false>, label);
 }
 
 // Time segments per sequence.  The scans walk a sequence chunk by chunk with one block; when there are
@@ -1249,7 +1420,8 @@ int segment_starts(bool bwd, const tops_chunk_problem& pb, int nseg, const void*
 }  // namespace
 
 bool supported(const tops_chunk_problem& pb) {
-  if (pb.dtype != TOPS_BF16 || pb.gate_dtype != TOPS_BF16 || pb.gate_kind != TOPS_GATE_PER_CHANNEL) return false;
+  if (pb.dtype != TOPS_BF16 || pb.gate_dtype != TOPS_BF16) return false;
+  if (pb.gate_kind != TOPS_GATE_PER_CHANNEL && pb.gate_kind != TOPS_GATE_SCALAR) return false;
   if (pb.K != D || pb.V != D || pb.chunk != C || pb.T % C != 0 || pb.cu_seqlens) return false;
   if (!(pb.scale > 0.f) || !(pb.scale < 1e30f)) return false;   // states are stored multiplied by scale
   if ((size_t)pb.B * pb.T >= (1u << 31)) return false;
@@ -1279,6 +1451,7 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
     return TOPS_E_ALIGN;
   const int BT = pb.B * pb.T, NT = pb.T / C;
   const int nseg = pick_segments(pb);
+  const bool scalar = pb.gate_kind == TOPS_GATE_SCALAR;
   // workspace: [chunk-start states unless the caller keeps them] [segment scratch]
   char* wsp = reinterpret_cast<char*>(ws);
   void* h = p.saved_out ? p.saved_out : wsp;
@@ -1299,8 +1472,10 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
     // enough blocks to fill the GPU with one per (batch, head, segment): one pass over q, k, g, v
     FusedParams up;
     if ((rc = act_map(&up.mq, p.q, BT, pb.H)) || (rc = act_map(&up.mk, p.k, BT, pb.H)) ||
-        (rc = act_map(&up.mg, p.g, BT, pb.H)) || (rc = act_map(&up.mv, p.v, BT, pb.H)))
+        (rc = act_map(&up.mv, p.v, BT, pb.H)))
       return rc;
+    if (!scalar && (rc = act_map(&up.mg, p.g, BT, pb.H))) return rc;
+    up.gscalar = reinterpret_cast<const __nv_bfloat16*>(p.g);
     up.states = nullptr;
     if (p.saved_out) {   // only a caller that keeps the states for its backward pass needs them in HBM
       if ((rc = state_map(&up.mst, p.saved_out, (size_t)pb.B * NT * pb.H * D))) return rc;
@@ -1308,22 +1483,25 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
     }
     up.s0 = start; up.s_final = last; up.o = reinterpret_cast<__nv_bfloat16*>(p.o);
     up.T = pb.T; up.H = pb.H; up.NT = NT / nseg; up.nseg = nseg; up.scale = pb.scale;
-    if ((rc = opt_in_smem(k_fwd_fused, FUSED_SMEM))) return rc;
+    if ((rc = opt_in_smem(k_fwd_fused<true>, FUSED_SMEM)) || (rc = opt_in_smem(k_fwd_fused<false>, FUSED_SMEM))) return rc;
     KernelScope ks("sm100_fwd_fused", st);
-    k_fwd_fused<<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
+    if (scalar) k_fwd_fused<true><<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
+    else k_fwd_fused<false><<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
     return post_launch();
   }
   rc = run_scan(false, pb, nseg, p.k, p.g, p.v, start, h, last, nullptr, st);
   if (rc) return rc;
   FwdOParams fp;
   if ((rc = act_map(&fp.mq, p.q, BT, pb.H)) || (rc = act_map(&fp.mk, p.k, BT, pb.H)) ||
-      (rc = act_map(&fp.mg, p.g, BT, pb.H)) || (rc = act_map(&fp.mv, p.v, BT, pb.H)) ||
-      (rc = state_map(&fp.mh, h, (size_t)pb.B * NT * pb.H * D)))
+      (rc = act_map(&fp.mv, p.v, BT, pb.H)) || (rc = state_map(&fp.mh, h, (size_t)pb.B * NT * pb.H * D)))
     return rc;
+  if (!scalar && (rc = act_map(&fp.mg, p.g, BT, pb.H))) return rc;
+  fp.gscalar = reinterpret_cast<const __nv_bfloat16*>(p.g);
   fp.o = reinterpret_cast<__nv_bfloat16*>(p.o); fp.T = pb.T; fp.H = pb.H; fp.NT = NT; fp.scale = pb.scale;
-  if ((rc = opt_in_smem(k_fwd_o, FWD_O_SMEM))) return rc;
+  if ((rc = opt_in_smem(k_fwd_o<true>, FWD_O_SMEM)) || (rc = opt_in_smem(k_fwd_o<false>, FWD_O_SMEM))) return rc;
   KernelScope ks("sm100_fwd_o", st);
-  k_fwd_o<<<dim3(pb.H, NT, pb.B), NTHREADS, FWD_O_SMEM, st>>>(fp);
+  if (scalar) k_fwd_o<true><<<dim3(pb.H, NT, pb.B), NTHREADS, FWD_O_SMEM, st>>>(fp);
+  else k_fwd_o<false><<<dim3(pb.H, NT, pb.B), NTHREADS, FWD_O_SMEM, st>>>(fp);
   return post_launch();
 }
 
@@ -1332,17 +1510,19 @@ size_t bwd_workspace_bytes(const tops_chunk_bwd_params& p) {
 }
 
 bool bwd_dtypes_ok(const tops_chunk_bwd_params& p) {
+  if (p.pb.gate_kind == TOPS_GATE_SCALAR)   // dg is the scalar gate's gradient, fp32 [B,T,H]
+    return (p.grad_dtype == TOPS_F32 || p.grad_dtype == TOPS_BF16) && p.dg_dtype == TOPS_F32;
   return (p.grad_dtype == TOPS_F32 && p.dg_dtype == TOPS_F32) ||
          (p.grad_dtype == TOPS_BF16 && (p.dg_dtype == TOPS_F32 || p.dg_dtype == TOPS_BF16));
 }
 
-template <typename TG, typename TD, bool SUMK = false>
+template <typename TG, typename TD, bool SUMK = false, bool SCALAR = false>
 int launch_bwd_main(const BwdParams& bp, cudaStream_t st) {
-  int rc = opt_in_smem(k_bwd_main<TG, TD, SUMK>, BWD_SMEM);
+  int rc = opt_in_smem(k_bwd_main<TG, TD, SUMK, SCALAR>, BWD_SMEM);
   if (rc) return rc;
   const int grid = bp.total < sm_count() ? bp.total : sm_count();
   KernelScope ks("sm100_bwd_main", st);
-  k_bwd_main<TG, TD, SUMK><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
+  k_bwd_main<TG, TD, SUMK, SCALAR><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
   return post_launch();
 }
 
@@ -1383,14 +1563,20 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   BwdParams bp;
   const int BT = pb.B * pb.T, NT = pb.T / C;
   const size_t rows = (size_t)pb.B * NT * pb.H * D;
+  const bool scalar = pb.gate_kind == TOPS_GATE_SCALAR;
   if ((rc = act_map(&bp.mq, p.q, BT, pb.H)) || (rc = act_map(&bp.mk, p.k, BT, pb.H)) ||
-      (rc = act_map(&bp.mg, p.g, BT, pb.H)) || (rc = act_map(&bp.mv, p.v, BT, pb.H)) ||
+      (rc = act_map(&bp.mv, p.v, BT, pb.H)) ||
       (rc = act_map(&bp.mdo, p.do_, BT, pb.H)) || (rc = state_map(&bp.mh, h, rows)) ||
       (rc = state_map(&bp.mdh, dh, rows)))
     return rc;
+  if (!scalar && (rc = act_map(&bp.mg, p.g, BT, pb.H))) return rc;
+  bp.gscalar = reinterpret_cast<const __nv_bfloat16*>(p.g);
   bp.dq = p.dq; bp.dk = p.dk; bp.dg = p.dg;
   bp.dv = reinterpret_cast<__nv_bfloat16*>(p.dv); bp.T = pb.T; bp.H = pb.H; bp.NT = NT; bp.scale = pb.scale;
   bp.total = NT * pb.B * pb.H;
+  if (scalar)
+    return p.grad_dtype == TOPS_F32 ? launch_bwd_main<float, float, true, true>(bp, st)
+                                    : launch_bwd_main<__nv_bfloat16, float, true, true>(bp, st);
   if (p.dg_sum_k) {
     if (!p.dg || p.dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;
     return p.grad_dtype == TOPS_F32 ? launch_bwd_main<float, float, true>(bp, st)

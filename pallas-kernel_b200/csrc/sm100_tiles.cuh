@@ -70,6 +70,40 @@ __device__ __forceinline__ void build_tri_tile(uint8_t* tile, int rows, int kind
     *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
+// Scalar gates (one log-gate per head and time step): the exponents of a chunk are 64 numbers, not a tile, so no
+// tensor-core product and no gate tile are needed.  Every warp keeps the chunk's 64 log-gates in registers
+// (lane l: time steps l and l + 32) and turns them into inclusive cumulative gates with shuffles.
+struct WarpGates {
+  float lo, hi;   // G of time steps lane and lane + 32
+  float g0, gn;   // G_0 (the first gate) and G_63 (the chunk's summed gates)
+  __device__ __forceinline__ float mid() const { return 0.5f * (g0 + gn); }
+};
+__device__ __forceinline__ WarpGates warp_cumulate(float a, float b, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b, o);
+    if (lane >= o) { a += x; b += y; }
+  }
+  b += __shfl_sync(0xffffffffu, a, 31);
+  WarpGates w;
+  w.lo = a; w.hi = b;
+  w.g0 = __shfl_sync(0xffffffffu, a, 0);
+  w.gn = __shfl_sync(0xffffffffu, b, 31);
+  return w;
+}
+// multiply 8 packed bf16 by one fp32 factor
+__device__ __forceinline__ uint4 scale8_by(uint4 x, float f) {
+  __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);
+  uint4 y;
+  uint32_t* py = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = __bfloat1622float2(px[t]);
+    py[t] = pack_bf16(v.x * f, v.y * f);
+  }
+  return y;
+}
+
 // multiply 8 packed bf16 by 8 fp32 factors
 __device__ __forceinline__ uint4 scale8(uint4 x, const float* f) {
   __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);
@@ -113,6 +147,7 @@ __device__ __forceinline__ void build_w_tile(uint8_t* tile) {
     *reinterpret_cast<uint4*>(tile + slab_off(r, c8)) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
+
 
 // 4 x 4 transpose over the lanes l, l^1, l^2, l^3.  In: v[j] = value of this lane's channel at
 // time t0 + j.  Out: v[j] = value of channel (lane & ~3) + j at time t0 + (lane & 3), so that a

@@ -84,7 +84,8 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
     dg_dtype = torch.float32
     direct = primal_dtypes and L.lib.tops_b200_chunk_selected_impl(C.byref(p.pb)) == L.IMPL_SM100
     if direct:
-        grad_dtype, dg_dtype = q.dtype, gate.dtype
+        grad_dtype = q.dtype
+        dg_dtype = torch.float32 if gate_kind == L.GATE_SCALAR else gate.dtype   # a scalar gate's dg is always fp32
     dq = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
     dk = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
     dv = torch.empty(B, T, H, V, dtype=do.dtype, device=dev)

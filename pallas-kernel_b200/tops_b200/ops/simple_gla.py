@@ -52,9 +52,8 @@ def _cu(cu_seqlens):
 
 
 def _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-    """True when the tcgen05 GLA kernels can serve this scalar-gate problem: a scalar
-    gate is a per-channel gate with the same value on all 128 channels, so the bf16
-    gate is replicated over K and the per-channel gate gradient summed over K."""
+    """True when the tcgen05 kernels serve this scalar-gate problem (their scalar-gate form: the gate
+    rides on the exponent pattern, nothing is replicated over K; dg comes back summed over K)."""
     return (g is not None and g_gamma is None and cu_seqlens is None and chunk_size == 64
             and q.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
             and q.shape[-1] == 128 and v.shape[-1] == 128 and q.shape[1] % 64 == 0)
@@ -67,13 +66,9 @@ def _expand_gate(g, K):
 def _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, want_saved):
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
-    gate_k = None
-    if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-        gate = gate_k = _expand_gate(g, q.shape[-1])
-        kind = L.GATE_PER_CHANNEL
     o, ht, _, _, saved = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
                                         _cu(cu_seqlens), want_saved=want_saved)
-    return o, ht, ((saved, gate_k) if want_saved else None)
+    return o, ht, ((saved, None) if want_saved else None)
 
 
 def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
@@ -93,13 +88,8 @@ def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chu
     that forward made (None makes it again)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
-    if _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-        # dq, dk leave the kernel in bf16; the gate gradient is summed over K inside the kernel (fp32 [B,T,H])
-        gk = _expand_gate(g, q.shape[-1]) if gate_k is None else gate_k
-        return chunk_bwd_call(q, k, v, gk, L.GATE_PER_CHANNEL, scale, initial_state, do, dht, chunk_size, q.dtype, True,
-                              initial_state is not None, h_saved=h_saved, dg_sum_k=True)
     return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
-                          g is not None, initial_state is not None, _cu(cu_seqlens))
+                          g is not None, initial_state is not None, _cu(cu_seqlens), h_saved=h_saved)
 
 
 class _ChunkSimpleGLA(torch.autograd.Function):

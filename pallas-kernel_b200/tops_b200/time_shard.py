@@ -139,7 +139,7 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
     def pack_problem(x, y, g):
         B, T, H, K = x.shape
         pb = common.make_problem(B, T, H, K, y.shape[-1], C, L.dtype_code(x.dtype), L.dtype_code(g.dtype),
-                                 L.GATE_PER_CHANNEL, 1.0)
+                                 L.GATE_PER_CHANNEL if g.ndim == 4 else L.GATE_SCALAR, 1.0)
         ok = (x.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
               and L.lib.tops_b200_chunk_selected_impl(C_.byref(pb)) == L.IMPL_SM100)
         return pb if ok else None
@@ -149,13 +149,11 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
     # shard take back so that they do not scan the shard a third time.
     kept = {}
 
-    def gate_k(g, K):
-        if g.ndim == 4:
-            return g
-        if kept.get("g") is not g:
-            kept.clear()
-            kept["g"], kept["gk"] = g, per_channel(g, K)
-        return kept["gk"]
+    def gate_k(g, K):   # the kernels take scalar gates as they are
+        return g.contiguous()
+
+    def kind_of(g):
+        return L.GATE_PER_CHANNEL if g.ndim == 4 else L.GATE_SCALAR
 
     def pack(x, y, g, reverse, scale):
         """Shard summary through the tcgen05 summary scan; None when the problem is not one it takes."""
@@ -214,8 +212,8 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
 
     if kind == "simple_gla":
         def fwd(q, k, v, g, scale, h_in):
-            if fast(q, v, g):   # the per-channel tcgen05 kernels on the replicated gate, segment summaries reused
-                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, gate_k(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale, h_in,
+            if fast(q, v, g):   # the tcgen05 kernels in their scalar-gate form, segment summaries reused
+                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, gate_k(g, q.shape[-1]), kind_of(g), scale, h_in,
                                                         True, C, want_saved=True, segments=segments("fwd", k))
                 kept["hs"] = (q.data_ptr(), hs)
                 return o, ht
@@ -225,9 +223,8 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
             if fast(q, v, g):
                 hs = kept.get("hs")
                 hs = hs[1] if hs is not None and hs[0] == q.data_ptr() else None
-                return _chunk.chunk_bwd_call(q, k, v, gate_k(g, q.shape[-1]), L.GATE_PER_CHANNEL, scale, h_in, do, dh_out,
-                                             C, q.dtype, True, True, h_saved=hs, dg_sum_k=True,
-                                             rev_segments=segments("rev", q))
+                return _chunk.chunk_bwd_call(q, k, v, gate_k(g, q.shape[-1]), kind_of(g), scale, h_in, do, dh_out,
+                                             C, q.dtype, True, True, h_saved=hs, rev_segments=segments("rev", q))
             return simple_gla.chunk_simple_gla_bwd(q, k, v, g, None, h_in, do, dh_out, scale, C)
     else:
         def fwd(q, k, v, g, scale, h_in):

@@ -101,13 +101,20 @@ def test_chunk_simple_gla_varlen():
         assert_close(name, a, b, torch.float32)
 
 
-def test_scalar_gate_on_tensor_core_kernels():
-    """bf16 scalar gates with K = V = 128, chunk 64 run on the tcgen05 GLA kernels
-    (gate replicated over the channels, gate gradient summed over them)."""
+@pytest.mark.parametrize("B,T,H", [
+    (1, 64, 1),        # a single chunk
+    (1, 512, 2),
+    (3, 192, 16),      # 48 (batch, head) pairs: the fused forward
+    (1, 2048, 3),      # few pairs, 32 chunks: time segments with summary scans and the join kernel
+    (2, 1536, 37),     # fused forward over two segments
+])
+def test_scalar_gate_on_tensor_core_kernels(B, T, H):
+    """bf16 scalar gates with K = V = 128, chunk 64 run on the tcgen05 GLA kernels in their scalar-gate
+    form (the gate is read as [B,T,H]; the gate gradient comes back summed over the channels)."""
     from tops_b200 import _lib as L
     from tops_b200.ops.simple_gla import chunk_simple_gla, chunk_simple_gla_bwd
     from tops_b200.synth import make_inputs
-    B, T, H, K, V, C = 1, 512, 2, 128, 128, 64
+    K, V, C = 128, 128, 64
     x = make_inputs(24, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
     assert x["g"].dtype == torch.bfloat16
     scale = K ** -0.5
@@ -122,6 +129,7 @@ def test_scalar_gate_on_tensor_core_kernels():
     buf = ctypes.create_string_buffer(4096)
     L.lib.tops_b200_profile_read(buf, len(buf))
     assert all(ln.startswith("sm100_") for ln in buf.value.decode().splitlines()), buf.value
+    assert L.device_error() == 0
     assert_close("o", o, o_ref, torch.bfloat16)
     assert_close("ht", ht, ht_ref, torch.bfloat16)
     assert got[0].dtype == torch.bfloat16 and got[3].shape == (B, T, H)
