@@ -258,11 +258,6 @@ typedef struct {
    * `tops/cpu/ops/gla/chunk.py:551-561`). */
   const void* h_saved;
   int32_t dg_dtype; /* TOPS_F32 (0) or TOPS_BF16, see above */
-  /* tcgen05 path only (TOPS_E_UNSUPPORTED elsewhere): the per-channel gate `[B,T,H,K]` is a scalar gate
-   * `[B,T,H]` replicated over K (simple_gla on the per-channel kernels); dg is then summed over K inside
-   * the kernel and written as fp32 `[B,T,H]` — the scalar gate's gradient
-   * (`tops/cpu/ops/simple_gla/chunk.py:348-412`). */
-  int32_t dg_sum_k;
   /* The same for the reverse scan: the workspace of a `tops_b200_chunk_state_exchange_pack` call with
    * reverse = 1 (x = q, y = do, the same scale) on this problem.  NULL otherwise. */
   void* rev_segments;
@@ -385,6 +380,10 @@ int tops_b200_chunk_kda_fwd(const tops_chunk_kda_fwd_params* p, void* stream);
  * `saved_*` are the residuals the forward wrote.  dq, dk, dg `[B,T,H,K]` and dbeta `[B,T,H]` in
  * `grad_dtype` (TOPS_F32 as the reference's orchestrator returns them, or TOPS_BF16); dv bf16;
  * dg is with respect to the natural-log gate; dh0 fp32 (NULL to skip).
+ * State gradient only: with dq = dk = dg = dbeta = NULL the call runs the reverse scan alone and
+ * writes dh0 (and dv).  The state gradient entering a span of tokens depends on the one leaving it
+ * linearly, dh_in = M^T dh_out + D; a call with dht = NULL gives D, the summary a rank needs when one
+ * sequence is sharded over time (no counterpart in the reference, which has no multi-device path).
  * ------------------------------------------------------------------------ */
 typedef struct {
   int32_t B, T, H, K, V, chunk;
@@ -394,7 +393,7 @@ typedef struct {
   const void* do_;
   const float* dht; /* [B,H,K,V] or NULL */
   const void *saved_h, *saved_vnew, *saved_T, *saved_R;
-  void *dq, *dk, *dg, *dbeta;
+  void *dq, *dk, *dg, *dbeta; /* all four, or all NULL (state gradient only) */
   int32_t grad_dtype;
   void* dv;
   float* dh0;

@@ -898,12 +898,12 @@ struct BwdParams {
 constexpr int BWD_THREADS = 704;
 constexpr int BWD_EPI_THREADS = 512, BWD_GATE_THREADS = 128;
 
-// TG: type of dq and dk; TD: type of dg; SUMK: dg is summed over the key channels inside the kernel and
-// written as fp32 [B,T,H] (a scalar gate replicated over K: its gradient is the sum of the channels').
-// SCALAR (with SUMK): the gate is one value per head and time step; no gate tile is fetched and no exponent
-// product issued: every write-out warp cumulates the 64 gates of a chunk in registers (warp_cumulate) and
-// hands the factors exp(+-(G - mid)) of the time steps around by shuffles.
-template <typename TG, typename TD, bool SUMK, bool SCALAR>
+// TG: type of dq and dk; TD: type of dg.
+// SCALAR: the gate is one value per head and time step; no gate tile is fetched and no exponent product
+// issued: every write-out warp cumulates the 64 gates of a chunk in registers (warp_cumulate) and hands the
+// factors exp(+-(G - mid)) of the time steps around by shuffles.  dg is summed over the key channels inside
+// the kernel and written as fp32 [B,T,H] (the scalar gate's gradient is the sum of the channels').
+template <typename TG, typename TD, bool SCALAR>
 __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_constant__ BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
@@ -925,7 +925,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   __shared__ float sufsum[2][4][D];   // per-segment totals of the dg suffix sums
   __shared__ float tails[2][4][D];    // per-segment sum_i dk_inter k
   __shared__ float hdh_s[2][D];       // sum_v h' dh'
-  __shared__ float dgk_s[2][C];       // SUMK: dg of a chunk summed over the channels
+  __shared__ float dgk_s[2][C];       // SCALAR: dg of a chunk summed over the channels
   __shared__ volatile int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // tensor-memory columns: the exponent tile E_mid is consumed by the gating before A and dA take its place
@@ -1054,7 +1054,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
       if (it + 1 < nit && !gate_chunk(it + 1)) break;
       if (SCALAR && it + 2 < nit) load_gates(it + 2);   // fetched where the thread waits anyway
       bool done = wait(&bar_main, it & 1, 8) && wait(&hdh_done[sl], (it >> 1) & 1, 11);
-      if (SUMK) done = __all_sync(0xffffffffu, done);   // (shuffles follow: the whole warp takes one path)
+      if (SCALAR) done = __all_sync(0xffffffffu, done);   // (shuffles follow: the whole warp takes one path)
       if (!done) break;
       tc_fence_after();
       const uint8_t* qt = qs + sl * TILE64;
@@ -1101,17 +1101,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
                         hdh_s[sl][col] / p.scale;
       // (exp(G_n) sum_v h dh = sum_v h' dh' / scale)
       mbar_arrive(&e_done[sl]);   // tensor memory, the q~ / k~ tiles and hdh_s of this chunk are free
-      if constexpr (SUMK) {
-        // sum over the 128 channels: the lanes of a warp by shuffles (lane t keeps the total of time step t),
-        // then the four warps that share this segment through shared memory
-        float mine = 0.f;
+      if constexpr (SCALAR) {
+        // sum over the 128 channels: the lanes of a warp by a shuffle butterfly (lane t keeps the total of time
+        // step t), then the four warps that share this segment through shared memory
 #pragma unroll
-        for (int t = 0; t < SEG; ++t) {
-          float w = dgl[t] + cst;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
-          if (lane == t) mine = w;
-        }
+        for (int t = 0; t < SEG; ++t) dgl[t] += cst;
+        const float mine = warp_sum16(dgl, lane);
         if (lane < SEG) atomicAdd(&dgk_s[sl][seg * SEG + lane], mine);
         asm volatile("bar.sync 1, %0;" ::"n"(BWD_EPI_THREADS) : "memory");
         if (tid < C) {
@@ -1516,13 +1511,13 @@ bool bwd_dtypes_ok(const tops_chunk_bwd_params& p) {
          (p.grad_dtype == TOPS_BF16 && (p.dg_dtype == TOPS_F32 || p.dg_dtype == TOPS_BF16));
 }
 
-template <typename TG, typename TD, bool SUMK = false, bool SCALAR = false>
+template <typename TG, typename TD, bool SCALAR = false>
 int launch_bwd_main(const BwdParams& bp, cudaStream_t st) {
-  int rc = opt_in_smem(k_bwd_main<TG, TD, SUMK, SCALAR>, BWD_SMEM);
+  int rc = opt_in_smem(k_bwd_main<TG, TD, SCALAR>, BWD_SMEM);
   if (rc) return rc;
   const int grid = bp.total < sm_count() ? bp.total : sm_count();
   KernelScope ks("sm100_bwd_main", st);
-  k_bwd_main<TG, TD, SUMK, SCALAR><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
+  k_bwd_main<TG, TD, SCALAR><<<grid, BWD_THREADS, BWD_SMEM, st>>>(bp);
   return post_launch();
 }
 
@@ -1575,13 +1570,8 @@ int chunk_bwd(const tops_chunk_bwd_params& p, void* ws, size_t, cudaStream_t st)
   bp.dv = reinterpret_cast<__nv_bfloat16*>(p.dv); bp.T = pb.T; bp.H = pb.H; bp.NT = NT; bp.scale = pb.scale;
   bp.total = NT * pb.B * pb.H;
   if (scalar)
-    return p.grad_dtype == TOPS_F32 ? launch_bwd_main<float, float, true, true>(bp, st)
-                                    : launch_bwd_main<__nv_bfloat16, float, true, true>(bp, st);
-  if (p.dg_sum_k) {
-    if (!p.dg || p.dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;
     return p.grad_dtype == TOPS_F32 ? launch_bwd_main<float, float, true>(bp, st)
                                     : launch_bwd_main<__nv_bfloat16, float, true>(bp, st);
-  }
   if (p.grad_dtype == TOPS_F32) return launch_bwd_main<float, float>(bp, st);
   if (p.dg_dtype == TOPS_F32) return launch_bwd_main<__nv_bfloat16, float>(bp, st);
   return launch_bwd_main<__nv_bfloat16, __nv_bfloat16>(bp, st);

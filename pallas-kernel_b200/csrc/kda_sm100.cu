@@ -987,11 +987,15 @@ struct KdaBwdOutParams {
   const float* dbeta1;
   void *dq, *dk, *dg;     // [B,T,H,K] fp32 or bf16
   void* dbeta;            // [B,T,H]   fp32 or bf16
-  int T, H, NT;
+  int T, H, NT, total;    // total = B * H * NT chunks
   float scale;
 };
 constexpr size_t KDA_OUT_SMEM = 7 * TILE64 + 2 * TILE128 + 2 * SLAB64 + 2 * SLAB64 + 1024;
 
+// Persistent: block x walks chunks x, x + gridDim.x, ... (heads fastest, so the blocks in flight read whole
+// token rows).  Everything of a chunk but q and k is dead once its products have completed, so the next
+// chunk's g, do, v', -dR, h', dh^, dS, dL are fetched while the threads write the gradients of this one out;
+// q and k (gated in place, read by the write-out) are brought into L2 meanwhile and fetched after it.
 template <typename TG>
 __global__ void __launch_bounds__(NTHREADS, 1) k_kda_bwd_out(const __grid_constant__ KdaBwdOutParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -1008,22 +1012,43 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_kda_bwd_out(const __grid_consta
   uint8_t* dSs = dhs + TILE128;        // dS (64 x 64)
   uint8_t* dLs = dSs + SLAB64;         // dL (64 x 64)
   uint8_t* mtm = dLs + SLAB64;         // TRI_MID pattern, rows repeated to 128
-  __shared__ uint64_t bar_g, bar_rest, bar_e, bar_main;
+  // every barrier completes once per chunk (parity it & 1)
+  __shared__ uint64_t bar_g, bar_qk, bar_rest, bar_e, bar_main;
   __shared__ uint32_t tmem_slot;
   __shared__ float sufsum[4][D], tails[4][D], hdh_s[D], beta_s[C], db_s[C];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, seg = warp >> 2, col = q4 * 32 + lane;
-  const int h = blockIdx.x, ci = blockIdx.y, b = blockIdx.z;
-  const int row = b * p.T + ci * C;
-  const int hrow = ((b * p.NT + ci) * p.H + h) * D;
+  const int nit = (p.total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   constexpr uint32_t cE = 0, cET = 128, cdq = 192, cdki = 256, cdkr = 320, cdkb = 384;
-  if (tid == 0) {
-    mbar_init(&bar_g, 1); mbar_init(&bar_rest, 1); mbar_init(&bar_e, 1); mbar_init(&bar_main, 1);
-    fence_barrier_init();
-    mbar_expect_tx(&bar_g, 3 * TILE64);
+  auto chunk_rows = [&](int it, int& h, int& row, int& hrow) {
+    const int cid = blockIdx.x + it * gridDim.x;
+    const int ci = (cid / p.H) % p.NT, b = cid / (p.H * p.NT);
+    h = cid % p.H;
+    row = b * p.T + ci * C;
+    hrow = ((b * p.NT + ci) * p.H + h) * D;
+  };
+  auto load_g = [&](int it) {
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
+    mbar_expect_tx(&bar_g, TILE64);
     tma_load_3d(gs, &p.mg, &bar_g, 0, h, row); tma_load_3d(gs + SLAB64, &p.mg, &bar_g, 64, h, row);
-    tma_load_3d(qs, &p.mq, &bar_g, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_g, 64, h, row);
-    tma_load_3d(ks, &p.mk, &bar_g, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_g, 64, h, row);
+  };
+  auto load_qk = [&](int it) {
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
+    mbar_expect_tx(&bar_qk, 2 * TILE64);
+    tma_load_3d(qs, &p.mq, &bar_qk, 0, h, row); tma_load_3d(qs + SLAB64, &p.mq, &bar_qk, 64, h, row);
+    tma_load_3d(ks, &p.mk, &bar_qk, 0, h, row); tma_load_3d(ks + SLAB64, &p.mk, &bar_qk, 64, h, row);
+  };
+  auto prefetch_qk = [&](int it) {
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
+    tma_prefetch_l2_3d(&p.mq, 0, h, row); tma_prefetch_l2_3d(&p.mq, 64, h, row);
+    tma_prefetch_l2_3d(&p.mk, 0, h, row); tma_prefetch_l2_3d(&p.mk, 64, h, row);
+  };
+  auto load_rest = [&](int it) {
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
     mbar_expect_tx(&bar_rest, 3 * TILE64 + 2 * TILE128 + 2 * SLAB64);
     tma_load_3d(dos, &p.mdo, &bar_rest, 0, h, row); tma_load_3d(dos + SLAB64, &p.mdo, &bar_rest, 64, h, row);
     tma_load_3d(vns, &p.mvn, &bar_rest, 0, h, row); tma_load_3d(vns + SLAB64, &p.mvn, &bar_rest, 64, h, row);
@@ -1032,13 +1057,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_kda_bwd_out(const __grid_consta
     tma_load_2d(dhs, &p.mdh, &bar_rest, 0, hrow); tma_load_2d(dhs + TILE128 / 2, &p.mdh, &bar_rest, 64, hrow);
     tma_load_3d(dSs, &p.mdS, &bar_rest, 0, h, row);
     tma_load_3d(dLs, &p.mdL, &bar_rest, 0, h, row);
+  };
+  auto beta_of = [&](int it) {   // threads 0..63
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
+    return p.beta[((size_t)row + tid) * p.H + h];
+  };
+  if (tid == 0) {
+    mbar_init(&bar_g, 1); mbar_init(&bar_qk, 1); mbar_init(&bar_rest, 1); mbar_init(&bar_e, 1); mbar_init(&bar_main, 1);
+    fence_barrier_init();
+    if (nit > 0) { load_g(0); load_qk(0); load_rest(0); }
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 512); tmem_relinquish(); }
-  if (tid < C) {
-    beta_s[tid] = __bfloat162float(p.beta[((size_t)row + tid) * p.H + h]);
-    db_s[tid] = 0.f;
-  }
+  __nv_bfloat16 beta_next = __float2bfloat16(0.f);   // threads 0..63: beta of the next chunk, as loaded
+  if (tid < C && nit > 0) beta_next = beta_of(0);
   build_tri_tile(mtm, 128, TRI_MID);
   fence_async_smem();
   tc_fence_before();
@@ -1046,109 +1079,133 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_kda_bwd_out(const __grid_consta
   tc_fence_after();
   const uint32_t tm = tmem_slot;
   const uint32_t lane_base = q4 * 32;
-  bool ok = __syncthreads_and(mbar_wait(&bar_g, 0));
-  if (!ok) fail(3);
-  if (ok && tid == 0) {
-    tc_fence_after();
-    const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm);
-#pragma unroll
-    for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
-      umma_bf16(tm + cE, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
-#pragma unroll
-    for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
-      umma_bf16(tm + cET, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0), umma_idesc(128, 64, 1, 0), j0 > 0);
-    umma_commit(&bar_e);
-  }
-  __syncwarp();
-  if (ok) { ok = __syncthreads_and(mbar_wait(&bar_e, 0)); if (!ok) fail(9); }
-  if (ok) {   // gate: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
-    tc_fence_after();
-    const int i = (q4 * 32 + lane) & 63;
-    const int cg = (q4 >> 1) * 4 + seg;
-    float em[16];
-    tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), em);
-    const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
-    const float bi = beta_s[i];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
-      float fb[8], fs[8], r[8];
-#pragma unroll
-      for (int t = 0; t < 8; ++t) {
-        const float f = fast_exp(em[8 * u + t]);
-        fb[t] = f * bi;
-        fs[t] = f * p.scale;
-        r[t] = fast_exp(-em[8 * u + t]);
-      }
-      const uint4 kraw = *reinterpret_cast<const uint4*>(ks + off);
-      *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), fs);
-      *reinterpret_cast<uint4*>(khs + off) = scale8(kraw, fb);
-      *reinterpret_cast<uint4*>(ks + off) = scale8(kraw, r);
-    }
-    fence_async_smem();
-    tc_fence_before();
-  }
-  if (ok) { ok = __syncthreads_and(mbar_wait(&bar_rest, 0)); if (!ok) fail(6); } else { __syncthreads(); }
-  if (ok && tid == 0) {
-    tc_fence_after();
-    const uint32_t qa = smem_u32(qs), ka = smem_u32(ks), kha = smem_u32(khs), doa = smem_u32(dos), vna = smem_u32(vns),
-                   nra = smem_u32(nrs), ha = smem_u32(hs), dha = smem_u32(dhs), dSa = smem_u32(dSs), dLa = smem_u32(dLs);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dq~^T[k][i] = h' do^T
-      umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dq~^T[k][i] += sum_j k~[j][k] dS[i][j]
-      umma_bf16(tm + cdq, desc_mnmajor(ka, 64, k0, 0), desc_kmajor(dSa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dk~_inter^T[k][j] = dh^ v'^T
-      umma_bf16(tm + cdki, desc_kmajor(dha, 128, 0, k0), desc_kmajor(vna, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dk~_rest^T[k][j] = sum_i q~[i][k] dS[i][j]
-      umma_bf16(tm + cdkr, desc_mnmajor(qa, 64, k0, 0), desc_mnmajor(dSa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dk~_rest^T[k][j] += sum_i (beta k^)[i][k] dL[i][j]
-      umma_bf16(tm + cdkr, desc_mnmajor(kha, 64, k0, 0), desc_mnmajor(dLa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
-#pragma unroll
-    for (int k0 = 0; k0 < D; k0 += 16)   // dk^b^T[k][j] = h' (-dR)^T
-      umma_bf16(tm + cdkb, desc_kmajor(ha, 128, 0, k0), desc_kmajor(nra, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
-#pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)   // dk^b^T[k][j] += sum_i k~[i][k] dL[j][i]
-      umma_bf16(tm + cdkb, desc_mnmajor(ka, 64, k0, 0), desc_kmajor(dLa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
-    umma_commit(&bar_main);
-  }
-  __syncwarp();
-  if (ok) {   // sum_v h'[k][v] dh^[k][v] while the products run: thread = (channel, quarter of the columns)
-    const int kk = tid >> 2, part = tid & 3;
-    float hd = 0.f;
-#pragma unroll
-    for (int c8 = 0; c8 < 32; c8 += 8) {
-      const uint32_t off = tile_off(128, kk, part * 32 + c8);
-      const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
-      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-      const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
-        hd = fmaf(fa.x, fd.x, hd);
-        hd = fmaf(fa.y, fd.y, hd);
-      }
-    }
-    hd += __shfl_xor_sync(0xffffffffu, hd, 1);
-    hd += __shfl_xor_sync(0xffffffffu, hd, 2);
-    if (part == 0) hdh_s[kk] = hd;
-  }
-  if (ok) { ok = __syncthreads_and(mbar_wait(&bar_main, 0)); if (!ok) fail(8); } else { __syncthreads(); }
   TG* const dq_out = reinterpret_cast<TG*>(p.dq);
   TG* const dk_out = reinterpret_cast<TG*>(p.dk);
   TG* const dg_out = reinterpret_cast<TG*>(p.dg);
   const size_t ostride = (size_t)p.H * D;
-  const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
-  const size_t obase4 = obase - (lane & 3) + (size_t)(lane & 3) * ostride;
-  float dgl[SEG];
-  float run = 0.f, tail = 0.f;
-  if (ok) {
+  const ColAddr ca = col_prep(64, col);
+  bool ok = true;
+  // Every bounded wait sits at the start of a chunk's work, before any copy for the chunk after it is issued:
+  // when one gives up, all copies in flight were issued before its spin began and have long landed.
+  for (int it = 0; it < nit; ++it) {
+    const uint32_t ph = it & 1;
+    const bool more = it + 1 < nit;
+    int h, row, hrow;
+    chunk_rows(it, h, row, hrow);
+    float db1 = 0.f;   // threads 0..63: the scan's part of dbeta (read here, used after the write-out)
+    if (tid < C) {
+      beta_s[tid] = __bfloat162float(beta_next);
+      db_s[tid] = 0.f;
+      db1 = p.dbeta1[((size_t)row + tid) * p.H + h];
+    }
+    ok = __syncthreads_and(mbar_wait(&bar_g, ph));
+    if (!ok) { fail(3); break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
+        umma_bf16(tm + cE, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+      for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
+        umma_bf16(tm + cET, desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0), umma_idesc(128, 64, 1, 0), j0 > 0);
+      umma_commit(&bar_e);
+    }
+    __syncwarp();
+    ok = __syncthreads_and(mbar_wait(&bar_e, ph) && mbar_wait(&bar_qk, ph));
+    if (!ok) { fail(9); break; }
+    {   // gate: thread (q4, lane, seg) owns time row (32 q4 + lane) mod 64 and 16 channels
+      tc_fence_after();
+      const int i = (q4 * 32 + lane) & 63;
+      const int cg = (q4 >> 1) * 4 + seg;
+      float em[16];
+      tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), em);
+      const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
+      const float bi = beta_s[i];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t off = rowoff + (((uint32_t)((cg & 3) * 2 + u) ^ (uint32_t)i) & 7u) * 16u;
+        float fb[8], fs[8], r[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float f = fast_exp(em[8 * u + t]);
+          fb[t] = f * bi;
+          fs[t] = f * p.scale;
+          r[t] = fast_exp(-em[8 * u + t]);
+        }
+        const uint4 kraw = *reinterpret_cast<const uint4*>(ks + off);
+        *reinterpret_cast<uint4*>(qs + off) = scale8(*reinterpret_cast<const uint4*>(qs + off), fs);
+        *reinterpret_cast<uint4*>(khs + off) = scale8(kraw, fb);
+        *reinterpret_cast<uint4*>(ks + off) = scale8(kraw, r);
+      }
+      fence_async_smem();
+      tc_fence_before();
+    }
+    ok = __syncthreads_and(mbar_wait(&bar_rest, ph));
+    if (!ok) { fail(6); break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t qa = smem_u32(qs), ka = smem_u32(ks), kha = smem_u32(khs), doa = smem_u32(dos), vna = smem_u32(vns),
+                     nra = smem_u32(nrs), ha = smem_u32(hs), dha = smem_u32(dhs), dSa = smem_u32(dSs), dLa = smem_u32(dLs);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dq~^T[k][i] = h' do^T
+        umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < C; k0 += 16)   // dq~^T[k][i] += sum_j k~[j][k] dS[i][j]
+        umma_bf16(tm + cdq, desc_mnmajor(ka, 64, k0, 0), desc_kmajor(dSa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dk~_inter^T[k][j] = dh^ v'^T
+        umma_bf16(tm + cdki, desc_kmajor(dha, 128, 0, k0), desc_kmajor(vna, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < C; k0 += 16)   // dk~_rest^T[k][j] = sum_i q~[i][k] dS[i][j]
+        umma_bf16(tm + cdkr, desc_mnmajor(qa, 64, k0, 0), desc_mnmajor(dSa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < C; k0 += 16)   // dk~_rest^T[k][j] += sum_i (beta k^)[i][k] dL[i][j]
+        umma_bf16(tm + cdkr, desc_mnmajor(kha, 64, k0, 0), desc_mnmajor(dLa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
+#pragma unroll
+      for (int k0 = 0; k0 < D; k0 += 16)   // dk^b^T[k][j] = h' (-dR)^T
+        umma_bf16(tm + cdkb, desc_kmajor(ha, 128, 0, k0), desc_kmajor(nra, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+      for (int k0 = 0; k0 < C; k0 += 16)   // dk^b^T[k][j] += sum_i k~[i][k] dL[j][i]
+        umma_bf16(tm + cdkb, desc_mnmajor(ka, 64, k0, 0), desc_kmajor(dLa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+      umma_commit(&bar_main);
+    }
+    __syncwarp();
+    {   // sum_v h'[k][v] dh^[k][v] while the products run: thread = (channel, quarter of the columns)
+      const int kk = tid >> 2, part = tid & 3;
+      float hd = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < 32; c8 += 8) {
+        const uint32_t off = tile_off(128, kk, part * 32 + c8);
+        const uint4 a = *reinterpret_cast<const uint4*>(hs + off), d = *reinterpret_cast<const uint4*>(dhs + off);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* pd = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 fa = __bfloat1622float2(pa[t]), fd = __bfloat1622float2(pd[t]);
+          hd = fmaf(fa.x, fd.x, hd);
+          hd = fmaf(fa.y, fd.y, hd);
+        }
+      }
+      hd += __shfl_xor_sync(0xffffffffu, hd, 1);
+      hd += __shfl_xor_sync(0xffffffffu, hd, 2);
+      if (part == 0) hdh_s[kk] = hd;
+    }
+    ok = __syncthreads_and(mbar_wait(&bar_main, ph));
+    if (!ok) { fail(8); break; }
+    // the products are complete and no thread reads h', dh^ any more: all of this chunk but q~, k~, beta k^
+    // is dead, the next chunk's tiles take their place while the gradients are written out
+    if (tid == 0 && more) {
+      load_g(it + 1);
+      load_rest(it + 1);
+      prefetch_qk(it + 1);
+    }
+    if (tid < C && more) beta_next = beta_of(it + 1);
+    const size_t obase = ((size_t)(row + seg * SEG) * p.H + h) * D + col;
+    const size_t obase4 = obase - (lane & 3) + (size_t)(lane & 3) * ostride;
+    float dgl[SEG], dbl[SEG];
+    float run = 0.f, tail = 0.f;
     tc_fence_after();
-    const ColAddr ca = col_prep(64, col);
 #pragma unroll
     for (int blk = 1; blk >= 0; --blk) {
       float et[8], dq[8], dki[8], dkr[8], dkb[8];
@@ -1170,34 +1227,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_kda_bwd_out(const __grid_consta
         dgl[t] = run;
         st_out(dq_out, obase + t * ostride, e * p.scale * dq[u]);
         st_out(dk_out, obase + t * ostride, r * dkt + e * beta_s[ti] * dkb[u]);
-        // dbeta2[t] = sum_k k exp(E) dk^b = sum_k k~ e^2 dk^b
-        float db = kv * e * e * dkb[u];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) db += __shfl_xor_sync(0xffffffffu, db, o);
-        if (lane == 0) atomicAdd(&db_s[ti], db);
+        dbl[t] = kv * e * e * dkb[u];   // dbeta2[t] = sum_k k exp(E) dk^b = sum_k k~ e^2 dk^b
       }
+    }
+    {   // sum over the channels: the lanes of a warp by a shuffle butterfly, the four warps of a segment by atomics
+      const float mine = warp_sum16(dbl, lane);
+      if (lane < SEG) atomicAdd(&db_s[seg * SEG + lane], mine);
     }
     sufsum[seg][col] = run;
     tails[seg][col] = tail;
-  }
-  __syncthreads();
-  if (ok) {
-    const float later = (seg < 1 ? sufsum[1][col] : 0.f) + (seg < 2 ? sufsum[2][col] : 0.f) + (seg < 3 ? sufsum[3][col] : 0.f);
-    const float cst = later + tails[0][col] + tails[1][col] + tails[2][col] + tails[3][col] + hdh_s[col];
+    tc_fence_before();
+    __syncthreads();   // q~, k~, beta k^ and tensor memory have been read
+    if (tid == 0 && more) load_qk(it + 1);
+    {
+      const float later = (seg < 1 ? sufsum[1][col] : 0.f) + (seg < 2 ? sufsum[2][col] : 0.f) + (seg < 3 ? sufsum[3][col] : 0.f);
+      const float cst = later + tails[0][col] + tails[1][col] + tails[2][col] + tails[3][col] + hdh_s[col];
 #pragma unroll
-    for (int t = 0; t < SEG; t += 4) {
-      float w[4] = {dgl[t] + cst, dgl[t + 1] + cst, dgl[t + 2] + cst, dgl[t + 3] + cst};
-      st_transposed4(dg_out, obase4 + t * ostride, w, lane);
+      for (int t = 0; t < SEG; t += 4) {
+        float w[4] = {dgl[t] + cst, dgl[t + 1] + cst, dgl[t + 2] + cst, dgl[t + 3] + cst};
+        st_transposed4(dg_out, obase4 + t * ostride, w, lane);
+      }
+      if (tid < C) st_out(reinterpret_cast<TG*>(p.dbeta), ((size_t)row + tid) * p.H + h, db_s[tid] + db1);
     }
-    if (tid < C) {
-      const size_t bi = ((size_t)row + tid) * p.H + h;
-      st_out(reinterpret_cast<TG*>(p.dbeta), bi, db_s[tid] + p.dbeta1[bi]);
-    }
+    __syncthreads();   // sufsum, tails, hdh_s, db_s, beta_s are free for the next chunk
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tm, 512);
-  if (tid == 0 && !ok) poison(dq_out + ((size_t)row * p.H + h) * D);
+  if (tid == 0 && !ok) {
+    int h, row, hrow;
+    chunk_rows(0, h, row, hrow);
+    poison(dq_out + ((size_t)row * p.H + h) * D);
+  }
 }
 
 }  // namespace
@@ -1286,6 +1347,8 @@ int kda_chunk_bwd(const tops_chunk_kda_bwd_params& p, void* ws, cudaStream_t st)
     k_kda_bwd_scan<<<p.B * p.H, KDA_THREADS, KDA_SCAN_SMEM, st>>>(sp);
     if ((rc = post_launch())) return rc;
   }
+  const bool state_gradient_only = !p.dq && !p.dk && !p.dg && !p.dbeta;
+  if (state_gradient_only) return TOPS_OK;
   {
     KdaIntraParams ip;
     if ((rc = act_map(&ip.mdo, p.do_, BT, p.H)) || (rc = act_map(&ip.mvn, p.saved_vnew, BT, p.H)) ||
@@ -1309,13 +1372,15 @@ int kda_chunk_bwd(const tops_chunk_kda_bwd_params& p, void* ws, cudaStream_t st)
     op.beta = reinterpret_cast<const __nv_bfloat16*>(p.beta);
     op.dbeta1 = dbeta1; op.dq = p.dq; op.dk = p.dk; op.dg = p.dg; op.dbeta = p.dbeta;
     op.T = p.T; op.H = p.H; op.NT = NT; op.scale = p.scale;
+    op.total = p.B * p.H * NT;
+    const int grid = op.total < sm_count() ? op.total : sm_count();
     KernelScope ks("sm100_kda_bwd_out", st);
     if (p.grad_dtype == TOPS_F32) {
       if ((rc = opt_in_smem(k_kda_bwd_out<float>, KDA_OUT_SMEM))) return rc;
-      k_kda_bwd_out<float><<<dim3(p.H, NT, p.B), NTHREADS, KDA_OUT_SMEM, st>>>(op);
+      k_kda_bwd_out<float><<<grid, NTHREADS, KDA_OUT_SMEM, st>>>(op);
     } else {
       if ((rc = opt_in_smem(k_kda_bwd_out<__nv_bfloat16>, KDA_OUT_SMEM))) return rc;
-      k_kda_bwd_out<__nv_bfloat16><<<dim3(p.H, NT, p.B), NTHREADS, KDA_OUT_SMEM, st>>>(op);
+      k_kda_bwd_out<__nv_bfloat16><<<grid, NTHREADS, KDA_OUT_SMEM, st>>>(op);
     }
     return post_launch();
   }

@@ -91,6 +91,21 @@ __device__ __forceinline__ WarpGates warp_cumulate(float a, float b, int lane) {
   w.gn = __shfl_sync(0xffffffffu, b, 31);
   return w;
 }
+// Sums 16 values per thread over the 32 lanes of a warp with 16 shuffles (a butterfly that halves the number of
+// live values at every step): on return lane l holds the warp's total of v[l & 15].
+__device__ __forceinline__ float warp_sum16(float (&v)[16], int lane) {
+#pragma unroll
+  for (int s = 8; s >= 1; s >>= 1) {
+    const bool up = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = up ? v[i] : v[i + s];
+      const float keep = up ? v[i + s] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+    }
+  }
+  return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 16);
+}
 // multiply 8 packed bf16 by one fp32 factor
 __device__ __forceinline__ uint4 scale8_by(uint4 x, float f) {
   __nv_bfloat162* px = reinterpret_cast<__nv_bfloat162*>(&x);

@@ -386,7 +386,7 @@ extern "C" int tops_b200_chunk_gla_bwd(const tops_chunk_bwd_params* p, void* wor
   if (!workspace || workspace_bytes < tops_b200_chunk_bwd_workspace_bytes(p)) return TOPS_E_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   if (use_sm100(p->pb) && sm100::bwd_dtypes_ok(*p)) return sm100::chunk_bwd(*p, workspace, workspace_bytes, st);
-  if (p->dg_dtype != TOPS_F32 || p->dg_sum_k) return TOPS_E_UNSUPPORTED;   // the generic kernels write fp32 dg per gate element
+  if (p->dg_dtype != TOPS_F32) return TOPS_E_UNSUPPORTED;   // the generic kernels write fp32 dg per gate element
 
   Problem pb;
   BwdLayout L;
@@ -468,8 +468,12 @@ extern "C" size_t tops_b200_chunk_kda_bwd_workspace_bytes(const tops_chunk_kda_b
 extern "C" int tops_b200_chunk_kda_bwd(const tops_chunk_kda_bwd_params* p, void* workspace, size_t workspace_bytes,
                                        void* stream) {
   if (!p || !p->q || !p->k || !p->v || !p->g || !p->beta || !p->do_ || !p->saved_h || !p->saved_vnew || !p->saved_T ||
-      !p->saved_R || !p->dq || !p->dk || !p->dv || !p->dg || !p->dbeta)
+      !p->saved_R || !p->dv)
     return TOPS_E_NULL;
+  {   // dq, dk, dg, dbeta: all four, or none (state gradient only, which must then be asked for)
+    const int given = !!p->dq + !!p->dk + !!p->dg + !!p->dbeta;
+    if ((given != 0 && given != 4) || (given == 0 && !p->dh0)) return TOPS_E_NULL;
+  }
   if (p->B < 1 || p->T < 1 || p->H < 1 || p->K < 1 || p->V < 1) return TOPS_E_BAD_SHAPE;
   if (!valid_dtype(p->dtype) || !valid_dtype(p->gate_dtype) || !valid_dtype(p->grad_dtype)) return TOPS_E_BAD_DTYPE;
   if (!sm100::kda_bwd_supported(*p)) return TOPS_E_UNSUPPORTED;

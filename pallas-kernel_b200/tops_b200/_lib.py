@@ -61,7 +61,7 @@ class ChunkFwdParams(C.Structure):
 class ChunkBwdParams(C.Structure):
     _fields_ = [("pb", ChunkProblem), ("q", _vp), ("k", _vp), ("v", _vp), ("g", _vp), ("h0", _vp), ("do_", _vp),
                 ("dht", _vp), ("dq", _vp), ("dk", _vp), ("grad_dtype", _i32), ("dv", _vp), ("dg", _vp),
-                ("dh0", _vp), ("h_saved", _vp), ("dg_dtype", _i32), ("dg_sum_k", _i32), ("rev_segments", _vp)]
+                ("dh0", _vp), ("h_saved", _vp), ("dg_dtype", _i32), ("rev_segments", _vp)]
 
 
 class RecurrentFwdParams(C.Structure):

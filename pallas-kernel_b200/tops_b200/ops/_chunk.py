@@ -56,15 +56,14 @@ def chunk_fwd_call(q, k, v, gate, gate_kind, scale, h0, want_ht, chunk, cu_seqle
 
 @L.on_tensor_device
 def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dtype, want_dg, want_dh0,
-                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False, dg_sum_k=False,
-                   rev_segments=None):
+                   cu_seqlens=None, impl=L.IMPL_AUTO, h_saved=None, primal_dtypes=False, rev_segments=None):
     """Run tops_b200_chunk_gla_bwd.  Returns (dq, dk, dv, dg, dh0).  `h_saved`
     is the scratch returned by chunk_fwd_call(want_saved=True) on the same inputs.
     With `primal_dtypes` the gradients come back in the dtypes of their primals
     (dq, dk as q, k; dg as the gate), as the reference's accelerator kernel
     writes them (`tops/ops/gla/chunk.py:1551-1554`): the tcgen05 kernel then
-    writes bf16 directly, any other kernel family writes fp32 and is cast.  `dg_sum_k` (tcgen05 kernels
-    only): `gate` is a scalar gate replicated over K and dg comes back summed over K, fp32 `[B,T,H]`."""
+    writes bf16 directly, any other kernel family writes fp32 and is cast.
+    A scalar gate's dg is fp32 `[B,T,H]` on every kernel family."""
     B, T, H, K = q.shape
     V = v.shape[-1]
     dev = q.device
@@ -90,9 +89,7 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
     dk = torch.empty(B, T, H, K, dtype=grad_dtype, device=dev)
     dv = torch.empty(B, T, H, V, dtype=do.dtype, device=dev)
     dg = None
-    if want_dg and dg_sum_k:
-        dg = torch.empty(B, T, H, dtype=torch.float32, device=dev)
-    elif want_dg and gate_kind == L.GATE_PER_CHANNEL:
+    if want_dg and gate_kind == L.GATE_PER_CHANNEL:
         dg = torch.empty(B, T, H, K, dtype=dg_dtype, device=dev)
     elif want_dg and gate_kind == L.GATE_SCALAR:
         dg = torch.empty(B, T, H, dtype=torch.float32, device=dev)
@@ -102,7 +99,6 @@ def chunk_bwd_call(q, k, v, gate, gate_kind, scale, h0, do, dht, chunk, grad_dty
     p.dq, p.dk, p.dv, p.dg, p.dh0 = L.ptr(dq), L.ptr(dk), L.ptr(dv), L.ptr(dg), L.ptr(dh0)
     p.grad_dtype = L.dtype_code(grad_dtype)
     p.dg_dtype = L.dtype_code(dg_dtype)
-    p.dg_sum_k = int(dg_sum_k)
     if h_saved is not None:
         assert h_saved.dtype == q.dtype and h_saved.shape[-3:] == (H, K, V)
         p.h_saved = L.ptr(h_saved)

@@ -177,6 +177,32 @@ def _chunk_bwd_call(q, k, v, g, beta, do, scale, dht, saved, want_dh0, grad_dtyp
     return dq, dk, dv, dg, dbeta, dh0
 
 
+@L.on_tensor_device
+def _chunk_bwd_state_gradient(q, k, v, g, beta, do, scale, dht, saved):
+    """The state-gradient-only form of tops_b200_chunk_kda_bwd: the reverse scan alone.  Returns dh0 fp32
+    `[B,H,K,V]` (for `dht = None`: the shard summary D of a time-sharded sequence)."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    dev = q.device
+    q, k, v, g = q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous()
+    beta_c = beta.to(q.dtype).contiguous()
+    do = do.to(q.dtype).contiguous()
+    dhtc = None if dht is None else dht.float().contiguous()
+    dv = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    dh0 = torch.empty(B, H, K, V, dtype=torch.float32, device=dev)
+    p = L.ChunkKdaBwdParams()
+    p.B, p.T, p.H, p.K, p.V, p.chunk = B, T, H, K, V, 64
+    p.dtype, p.gate_dtype, p.scale = L.dtype_code(q.dtype), L.dtype_code(g.dtype), float(scale)
+    p.q, p.k, p.v, p.g, p.beta, p.do_, p.dht = (L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta_c), L.ptr(do),
+                                                L.ptr(dhtc))
+    p.saved_h, p.saved_vnew, p.saved_T, p.saved_R = (L.ptr(t) for t in saved)
+    p.dv, p.dh0 = L.ptr(dv), L.ptr(dh0)
+    p.grad_dtype = L.F32
+    ws = L.workspace(L.lib.tops_b200_chunk_kda_bwd_workspace_bytes(C.byref(p)), dev)
+    L.check(L.lib.tops_b200_chunk_kda_bwd(C.byref(p), ws.data_ptr(), ws.numel(), L.stream_ptr(dev)), "chunk_kda_bwd")
+    return dh0
+
+
 def chunk_kda_bwd(q, k, v, g, beta, do, scale=None, initial_state=None, dht=None, chunk_size=64):
     """Explicit chunked backward (reference `tops/cpu/ops/kda/chunk_bwd.py:525-668`) for problems the
     tensor-core kernels take: recomputes the forward's residuals, then the three backward kernels.

@@ -51,24 +51,12 @@ def _cu(cu_seqlens):
     return None if cu_seqlens is None else [int(x) for x in cu_seqlens]
 
 
-def _tensor_core_shape(q, v, g, g_gamma, cu_seqlens, chunk_size):
-    """True when the tcgen05 kernels serve this scalar-gate problem (their scalar-gate form: the gate
-    rides on the exponent pattern, nothing is replicated over K; dg comes back summed over K)."""
-    return (g is not None and g_gamma is None and cu_seqlens is None and chunk_size == 64
-            and q.dtype == torch.bfloat16 and g.dtype == torch.bfloat16
-            and q.shape[-1] == 128 and v.shape[-1] == 128 and q.shape[1] % 64 == 0)
-
-
-def _expand_gate(g, K):
-    return g.unsqueeze(-1).expand(*g.shape, K).contiguous()
-
-
 def _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, want_saved):
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
     o, ht, _, _, saved = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
                                         _cu(cu_seqlens), want_saved=want_saved)
-    return o, ht, ((saved, None) if want_saved else None)
+    return o, ht, saved
 
 
 def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size=64,
@@ -80,12 +68,11 @@ def chunk_simple_gla_fwd(q, k, v, g, g_gamma, scale, initial_state, output_final
 
 
 def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chunk_size=64, cu_seqlens=None,
-                         h_saved=None, gate_k=None):
+                         h_saved=None):
     """Backward orchestrator (reference `tops/cpu/ops/simple_gla/chunk.py:668-788`).
     Returns (dq, dk in the input dtype, dv in do.dtype, dg fp32 `[B,T,H]` or
     None, dh0 fp32 or None).  `h_saved`: the chunk-start states the tcgen05
-    forward kept (None recomputes them, as the reference does); `gate_k`: the gate replicated over K
-    that forward made (None makes it again)."""
+    forward kept (None recomputes them, as the reference does)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
     return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
@@ -96,17 +83,16 @@ class _ChunkSimpleGLA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, g, g_gamma, initial_state, scale, output_final_state, cu, chunk_size):
         keep = any(t is not None and t.requires_grad for t in (q, k, v, g, initial_state))
-        o, ht, kept = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu, keep)
-        hs, gate_k = kept if kept is not None else (None, None)
-        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state, hs, gate_k)
+        o, ht, hs = _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu, keep)
+        ctx.save_for_backward(q, k, v, g, g_gamma, initial_state, hs)
         ctx.scale, ctx.cu, ctx.chunk = scale, cu, chunk_size
         return o, ht
 
     @staticmethod
     def backward(ctx, do, dht):
-        q, k, v, g, g_gamma, h0, hs, gate_k = ctx.saved_tensors
+        q, k, v, g, g_gamma, h0, hs = ctx.saved_tensors
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(q, k, v, g, g_gamma, h0, do.to(q.dtype), dht, ctx.scale, ctx.chunk,
-                                                   ctx.cu, h_saved=hs, gate_k=gate_k)
+                                                   ctx.cu, h_saved=hs)
         # a constant decay gets a zero cotangent, as in the reference (tops/ops/simple_gla/chunk.py:764)
         if L.CHECK_DEVICE:
             L.raise_on_device_error("chunk_simple_gla backward")

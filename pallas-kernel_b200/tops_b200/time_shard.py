@@ -133,9 +133,6 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
         gc = common.chunk_local_cumsum(g, C)
         return dict(g=gc) if g.ndim == 3 else dict(gk=gc)
 
-    def per_channel(g, K):
-        return g if g.ndim == 4 else g.unsqueeze(-1).expand(*g.shape, K).contiguous()
-
     def pack_problem(x, y, g):
         B, T, H, K = x.shape
         pb = common.make_problem(B, T, H, K, y.shape[-1], C, L.dtype_code(x.dtype), L.dtype_code(g.dtype),
@@ -144,13 +141,10 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
               and L.lib.tops_b200_chunk_selected_impl(C_.byref(pb)) == L.IMPL_SM100)
         return pb if ok else None
 
-    # What one shard's calls share: the gate replicated over K (scalar gates) and the workspaces the two
+    # What one shard's calls share: the chunk-start states its forward kept and the workspaces the two
     # pack calls leave behind (the time segments' summaries), which the forward / backward of the same
     # shard take back so that they do not scan the shard a third time.
     kept = {}
-
-    def gate_k(g, K):   # the kernels take scalar gates as they are
-        return g.contiguous()
 
     def kind_of(g):
         return L.GATE_PER_CHANNEL if g.ndim == 4 else L.GATE_SCALAR
@@ -164,7 +158,7 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
             pb.scale = float(scale)
             B, T, H, K = x.shape
             x, y = x.contiguous(), y.contiguous()
-            gk = gate_k(g, K)
+            gk = g.contiguous()
             out = torch.empty(B, H, K, y.shape[-1], dtype=torch.float32, device=x.device)
             p = L.StatePackParams()
             p.pb, p.reverse, p.x, p.g, p.y, p.state_out = pb, int(reverse), L.ptr(x), L.ptr(gk), L.ptr(y), L.ptr(out)
@@ -213,7 +207,7 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
     if kind == "simple_gla":
         def fwd(q, k, v, g, scale, h_in):
             if fast(q, v, g):   # the tcgen05 kernels in their scalar-gate form, segment summaries reused
-                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, gate_k(g, q.shape[-1]), kind_of(g), scale, h_in,
+                o, ht, _, _, hs = _chunk.chunk_fwd_call(q, k, v, g, kind_of(g), scale, h_in,
                                                         True, C, want_saved=True, segments=segments("fwd", k))
                 kept["hs"] = (q.data_ptr(), hs)
                 return o, ht
@@ -223,7 +217,7 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
             if fast(q, v, g):
                 hs = kept.get("hs")
                 hs = hs[1] if hs is not None and hs[0] == q.data_ptr() else None
-                return _chunk.chunk_bwd_call(q, k, v, gate_k(g, q.shape[-1]), kind_of(g), scale, h_in, do, dh_out,
+                return _chunk.chunk_bwd_call(q, k, v, g, kind_of(g), scale, h_in, do, dh_out,
                                              C, q.dtype, True, True, h_saved=hs, rev_segments=segments("rev", q))
             return simple_gla.chunk_simple_gla_bwd(q, k, v, g, None, h_in, do, dh_out, scale, C)
     else:
@@ -244,3 +238,100 @@ def cuda_ops(kind: str = "simple_gla", chunk_size: int = 64) -> LocalOps:
                                              True, True, h_saved=hs, rev_segments=segments("rev", q))
             return gla.chunk_gla_bwd(q, k, v, g, None, scale, h_in, None, None, do, dh_out, C)
     return LocalOps(end_state, grad_start, fwd, bwd, fold)
+
+
+# ---------------------------------------------------------------------------------------------------
+# KDA: the delta rule's transition is not diagonal.  A shard acts on an incoming state as
+#     h_out = M_r h_in + S_r,     M_r [B,H,K,K] dense,
+# and on the state gradient leaving it as  dh_in = M_r^T dh_out + D_r  (the reverse scan is linear in dh and
+# its coefficients depend on q, k, g, beta only).  M_r is what the ordinary forward returns as final state
+# for v = 0 and initial_state = I (V = K), so no extra kernel is needed; the exchange is one all-gather of
+# (M_r, S_r) forward and one of D_r backward, 2 MiB per tensor and rank at H = 32, K = V = 128.
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class KdaLocalOps:
+    """The single-device KDA ops a rank applies to its shard.
+    transition(k, g, beta) -> M [B,H,K,K] fp32
+    end_state(k, v, g, beta) -> S [B,H,K,V] fp32: state after the shard from a zero start
+    fwd(q, k, v, g, beta, scale, h_in) -> (o, kept): kept is whatever `grad_start` / `bwd` want back
+    grad_start(q, k, v, g, beta, scale, h_in, do, kept) -> D [B,H,K,V] fp32: dh0 of the shard for dht = 0
+    bwd(q, k, v, g, beta, scale, h_in, do, dh_out, kept) -> (dq, dk, dv, dg, dbeta)
+    """
+    transition: Callable
+    end_state: Callable
+    fwd: Callable
+    grad_start: Callable
+    bwd: Callable
+
+
+def kda_fold_left(Ms, Ss, h0, rank):
+    """State entering rank `rank`: h0 pushed through the affine maps of ranks 0 .. rank-1."""
+    h = torch.zeros_like(Ss[0]) if h0 is None else _acc(h0).clone()
+    for s in range(rank):
+        h = Ms[s] @ h + Ss[s]
+    return h
+
+
+def kda_fold_right(Ms, Ds, dht, rank):
+    """State gradient leaving rank `rank` on its right: dht pulled back through ranks R-1 .. rank+1."""
+    d = torch.zeros_like(Ds[0]) if dht is None else _acc(dht).clone()
+    for s in range(len(Ds) - 1, rank, -1):
+        d = Ms[s].transpose(-1, -2) @ d + Ds[s]
+    return d
+
+
+def kda_forward(ops: KdaLocalOps, q, k, v, g, beta, scale, initial_state=None, group=None):
+    """Forward of this rank's time shard of ONE KDA sequence (K = V).  Returns
+    (o_shard, final_state_of_the_whole_sequence, ctx); ctx goes to kda_backward."""
+    assert q.shape[-1] == v.shape[-1], "the transition is obtained from a forward with V = K"
+    rank = dist.get_rank(group)
+    M = _acc(ops.transition(k, g, beta))
+    S = _acc(ops.end_state(k, v, g, beta))
+    Ms, Ss = _gather(M, group), _gather(S, group)
+    h_in = kda_fold_left(Ms, Ss, initial_state, rank)
+    final = kda_fold_left(Ms, Ss, initial_state, len(Ss))
+    o, kept = ops.fwd(q, k, v, g, beta, scale, h_in)
+    return o, final, dict(Ms=Ms, h_in=h_in, kept=kept)
+
+
+def kda_backward(ops: KdaLocalOps, q, k, v, g, beta, scale, ctx, do, dht=None, group=None):
+    """Backward of this rank's time shard.  Returns (dq, dk, dv, dg, dbeta of the shard, dh0 of the whole
+    sequence)."""
+    rank = dist.get_rank(group)
+    Ms, h_in, kept = ctx["Ms"], ctx["h_in"], ctx["kept"]
+    D = _acc(ops.grad_start(q, k, v, g, beta, scale, h_in, do, kept))
+    Ds = _gather(D, group)
+    dh_out = kda_fold_right(Ms, Ds, dht, rank)
+    dh0 = kda_fold_right(Ms, Ds, dht, -1)
+    dq, dk, dv, dg, dbeta = ops.bwd(q, k, v, g, beta, scale, h_in, do, dh_out, kept)
+    return dq, dk, dv, dg, dbeta, dh0
+
+
+def kda_cuda_ops() -> KdaLocalOps:
+    """KdaLocalOps on the chunked tcgen05 KDA kernels (bf16 q/k/v/g, K = V = 128, whole chunks of 64)."""
+    from .ops import kda as K_
+
+    def eye_like(k):
+        B, _, H, K = k.shape
+        return torch.eye(K, dtype=torch.float32, device=k.device).expand(B, H, K, K).contiguous()
+
+    def transition(k, g, beta):
+        assert K_.chunk_kernels_take(k, k, k, g, beta, 64), "time-sharded KDA takes bf16, K = V = 128, T % 64 == 0"
+        _, M, _, _, _ = K_._chunk_fwd_call(k, k, torch.zeros_like(k), g, beta, 1.0, eye_like(k), True, 64, False, False)
+        return M
+
+    def end_state(k, v, g, beta):
+        _, S, _, _, _ = K_._chunk_fwd_call(k, k, v, g, beta, 1.0, None, True, 64, False, False)
+        return S
+
+    def fwd(q, k, v, g, beta, scale, h_in):
+        o, _, _, _, saved = K_._chunk_fwd_call(q, k, v, g, beta, scale, h_in, False, 64, False, True)
+        return o, saved
+
+    def grad_start(q, k, v, g, beta, scale, h_in, do, saved):
+        return K_._chunk_bwd_state_gradient(q, k, v, g, beta, do, scale, None, saved)
+
+    def bwd(q, k, v, g, beta, scale, h_in, do, dh_out, saved):
+        dq, dk, dv, dg, dbeta, _ = K_._chunk_bwd_call(q, k, v, g, beta, do, scale, dh_out, saved, False, q.dtype)
+        return dq, dk, dv, dg, dbeta
+    return KdaLocalOps(transition, end_state, fwd, grad_start, bwd)

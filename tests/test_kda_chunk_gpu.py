@@ -126,3 +126,42 @@ def test_chunk_kda_autograd_equals_explicit_backward_and_stage_oracle():
     assert_close("o", o.detach().float().cpu(), o_ref, BF16)
     for name, a, r in zip(("dq", "dk", "dv", "dg", "dbeta", "dh0"), (dq, dk, dv, dg, db, dh0), (rq, rk, rv, rg, rb, rh0)):
         assert_close(name, a.float().cpu(), r.float(), BF16)
+
+
+def test_kda_time_shards_chain_on_one_gpu():
+    """The pieces of time-sharded KDA without the collective: two halves of one sequence, each summarised as
+    h_out = M h_in + S (M from a forward with v = 0 and initial_state = I) and dh_in = M^T dh_out + D
+    (the state-gradient-only form of the backward call), folded by hand, against one pass of the CPU oracle."""
+    from oracle import kda as OK
+    from tops_b200 import _lib as L
+    from tops_b200 import time_shard as TS
+    from tops_b200.synth import make_inputs
+    B, T, H, K, V, R = 1, 512, 2, 128, 128, 2
+    x = make_inputs(72, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_grads=True, with_beta=True,
+                    l2norm_qk=True)
+    scale = K ** -0.5
+    ops = TS.kda_cuda_ops()
+    sls = [slice(r * T // R, (r + 1) * T // R) for r in range(R)]
+    sh = [{n: (t[:, s] if t.ndim >= 3 and t.shape[1] == T else t).cuda().contiguous() for n, t in x.items()}
+          for s in sls]
+    Ms = [ops.transition(c["k"], c["g"], c["beta"]) for c in sh]
+    Ss = [ops.end_state(c["k"], c["v"], c["g"], c["beta"]) for c in sh]
+    h_in = [TS.kda_fold_left(Ms, Ss, sh[0]["h0"], r) for r in range(R)]
+    final = TS.kda_fold_left(Ms, Ss, sh[0]["h0"], R)
+    fw = [ops.fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], scale, h_in[r]) for r, c in enumerate(sh)]
+    Ds = [ops.grad_start(c["q"], c["k"], c["v"], c["g"], c["beta"], scale, h_in[r], c["do"], fw[r][1])
+          for r, c in enumerate(sh)]
+    dh_out = [TS.kda_fold_right(Ms, Ds, sh[0]["dht"], r) for r in range(R)]
+    dh0 = TS.kda_fold_right(Ms, Ds, sh[0]["dht"], -1)
+    bw = [ops.bwd(c["q"], c["k"], c["v"], c["g"], c["beta"], scale, h_in[r], c["do"], dh_out[r], fw[r][1])
+          for r, c in enumerate(sh)]
+    torch.cuda.synchronize()
+    assert L.device_error() == 0
+    o_ref, ht_ref = OK.naive_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+    ref = OK.fused_recurrent_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
+    assert rel_l2(torch.cat([f[0] for f in fw], 1), o_ref) <= 2e-2
+    assert rel_l2(final, ht_ref) <= 2e-2
+    assert rel_l2(dh0, ref[5]) <= 2e-2
+    for i, name in enumerate(("dq", "dk", "dv", "dg", "dbeta")):
+        e = rel_l2(torch.cat([b[i] for b in bw], 1), ref[i])
+        assert e <= 2e-2, (name, e)

@@ -94,3 +94,72 @@ def test_fold_helpers():
     assert torch.allclose(fold_right(dec, st, h0, 1), h0)
     assert torch.allclose(fold_right(dec, st, h0, 0), h0 * math.exp(-0.25) + 2)
     assert torch.allclose(fold_right(dec, st, None, -1), torch.full((1, 1, 2, 2), 2 * math.exp(-0.5) + 1))
+
+
+def _oracle_kda_ops():
+    from oracle import kda as OK
+    from tops_b200.time_shard import KdaLocalOps
+
+    def transition(k, g, beta):
+        B, T, H, K = k.shape
+        eye = torch.eye(K, dtype=k.dtype).expand(B, H, K, K).contiguous()
+        return OK.naive_recurrent_kda(k, k, torch.zeros_like(k), g, beta, 1.0, eye, True)[1]
+
+    def end_state(k, v, g, beta):
+        return OK.naive_recurrent_kda(k, k, v, g, beta, 1.0, None, True)[1]
+
+    def fwd(q, k, v, g, beta, scale, h_in):
+        return OK.naive_recurrent_kda(q, k, v, g, beta, scale, h_in, False)[0], None
+
+    def grad_start(q, k, v, g, beta, scale, h_in, do, kept):
+        return OK.fused_recurrent_kda_bwd(q, k, v, g, beta, do, scale, h_in, None)[5]
+
+    def bwd(q, k, v, g, beta, scale, h_in, do, dh_out, kept):
+        return OK.fused_recurrent_kda_bwd(q, k, v, g, beta, do, scale, h_in, dh_out)[:5]
+    return KdaLocalOps(transition, end_state, fwd, grad_start, bwd)
+
+
+def _kda_worker(rank, world, port, out):
+    for p in (ROOT, os.path.join(ROOT, "pallas-kernel_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import kda as OK
+        from tops_b200 import time_shard as TS
+        torch.manual_seed(1)
+        B, T, H, K = 1, 24 * world, 2, 8
+        dt = torch.float64
+        q, k = torch.randn(B, T, H, K, dtype=dt), torch.randn(B, T, H, K, dtype=dt)
+        q, k = q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True)
+        v, do = torch.randn(B, T, H, K, dtype=dt), torch.randn(B, T, H, K, dtype=dt)
+        g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, dtype=dt)) / 4
+        beta = torch.sigmoid(torch.randn(B, T, H, dtype=dt))
+        h0, dht = 0.1 * torch.randn(B, H, K, K, dtype=dt), 0.1 * torch.randn(B, H, K, K, dtype=dt)
+        scale = K ** -0.5
+        ops = _oracle_kda_ops()
+        sl = slice(rank * T // world, (rank + 1) * T // world)
+        o, final, ctx = TS.kda_forward(ops, q[:, sl], k[:, sl], v[:, sl], g[:, sl], beta[:, sl], scale, h0)
+        got = TS.kda_backward(ops, q[:, sl], k[:, sl], v[:, sl], g[:, sl], beta[:, sl], scale, ctx, do[:, sl], dht)
+        o_ref, ht_ref = OK.naive_recurrent_kda(q, k, v, g, beta, scale, h0, True)
+        ref = OK.fused_recurrent_kda_bwd(q, k, v, g, beta, do, scale, h0, dht)
+        errs = [(o - o_ref[:, sl]).abs().max().item(), (final - ht_ref).abs().max().item(),
+                (got[5] - ref[5]).abs().max().item()]
+        errs += [(a - b[:, sl]).abs().max().item() for a, b in zip(got[:5], ref[:5])]
+        out[rank] = max(errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_time_sharded_kda_equals_single_pass(world):
+    """KDA's transition is dense: shards exchange (M, S) with h_out = M h_in + S forward and D with
+    dh_in = M^T dh_out + D backward; M comes from a forward with v = 0 and initial_state = I."""
+    mgr = mp.get_context("spawn").Manager()
+    out = mgr.dict()
+    port = 29800 + os.getpid() % 150 + world
+    mp.spawn(_kda_worker, args=(world, port, out), nprocs=world, join=True)
+    assert len(out) == world
+    for r in range(world):
+        assert out[r] < 1e-9, (r, out[r])

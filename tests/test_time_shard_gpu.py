@@ -60,3 +60,54 @@ def test_time_sharded_simple_gla_on_gpus(world):
     for r in range(world):
         for name, e in out[r].items():
             assert e <= 2e-2, (r, name, e)      # bf16 bar: relative L2
+
+
+def _kda_worker(rank, world, port, out):
+    for p in (ROOT, os.path.join(ROOT, "pallas-kernel_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle import kda as OK
+        from tests.util import rel_l2
+        from tops_b200 import _lib as L
+        from tops_b200 import time_shard as TS
+        from tops_b200.synth import make_inputs
+        B, T, H, K, V = 1, 256 * world, 2, 128, 128
+        x = make_inputs(71, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_grads=True, with_beta=True,
+                        l2norm_qk=True)
+        scale = K ** -0.5
+        sl = slice(rank * T // world, (rank + 1) * T // world)
+        c = {n: (t[:, sl] if t.ndim >= 3 and t.shape[1] == T else t).cuda().contiguous() for n, t in x.items()}
+        ops = TS.kda_cuda_ops()
+        o, final, ctx = TS.kda_forward(ops, c["q"], c["k"], c["v"], c["g"], c["beta"], scale, c["h0"])
+        dq, dk, dv, dg, dbeta, dh0 = TS.kda_backward(ops, c["q"], c["k"], c["v"], c["g"], c["beta"], scale, ctx,
+                                                     c["do"], c["dht"])
+        torch.cuda.synchronize()
+        assert L.device_error() == 0
+        o_ref, ht_ref = OK.naive_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+        r = OK.fused_recurrent_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
+        errs = {"o": rel_l2(o, o_ref[:, sl]), "ht": rel_l2(final, ht_ref), "dh0": rel_l2(dh0, r[5])}
+        for n, a, b in zip(("dq", "dk", "dv", "dg", "dbeta"), (dq, dk, dv, dg, dbeta), r[:5]):
+            errs[n] = rel_l2(a, b[:, sl])
+        out[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_time_sharded_kda_on_gpus(world):
+    """One KDA sequence split over ranks: the shards exchange their dense transitions and summaries
+    (NCCL all-gathers) and must reproduce one pass of the CPU oracle over the whole sequence."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mgr = mp.get_context("spawn").Manager()
+    out = mgr.dict()
+    mp.spawn(_kda_worker, args=(world, 29741, out), nprocs=world, join=True)
+    assert len(out) == world
+    for r in range(world):
+        for name, e in out[r].items():
+            assert e <= 2e-2, (r, name, e)      # bf16 bar: relative L2
