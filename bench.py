@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
                     [--scaling strong|weak] [--grads primal|fp32]
-                    [--workload gla_train|decode|simple_gla_long|kda]
+                    [--workload gla_train|decode|simple_gla_long|kda|kda_long]
 
 One "step" is one forward + backward pass of `chunk_gla` over one synthetic
 batch of the headline configuration (bf16, B=8, T=4096, H=16, K=V=128,
@@ -616,6 +616,14 @@ def simple_gla_bytes(B, T, H, K, V):
     return B * T * H * per_token_head + 4 * B * H * K * V * 4
 
 
+def kda_bytes(B, T, H, K, V):
+    """Every API tensor of a KDA forward + backward once, at the dtypes of the differentiable op (all bf16 but
+    the fp32 states): q, k, v, g, beta in, o out; q, k, v, g, beta, do in, dq, dk, dv, dg, dbeta out; h0, ht,
+    dht, dh0.  The residuals the forward keeps for the backward are not counted."""
+    per_token_head = (3 * 2 * K + 2 * V + 2 + 2 * V) + (3 * 2 * K + 2 * 2 * V + 2 + 3 * 2 * K + 2 * V + 2)
+    return B * T * H * per_token_head + 4 * B * H * K * V * 4
+
+
 def secondary(name, steps, seq):
     """One secondary workload (BASELINE configs[2..4]) on the current GPU, device-resident, through
     the public ops.  Returns a dict with ms_per_step, value, unit, algorithmic_bytes, frac, config."""
@@ -663,9 +671,9 @@ def secondary(name, steps, seq):
         out = {"metric": "simple_gla chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s",
                "config": {"workload": f"simple_gla fwd+bwd B=1 T={T} H=32 K=V=128 chunk 64 bf16, scalar bf16 gate, one GPU "
                                       "(BASELINE configs[3] without the time sharding)"}}
-    elif name == "kda":
+    elif name in ("kda", "kda_long"):
         from tops_b200.ops.kda import chunk_kda
-        B, T, H, K, V = 4, seq or 8192, 32, 128, 128
+        B, T, H, K, V = (4, seq or 8192, 32, 128, 128) if name == "kda" else (1, seq or 32768, 32, 128, 128)
         x = {k: v.cuda() for k, v in make_inputs(5, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_grads=True,
                                                    with_beta=True, l2norm_qk=True).items()}
         leaves = [x[n].requires_grad_(True) for n in ("q", "k", "v", "g", "beta", "h0")]
@@ -675,11 +683,10 @@ def secondary(name, steps, seq):
                               chunk_size=64)
             return torch.autograd.grad((o, ht), leaves, (x["do"], x["dht"]))
         ms = timed(step, max(2, min(steps, 5)), 2)
-        # q, k, v, g, beta in, o out; q, k, v, g, beta, do in, dq, dk, dv, dg, dbeta out; h0, ht, dht, dh0
-        nbytes = B * T * H * (4 * 2 * K + 2 + 2 * V) + B * T * H * (4 * 2 * K + 2 + 2 * V + 3 * 2 * K + 2 * V + 2) \
-            + 4 * B * H * K * V * 4
+        nbytes = kda_bytes(B, T, H, K, V)
         out = {"metric": "KDA chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s",
-               "config": {"workload": f"KDA fwd+bwd B=4 T={T} H=32 K=V=128 chunk 64 bf16, one GPU (BASELINE configs[4])"}}
+               "config": {"workload": f"KDA fwd+bwd B={B} T={T} H=32 K=V=128 chunk 64 bf16, one GPU"
+                                      + (" (BASELINE configs[4])" if name == "kda" else "")}}
     else:
         raise ValueError(name)
     L.lib.tops_b200_profile_enable(0)
@@ -701,7 +708,9 @@ def secondary(name, steps, seq):
 def run_time_shard(args):
     """`--workload simple_gla_long --gpus N`: BASELINE configs[3], ONE sequence of 65536 tokens sharded
     over time across N ranks.  A step is forward + backward of every shard, with one all-gather of the shard
-    summaries (fp32 [B,H,K,V] + the summed gates) per direction; strong scaling (the sequence is fixed)."""
+    summaries (fp32 [B,H,K,V] + the summed gates) per direction; strong scaling (the sequence is fixed).
+    `--workload kda_long --gpus N`: the same for ONE KDA sequence (B=1, T=32768, H=32), whose shards exchange
+    their dense transitions [B,H,K,K] as well (no BASELINE configuration: KDA there shards over batch x head)."""
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -711,14 +720,19 @@ def run_time_shard(args):
     from tops_b200 import _lib as L
     from tops_b200 import time_shard as TS
     from tops_b200.synth import make_inputs
-    B, T, H, K, V, C = 1, args.seq or 65536, 32, 128, 128, 64
+    kda = args.workload == "kda_long"
+    B, T, H, K, V, C = 1, args.seq or (32768 if kda else 65536), 32, 128, 128, 64
     assert T % (world * C) == 0
-    full = make_inputs(4, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
+    if kda:
+        full = make_inputs(5, B, T, H, K, V, dtype=torch.bfloat16, with_h0=True, with_grads=True, with_beta=True,
+                           l2norm_qk=True)
+    else:
+        full = make_inputs(4, B, T, H, K, V, dtype=torch.bfloat16, gate="scalar", with_h0=True, with_grads=True)
     sl = slice(rank * T // world, (rank + 1) * T // world)
     x = {n: (t[:, sl] if t.ndim >= 3 and t.shape[1] == T else t).contiguous().to(dev) for n, t in full.items()}
     del full
     scale = K ** -0.5
-    ops = TS.cuda_ops("simple_gla", C)
+    ops = TS.kda_cuda_ops() if kda else TS.cuda_ops("simple_gla", C)
     # the exchange alone, timed with its own events inside the step
     ev = []
 
@@ -734,6 +748,9 @@ def run_time_shard(args):
     TS._gather = timed_gather
 
     def step():
+        if kda:
+            o, final, ctx = TS.kda_forward(ops, x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"])
+            return TS.kda_backward(ops, x["q"], x["k"], x["v"], x["g"], x["beta"], scale, ctx, x["do"], x["dht"])
         o, final, h_in = TS.forward(ops, x["q"], x["k"], x["v"], x["g"], scale, x["h0"])
         return TS.backward(ops, x["q"], x["k"], x["v"], x["g"], scale, h_in, x["do"], x["dht"])
 
@@ -761,8 +778,22 @@ def run_time_shard(args):
     err = L.device_error()
     assert err == 0, f"a kernel gave up on a bounded wait (code {err})"
     hbm_peak, _, peak_kind = measured_peaks()
-    nbytes = simple_gla_bytes(B, T, H, K, V)
-    if rank == 0:
+    nbytes = kda_bytes(B, T, H, K, V) if kda else simple_gla_bytes(B, T, H, K, V)
+    if rank == 0 and kda:
+        print(json.dumps({
+            "metric": "KDA chunk fwd+bwd tokens/s, one sequence sharded over time", "value": B * T / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"KDA fwd+bwd B=1 T={T} H=32 K=V=128 chunk 64 bf16, {T // world} tokens per GPU",
+                       "exchange": "NCCL all-gathers of fp32 [B,H,K,K] transitions and [B,H,K,V] summaries forward, "
+                                   "[B,H,K,V] summaries backward, NVLS off",
+                       "extra_passes": "per shard: two forward passes for the transition and the summary, one reverse "
+                                       "scan for the backward summary"},
+            "exchange_ms_per_step": ms_x, "exchange_share": ms_x / ms,
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9 / world, "peak": hbm_peak, "unit": "GB/s per GPU",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / world / hbm_peak, "peak_source": peak_kind},
+            "gpu_launches": int(L.launch_count() - n0), "clocks": clocks.summary(), "device_error": err}), flush=True)
+    elif rank == 0:
         print(json.dumps({
             "metric": "simple_gla chunk fwd+bwd tokens/s, one sequence sharded over time", "value": B * T / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
@@ -798,7 +829,7 @@ def main():
                     help="dtype of dq, dk, dg in the timed step: the primal dtypes (bf16) or fp32")
     ap.add_argument("--batch", type=int, default=0, help="override B (profiler captures on a smaller case)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timed steps only, short JSON")
-    ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda"],
+    ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda", "kda_long"],
                     help="gla_train is the headline metric; the others are secondary one-GPU measurements")
     ap.add_argument("--seq", type=int, default=0, help="override T of a secondary workload")
     args = ap.parse_args()
@@ -810,7 +841,7 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "simple_gla_long" and int(os.environ.get("WORLD_SIZE", 1)) > 1:
+    elif args.workload in ("simple_gla_long", "kda_long") and int(os.environ.get("WORLD_SIZE", 1)) > 1:
         run_time_shard(args)
     elif args.workload != "gla_train":
         run_extra(args)
