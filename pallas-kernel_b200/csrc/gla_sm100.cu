@@ -366,14 +366,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
 // state from a zero start.  Forward order for states, reverse order for state gradients.
 //   first [BH,K,V] or null;  P [BH,nseg,K];  S [BH,nseg,K,V];  start [BH,nseg,K,V] (out);  last [BH,K,V] or null (out)
 template <bool REVERSE>
-__global__ void k_join_segments(const float* first, const float* P, const float* S, float* start, float* last,
-                                int nseg) {
+__global__ void k_join_segments(const float* __restrict__ first, const float* __restrict__ P, const float* __restrict__ S,
+                                float* __restrict__ start, float* __restrict__ last, int nseg) {
   // grid (batch x head, slices): a block chains one slice of the K x V elements of one (batch, head)
+  // (the loads of a step do not depend on the chain: unrolled, they are all in flight together)
   const int bh = blockIdx.x;
   const int span = D * D / gridDim.y;
   for (int e = blockIdx.y * span + threadIdx.x * 4; e < (blockIdx.y + 1) * span; e += blockDim.x * 4) {
     const int k = e / D;
     float4 cur = first ? *reinterpret_cast<const float4*>(first + (size_t)bh * D * D + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
     for (int i = 0; i < nseg; ++i) {
       const int r = REVERSE ? nseg - 1 - i : i;
       const size_t sb = ((size_t)bh * nseg + r) * D * D + e;
@@ -1168,52 +1170,58 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
   } else if (warp == 20) {
     // ------------------------------------------------------------------ tensor-core issue
     if (lane == 0) {
-      // descriptors of contraction step 0 of every operand, built once (see kmajor_step)
       const uint32_t ga = smem_u32(gs), mma = smem_u32(mtm), va = smem_u32(vs), doa = smem_u32(dos), ha = smem_u32(hs),
                      dha = smem_u32(dhs), pa = smem_u32(Ps), daa = smem_u32(dAs);
-      const uint64_t pat128_k = desc_kmajor(mma, 128, 0, 0), pat64_k = desc_kmajor(mma, 64, 0, 0);
-      const uint64_t g_mn = desc_mnmajor(ga, 64, 0, 0);
-      // (q~, k~ have two slots, TILE64 bytes apart: slot(it) moves a descriptor to the chunk's slot)
-      const uint64_t q_k = desc_kmajor(smem_u32(qs), 64, 0, 0), k_k = desc_kmajor(smem_u32(ks), 64, 0, 0);
-      const uint64_t q_mn = desc_mnmajor(smem_u32(qs), 64, 0, 0), k_mn = desc_mnmajor(smem_u32(ks), 64, 0, 0);
-      auto slot = [](int it) { return (uint64_t)((it & 1) * (TILE64 >> 4)); };
-      const uint64_t do_k = desc_kmajor(doa, 64, 0, 0), do_mn = desc_mnmajor(doa, 64, 0, 0), v_k = desc_kmajor(va, 64, 0, 0);
-      const uint64_t h_k = desc_kmajor(ha, 128, 0, 0), dh_k = desc_kmajor(dha, 128, 0, 0), dh_mn = desc_mnmajor(dha, 128, 0, 0);
-      const uint64_t p_mn = desc_mnmajor(pa, 64, 0, 0), da_k = desc_kmajor(daa, 64, 0, 0), da_mn = desc_mnmajor(daa, 64, 0, 0);
       auto issue_gate = [&](int it) {
-        // G - mid, [time (repeated)][channel]
-        umma_product<C / 16, false>(tm + cEm, pat128_k, g_mn, umma_idesc(128, 128, 0, 1), KStep<128>{}, MnStep{});
-        // G - mid, [channel][time]
-        umma_product<C / 16, false>(tm + cET + 64 * (it & 1), g_mn, pat64_k, umma_idesc(128, 64, 1, 0), MnStep{}, KStep<64>{});
+#pragma unroll
+        for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [time (repeated)][channel]
+          umma_bf16(tm + cEm, desc_kmajor(mma, 128, 0, j0), desc_mnmajor(ga, 64, j0, 0), umma_idesc(128, 128, 0, 1), j0 > 0);
+#pragma unroll
+        for (int j0 = 0; j0 < C; j0 += 16)   // G - mid, [channel][time]
+          umma_bf16(tm + cET + 64 * (it & 1), desc_mnmajor(ga, 64, j0, 0), desc_kmajor(mma, 64, 0, j0),
+                    umma_idesc(128, 64, 1, 0), j0 > 0);
         umma_commit(&bar_gate);
       };
-      auto issue_A = [&](int it) {   // A[i][j] = q~ k~^T
-        umma_product<D / 16, false>(tm + cA, q_k + slot(it), k_k + slot(it), umma_idesc(64, 64, 0, 0), KStep<64>{}, KStep<64>{});
+      auto issue_A = [&](int it) {
+        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // A[i][j] = q~ k~^T
+          umma_bf16(tm + cA, desc_kmajor(qta, 64, 0, k0), desc_kmajor(kta, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
       };
-      auto issue_dA = [&]() {        // dA[i][j] = do v^T
-        umma_product<D / 16, false>(tm + cdA, do_k, v_k, umma_idesc(64, 64, 0, 0), KStep<64>{}, KStep<64>{});
+      auto issue_dA = [&]() {
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dA[i][j] = do v^T
+          umma_bf16(tm + cdA, desc_kmajor(doa, 64, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(64, 64, 0, 0), k0 > 0);
         umma_commit(&bar_A);
       };
       // The gradient products in two groups.  The first needs neither A nor dA, so it starts as soon as
       // the chunk's tiles have landed, while the conversion warps still work on A and dA; after it dh'
       // and v are dead and the next chunk's are fetched.  The second group needs the converted operands.
       auto issue_inter = [&](int it) {
-        // dq_inter^T[k][i] = h' do^T
-        umma_product<D / 16, false>(tm + cdq, h_k, do_k, umma_idesc(128, 64, 0, 0), KStep<128>{}, KStep<64>{});
-        // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
-        umma_product<D / 16, false>(tm + cdk2, dh_k, v_k, umma_idesc(128, 64, 0, 0), KStep<128>{}, KStep<64>{});
-        // dv^T[v][j] = dh'^T k~^T
-        umma_product<D / 16, false>(tm + cdv, dh_mn, k_k + slot(it), umma_idesc(128, 64, 1, 0), MnStep{}, KStep<64>{});
+        const uint32_t kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dq_inter^T[k][i] = h' do^T
+          umma_bf16(tm + cdq, desc_kmajor(ha, 128, 0, k0), desc_kmajor(doa, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // (dk_inter exp(G - mid))^T[k][j] = dh' v^T
+          umma_bf16(tm + cdk2, desc_kmajor(dha, 128, 0, k0), desc_kmajor(va, 64, 0, k0), umma_idesc(128, 64, 0, 0), k0 > 0);
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16)   // dv^T[v][j] = dh'^T k~^T
+          umma_bf16(tm + cdv, desc_mnmajor(dha, 128, k0, 0), desc_kmajor(kta, 64, 0, k0), umma_idesc(128, 64, 1, 0), k0 > 0);
         umma_commit(&bar_r2);
       };
       auto issue_intra = [&](int it) {
-        // dv^T[v][j] += sum_i do[i][v] A[i][j]
-        umma_product<C / 16, true>(tm + cdv, do_mn, p_mn, umma_idesc(128, 64, 1, 1), MnStep{}, MnStep{});
+        const uint32_t qta = smem_u32(qs + (it & 1) * TILE64), kta = smem_u32(ks + (it & 1) * TILE64);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dv^T[v][j] += sum_i do[i][v] A[i][j]
+          umma_bf16(tm + cdv, desc_mnmajor(doa, 64, k0, 0), desc_mnmajor(pa, 64, k0, 0), umma_idesc(128, 64, 1, 1), 1);
         umma_commit(&bar_r1);                // h' and do are dead
-        // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
-        umma_product<C / 16, true>(tm + cdq, k_mn + slot(it), da_k, umma_idesc(128, 64, 1, 0), MnStep{}, KStep<64>{});
-        // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
-        umma_product<C / 16, false>(tm + cdk1, q_mn + slot(it), da_mn, umma_idesc(128, 64, 1, 1), MnStep{}, MnStep{});
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dq^T[k][i] += sum_j k~[j][k] dA[i][j]
+          umma_bf16(tm + cdq, desc_mnmajor(kta, 64, k0, 0), desc_kmajor(daa, 64, 0, k0), umma_idesc(128, 64, 1, 0), 1);
+#pragma unroll
+        for (int k0 = 0; k0 < C; k0 += 16)   // dk_intra^T[k][j] = sum_i q~[i][k] dA[i][j]
+          umma_bf16(tm + cdk1, desc_mnmajor(qta, 64, k0, 0), desc_mnmajor(daa, 64, k0, 0), umma_idesc(128, 64, 1, 1), k0 > 0);
         umma_commit(&bar_main);
       };
       bool ok = SCALAR || wait(&full_g, 0, 6);

@@ -122,16 +122,6 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// the same with the accumulate flag fixed at compile time (no predicate to set up at run time)
-template <bool ACC>
-__device__ __forceinline__ void umma_bf16_c(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
-      : "memory");
-}
 // Arrive on `bar` once every UMMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -252,29 +242,6 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_saddr, int rows, 
   uint32_t a = tile_saddr + (uint32_t)((mn0 >> 6) * rows * 128) + (uint32_t)k0 * 128;
   uint64_t lbo = (uint64_t)((rows * 128) >> 4) & 0x3FFF;
   return kDescBase | (uint64_t)((a & 0x3FFFF) >> 4) | (lbo << 16) | ((uint64_t)(1024 >> 4) << 32);
-}
-// A descriptor built once for (row 0, k 0) of a tile moves to contraction step k0 by adding a constant to its
-// address field (bits 0-13, in 16-byte units; shared-memory addresses stay below 2^18, so the field cannot carry
-// out).  The thread that issues the products of a kernel shares its scheduler with busy warps, so the handful of
-// integer instructions a descriptor costs is paid at every issue: build the bases once, add constants in the loops.
-__host__ __device__ constexpr uint64_t kmajor_step(int rows, int k0) {
-  return (uint64_t)(((k0 >> 6) * rows * 128 + (k0 & 63) * 2) >> 4);
-}
-__host__ __device__ constexpr uint64_t mnmajor_step(int k0) { return (uint64_t)((k0 * 128) >> 4); }
-template <int ROWS>
-struct KStep {
-  __device__ constexpr uint64_t operator()(int k0) const { return kmajor_step(ROWS, k0); }
-};
-struct MnStep {
-  __device__ constexpr uint64_t operator()(int k0) const { return mnmajor_step(k0); }
-};
-// One product D (+)= A B over a contraction of KSTEPS x 16 elements: A, B are descriptors of step 0 and
-// sa(k), sb(k) the constants that move them to step k (kmajor_step / mnmajor_step).
-template <int KSTEPS, bool ACC_FIRST, typename FA, typename FB>
-__device__ __forceinline__ void umma_product(uint32_t d_tmem, uint64_t a0, uint64_t b0, uint32_t idesc, FA sa, FB sb) {
-  umma_bf16_c<ACC_FIRST>(d_tmem, a0, b0, idesc);
-#pragma unroll
-  for (int k = 1; k < KSTEPS; ++k) umma_bf16_c<true>(d_tmem, a0 + sa(k * 16), b0 + sb(k * 16), idesc);
 }
 // instruction descriptor: bf16 x bf16 -> fp32, M x N, operand majors (0 = K, 1 = MN)
 __host__ __device__ constexpr uint32_t umma_idesc(int M, int N, int a_mn, int b_mn) {
