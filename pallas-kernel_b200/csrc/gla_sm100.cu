@@ -79,7 +79,7 @@ struct ScanParams {
 // state staging: 2 tiles.
 constexpr int SCAN_THREADS = NTHREADS + 32;
 struct ScanShared {
-  uint64_t fullg[3], fullxy[3], ebar[2], sbar[2];
+  uint64_t fullg[3], fullxy[5], ebar[2], sbar[2];
   uint32_t tmem_slot;
   int abort_flag;
   float gn[2][D], e0[2][D];   // row 63 (G_n) and row 0 of the exponent tile, per channel
@@ -88,8 +88,15 @@ struct ScanShared {
 // SCALAR: one gate per head and time step (simple_gla).  No gate tile is fetched and no exponent product is
 // issued: every compute warp keeps the 64 gates of the next chunk in registers and cumulates them with
 // shuffles (warp_cumulate), so a thread gates its 16 channels of x with one factor.
-template <bool BWD, bool SCALAR>
-__global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ ScanParams p) {
+// SUM (summary pass: no chunk-start states, zero start): only the state after the block's chunks is wanted,
+//     S = sum_c [prod_{c' after c} exp(G_n(c'))] D(c),
+// so the decay of all later chunks is folded into the gating of x (exponent + R, R the summed gates of the chunks
+// already done) and every state product accumulates into ONE tensor-memory tile: nothing of a chunk depends on
+// the chunk before it but the running sum R, the chain product -> register update -> next product is gone and a
+// chunk costs its gating and its products.  The chunks are walked from the far end (forward scan: last chunk
+// first; reverse scan: first chunk first), so that R is known when a chunk is gated.
+template <bool BWD, bool SCALAR, bool SUM>
+__global__ void __launch_bounds__(SCAN_THREADS, 1) k_scan(const __grid_constant__ ScanParams p) {
   // every shared object is carved from the dynamic allocation, whose start is 1024-byte aligned when the
   // kernel has no static shared memory (checked below: the swizzled tiles need that alignment)
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -113,8 +120,20 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     return;
   }
 
-  // chunk pp of this block (in scan order) within its sequence
-  auto chunk_of = [&](int pp) { return sg * NT + (BWD ? NT - 1 - pp : pp); };
+  // chunk pp of this block (in the order the block walks them) within its sequence
+  auto chunk_of = [&](int pp) { return sg * NT + ((BWD != SUM) ? NT - 1 - pp : pp); };
+  // SUM: summed gates of the chunks already done, per channel (two copies, written for the next chunk while the
+  // current one is read; in the place of e0, which a summary pass does not use) or, for scalar gates, in a
+  // register of every thread
+  float* const racc = &sh.e0[0][0];
+  float racc_s = 0.f;
+  // x / y stages: three; a summary pass, which is bound by how many bytes it keeps in flight, has two more in the
+  // state staging tiles it does not use
+  constexpr int NXY = SUM ? 5 : 3;
+  auto x_stage = [&](int pp) { const int st = pp % NXY; return st < 3 ? xs + st * TILE64 : hst + (st - 3) * 2 * TILE64; };
+  auto y_stage = [&](int pp) { const int st = pp % NXY; return st < 3 ? ys + st * TILE64 : hst + (st - 3) * 2 * TILE64 + TILE64; };
+  auto xy_bar = [&](int pp) { return &sh.fullxy[pp % NXY]; };
+  auto xy_parity = [&](int pp) { return (uint32_t)((pp / NXY) & 1); };
   auto chunk_row = [&](int pp) { return b * p.T + chunk_of(pp) * C; };
   auto issue_g = [&](int pp) {
     uint8_t* dst = gs + (pp % 3) * TILE64;
@@ -123,40 +142,46 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     tma_load_3d(dst + SLAB64, &p.mg, &sh.fullg[pp % 3], 64, h, chunk_row(pp));
   };
   auto issue_xy = [&](int pp) {
-    const int st = pp % 3;
-    mbar_expect_tx(&sh.fullxy[st], 2 * TILE64);
-    tma_load_3d(xs + st * TILE64, &p.mx, &sh.fullxy[st], 0, h, chunk_row(pp));
-    tma_load_3d(xs + st * TILE64 + SLAB64, &p.mx, &sh.fullxy[st], 64, h, chunk_row(pp));
-    tma_load_3d(ys + st * TILE64, &p.my, &sh.fullxy[st], 0, h, chunk_row(pp));
-    tma_load_3d(ys + st * TILE64 + SLAB64, &p.my, &sh.fullxy[st], 64, h, chunk_row(pp));
+    uint8_t *xd = x_stage(pp), *yd = y_stage(pp);
+    uint64_t* bar = xy_bar(pp);
+    mbar_expect_tx(bar, 2 * TILE64);
+    tma_load_3d(xd, &p.mx, bar, 0, h, chunk_row(pp));
+    tma_load_3d(xd + SLAB64, &p.mx, bar, 64, h, chunk_row(pp));
+    tma_load_3d(yd, &p.my, bar, 0, h, chunk_row(pp));
+    tma_load_3d(yd + SLAB64, &p.my, bar, 64, h, chunk_row(pp));
   };
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) { mbar_init(&sh.fullg[i], 1); mbar_init(&sh.fullxy[i], 1); }
+    for (int i = 0; i < 3; ++i) mbar_init(&sh.fullg[i], 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&sh.fullxy[i], 1);
     mbar_init(&sh.ebar[0], 1); mbar_init(&sh.ebar[1], 1); mbar_init(&sh.sbar[0], 1); mbar_init(&sh.sbar[1], 1);
     fence_barrier_init();
     tma_prefetch_desc(&p.mx); tma_prefetch_desc(&p.my);
     if (!SCALAR) tma_prefetch_desc(&p.mg);
     if (p.states) tma_prefetch_desc(&p.mst);
     sh.abort_flag = 0;
-    for (int c = 0; c < 3 && c < NT; ++c) {
+    for (int c = 0; c < 3 && c < NT; ++c)
       if (!SCALAR) issue_g(c);
-      issue_xy(c);
-    }
+    for (int c = 0; c < NXY && c < NT; ++c) issue_xy(c);
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
-  // SCALAR: the gates of time steps lane and lane + 32 of the next chunk to be gated
-  // (kept as loaded: the conversion, the first use of the loaded value, comes a chunk later)
-  __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
-  auto load_gates = [&](int c) {
-    const __nv_bfloat16* src = p.gscalar + (size_t)(chunk_row(c) + lane) * p.H + h;
-    greg_lo = src[0];
-    greg_hi = src[(size_t)32 * p.H];
-  };
+  // SCALAR: the gates of the next chunks, fetched three chunks ahead into this warp's ring (see GateRing; the
+  // rings take the place of the gate tiles, which scalar gates do not use)
+  GateRing gring;
+  const long long gidx0 = (long long)(chunk_row(0) + lane) * p.H + h;
+  const long long gstep = (long long)(chunk_row(NT > 1 ? 1 : 0) - chunk_row(0)) * p.H;   // +-64 H elements per chunk
+  auto gate_index = [&](int c) { return (size_t)(gidx0 + c * gstep); };
+  auto load_gates = [&](int c) { gring.prefetch(p.gscalar, c < NT, c < NT ? gate_index(c) : 0, (size_t)32 * p.H, c, lane); };
   if (SCALAR) {
-    if (!driver) load_gates(0);
+    if (!driver) {
+      gring.init(gs + warp * GateRing::kBytesPerWarp);
+      load_gates(0);
+      load_gates(1);
+      load_gates(2);
+    }
   } else {
     build_tri_tile(mt, 128, BWD ? TRI_INCL : TRI_REVN);
+    if (SUM && tid < 2 * D) racc[tid] = 0.f;
   }
   fence_async_smem();
   tc_fence_before();
@@ -179,19 +204,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     umma_commit(&sh.ebar[pp & 1]);
   };
   auto issue_state_mma = [&](int pp) {
-    const uint32_t xa = smem_u32(xs + (pp % 3) * TILE64), ya = smem_u32(ys + (pp % 3) * TILE64);
+    const uint32_t xa = smem_u32(x_stage(pp)), ya = smem_u32(y_stage(pp));
     tc_fence_after();
 #pragma unroll
-    for (int k0 = 0; k0 < C; k0 += 16)
-      umma_bf16(tm + cS + (pp & 1) * 128, desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0),
-                umma_idesc(128, 128, 1, 1), k0 > 0);
+    for (int k0 = 0; k0 < C; k0 += 16)   // (SUM: every chunk accumulates into the first tile)
+      umma_bf16(tm + cS + (SUM ? 0 : (pp & 1) * 128), desc_mnmajor(xa, 64, k0, 0), desc_mnmajor(ya, 64, k0, 0),
+                umma_idesc(128, 128, 1, 1), k0 > 0 || (SUM && pp > 0));
     umma_commit(&sh.sbar[pp & 1]);
   };
   // gate x of chunk pp in place and publish G_n (and G_n - G_0, or G_0) of its channels
   // (SCALAR: they are the same for every channel and stay in the registers gn_next, e0_next of every thread)
   float gn_next = 0.f, e0_next = 0.f;
   auto gate_chunk = [&](int pp) {
-    if ((!SCALAR && !mbar_wait(&sh.ebar[pp & 1], (pp >> 1) & 1)) || !mbar_wait(&sh.fullxy[pp % 3], (pp / 3) & 1)) {
+    if ((!SCALAR && !mbar_wait(&sh.ebar[pp & 1], (pp >> 1) & 1)) || !mbar_wait(xy_bar(pp), xy_parity(pp))) {
       *abort_flag = 1;
       fail(1);
     }
@@ -199,12 +224,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     const int i = (q4 * 32 + lane) & 63;          // time row of this thread
     const int cg = (q4 >> 1) * 4 + seg;           // its 16 channels
     if (SCALAR) {
-      const WarpGates w = warp_cumulate(__bfloat162float(greg_lo), __bfloat162float(greg_hi), lane);
+      float g_lo, g_hi;
+      gring.take(gate_index(pp), pp, lane, g_lo, g_hi);
+      const WarpGates w = warp_cumulate(g_lo, g_hi, lane);
       const float Gi = (q4 & 1) ? w.hi : w.lo;
       gn_next = w.gn;
       e0_next = BWD ? w.g0 : w.gn - w.g0;
-      const float f = BWD ? fast_exp(Gi) * p.scale : fast_exp(w.gn - Gi);
-      uint8_t* xt = xs + (pp % 3) * TILE64;
+      const float f = BWD ? fast_exp(Gi + racc_s) * p.scale : fast_exp(w.gn - Gi + racc_s);
+      if (SUM) racc_s += w.gn;
+      uint8_t* xt = x_stage(pp);
       const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -220,18 +248,26 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     if (i == 63) {
 #pragma unroll
       for (int t = 0; t < 16; ++t) sh.gn[pp & 1][cg * 16 + t] = e[t];
+      if (SUM) {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) racc[((pp + 1) & 1) * D + cg * 16 + t] = racc[(pp & 1) * D + cg * 16 + t] + e[t];
+      }
       if (!BWD) {
 #pragma unroll
         for (int t = 0; t < 16; ++t) e[t] = 0.f;   // row 63 of TRI_REVN carries G_n, its own exponent is 0
       }
     }
-    if (i == 0) {   // forward: G_n - G_0; reverse: G_0
+    if (i == 0 && !SUM) {   // forward: G_n - G_0; reverse: G_0 (for the scale of the stored states)
 #pragma unroll
       for (int t = 0; t < 16; ++t) sh.e0[pp & 1][cg * 16 + t] = e[t];
     }
+    if (SUM) {
+#pragma unroll
+      for (int t = 0; t < 16; ++t) e[t] += racc[(pp & 1) * D + cg * 16 + t];
+    }
 #pragma unroll
     for (int t = 0; t < 16; ++t) e[t] = BWD ? fast_exp(e[t]) * p.scale : fast_exp(e[t]);
-    uint8_t* xt = xs + (pp % 3) * TILE64;
+    uint8_t* xt = x_stage(pp);
     const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -278,9 +314,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
         }
         if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
         if (!SCALAR && pp + 4 < NT) issue_g(pp + 4);   // the stage of chunk pp+1, whose exponent product is complete
-        if (pp + 3 < NT) {                         // the x/y stage of chunk pp is free once its state product is done
+        if (pp + NXY < NT) {                       // the x/y stage of chunk pp is free once its state product is done
           if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
-          if (pp + 3 != p.skip_xy) issue_xy(pp + 3);
+          if (pp + NXY != p.skip_xy) issue_xy(pp + NXY);
         }
       }
       __syncwarp();
@@ -300,7 +336,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
     }
     float gtot = 0.f;   // summed log-gates of this thread's channel over the block's chunks
     gate_chunk(0);
-    if (SCALAR && NT > 1) load_gates(1);
+    if (SCALAR) load_gates(3);
     bool ok = !__syncthreads_or(*abort_flag);
     float decay = 1.f, hscale = 1.f, gn_cur = 0.f;   // of the chunk whose state product comes next
     if (ok) {
@@ -329,11 +365,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
         decay_n = fast_exp(gn_n);
         hscale_n = state_scale(pp + 1);
       }
-      // (the gates of the chunk gated in the next iteration: fetched where the thread waits anyway)
-      if (SCALAR && pp + 2 < NT) load_gates(pp + 2);
+      if (SCALAR) load_gates(pp + 4);
+      // (SUM: the wait only keeps this thread within one phase of the barrier; the product was issued a chunk ago)
       if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
       tc_fence_after();
-      {
+      if (!SUM) {
         float d[32];
         tmem_ld32(tmem_addr(tm, lane_base, cS + (pp & 1) * 128 + seg * 32), d);
 #pragma unroll
@@ -343,6 +379,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_scan(const __grid_constant__ S
       decay = decay_n;
       hscale = hscale_n;
       gn_cur = gn_n;
+    }
+    if (SUM && ok) {   // every product has completed: the accumulated tile is the state after the block's chunks
+      tc_fence_after();
+      tmem_ld32(tmem_addr(tm, lane_base, cS + seg * 32), S);
+      tc_fence_before();
     }
     if (ok && p.s_final) {
       float* dst = p.s_final + ((size_t)blk * D + col) * D + seg * 32;
@@ -434,7 +475,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) k_fwd_o(const __grid_constant__ F
   __syncwarp();
   if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
   __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;   // SCALAR: the gates of time steps lane and lane + 32
-  if (SCALAR) {
+  if (SCALAR) {   // (one chunk per block: the loads have the whole tile fetch to land)
     const __nv_bfloat16* src = p.gscalar + (size_t)(row + lane) * p.H + h;
     greg_lo = src[0];
     greg_hi = src[(size_t)32 * p.H];
@@ -640,8 +681,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
   }
   __syncwarp();
   if (warp == 0) { tmem_alloc(&sh.tmem_slot, 512); tmem_relinquish(); }
-  // SCALAR: the gates of time steps lane and lane + 32 of the next chunk
-  // (kept as loaded: the conversion, the first use of the loaded value, comes a chunk later)
+  // SCALAR: the gates of time steps lane and lane + 32 of the next chunk, in registers, loaded right after the
+  // first barrier of the chunk before: a chunk is long enough here for the load to land before the loop's back
+  // edge (where a register with a load in flight stalls the warp; the state scans, whose chunks are short, use
+  // GateRing instead)
   __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
   auto load_gates = [&](int c) {
     const __nv_bfloat16* src = p.gscalar + (size_t)(b * p.T + (c0 + c) * C + lane) * p.H + h;
@@ -821,7 +864,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constan
       tc_fence_before();
       if (__syncthreads_or(*abort_flag)) { ok = false; break; }   // B1
       if (pp > 0) copy_out(pp - 1);   // staged before the barrier; the products of this chunk run meanwhile
-      if (SCALAR && pp + 1 < NT) load_gates(pp + 1);   // the next chunk's gates, fetched where the thread waits anyway
+      if (SCALAR && pp + 1 < NT) load_gates(pp + 1);
       // tril(A) scale -> bf16 operand in the (dead) gate tile
       if (!mbar_wait(&sh.abar, ph)) { *abort_flag = 1; fail(4); }
       tc_fence_after();
@@ -987,6 +1030,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) k_bwd_main(const __grid_consta
     // (32 q4 + lane) mod 64 and 16 channels
     // SCALAR: the gates of time steps lane and lane + 32 of the next chunk to be gated, and the factors
     // exp(G - mid), exp(mid - G) of time step (16 seg + lane) mod 32 + 32 (seg / 2) of the chunk gated last
+    // (in registers, loaded a chunk ahead: see the note in k_fwd_fused)
     __nv_bfloat16 greg_lo = __float2bfloat16(0.f), greg_hi = greg_lo;
     float fw_next = 1.f, rw_next = 1.f;
     auto load_gates = [&](int it) {
@@ -1367,12 +1411,16 @@ int run_scan(bool bwd, const tops_chunk_problem& pb, int nseg, const void* x, co
     kernel<<<grid, SCAN_THREADS, SCAN_SMEM, st>>>(sp);
     return post_launch();
   };
+  // no chunk-start states and a zero start: the summary form of the kernel
+  const bool sum = !states && !s0;
   if (bwd) {
     const char* label = states ? "sm100_bwd_dh" : "sm100_bwd_dh_summary";
-    return scalar ? launch(k_scan<true, true>, label) : launch(k_scan<true, false>, label);
+    if (sum) return scalar ? launch(k_scan<true, true, true>, label) : launch(k_scan<true, false, true>, label);
+    return scalar ? launch(k_scan<true, true, false>, label) : launch(k_scan<true, false, false>, label);
   }
   const char* label = states ? "sm100_fwd_h" : "sm100_fwd_h_summary";
-  return scalar ? launch(k_scan<false, true>, label) : launch(k_scan<false, false>, label);
+  if (sum) return scalar ? launch(k_scan<false, true, true>, label) : launch(k_scan<false, false, true>, label);
+  return scalar ? launch(k_scan<false, true, false>, label) : launch(k_scan<false, false, false>, label);
 }
 
 // Time segments per sequence.  The scans walk a sequence chunk by chunk with one block; when there are

@@ -91,6 +91,40 @@ __device__ __forceinline__ WarpGates warp_cumulate(float a, float b, int lane) {
   w.gn = __shfl_sync(0xffffffffu, b, 31);
   return w;
 }
+// The scalar gates of the chunks a warp will gate next.  They are fetched three chunks ahead with cp.async into a
+// small ring in shared memory that belongs to the warp (4 slots x 64 words; lane l owns the words of time steps l
+// and l + 32), never into registers: a register that a load in flight will write, carried around the chunk loop,
+// makes the warp wait for the load at the loop's back edge (measured: ~1000 cycles per chunk in every kernel that
+// did so).  The gates are bf16, cp.async moves 4-byte words: a lane copies the aligned word that holds its gate
+// and picks the half when it takes it.  One group is committed per chunk index, fetched or not, so that
+// `wait_group 2` at chunk c always means "chunk c has landed".
+struct GateRing {
+  static constexpr int kBytesPerWarp = 4 * 64 * 4;
+  uint32_t base = 0;
+  __device__ __forceinline__ void init(uint8_t* warp_area) { base = smem_u32(warp_area); }
+  // idx: element index of the gate of time step `lane` of chunk c in the [B,T,H] tensor; hi_off: elements to
+  // time step lane + 32 (an even number)
+  __device__ __forceinline__ void prefetch(const __nv_bfloat16* g, bool valid, size_t idx, size_t hi_off, int c, int lane) {
+    if (valid) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(g);
+      const uint32_t dst = base + (uint32_t)(((c & 3) * 64 + lane) * 4);
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(w + (idx >> 1)) : "memory");
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 128u), "l"(w + ((idx + hi_off) >> 1)) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  __device__ __forceinline__ void take(size_t idx, int c, int lane, float& lo, float& hi) {
+    asm volatile("cp.async.wait_group 2;" ::: "memory");
+    const uint32_t src = base + (uint32_t)(((c & 3) * 64 + lane) * 4);
+    uint32_t a, b;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(a) : "r"(src));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(b) : "r"(src + 128u));
+    const bool upper = (idx & 1) != 0;
+    lo = __uint_as_float(upper ? (a & 0xffff0000u) : (a << 16));
+    hi = __uint_as_float(upper ? (b & 0xffff0000u) : (b << 16));
+  }
+};
+
 // Sums 16 values per thread over the 32 lanes of a warp with 16 shuffles (a butterfly that halves the number of
 // live values at every step): on return lane l holds the warp's total of v[l & 15].
 __device__ __forceinline__ float warp_sum16(float (&v)[16], int lane) {
