@@ -66,18 +66,20 @@ struct ScanParams {
                            // bounded wait for it runs out and the kernel leaves through its error path
 };
 
-// One block per (batch, head): 16 compute warps and one driver warp.  The whole K x V state lives in
+// One block per (batch, head): 16 compute warps and two issuing warps.  The whole K x V state lives in
 // registers of the compute warps (thread (q4, lane, seg): row k = 32 q4 + lane, columns 32 seg .. + 31).
 // Software pipeline over the chunks p (in scan order), one block-wide barrier per chunk:
 //   compute warps, iteration p:  stage h'_p for its TMA store;  gate x(p+1) in place (its exponents
 //       were put in tensor memory two iterations ago);  barrier;  wait for the state product of
 //       chunk p;  state <- state * exp(G_n(p)) + D(p).
-//   driver thread, iteration p:  barrier;  state product of chunk p+1 -> accumulator (p+1)&1;  TMA store
-//       of h'_p;  exponent product of chunk p+3 -> exponent slot (p+1)&1;  TMA loads of x, y of chunk
-//       p+3 and g of chunk p+4.
+//   product thread, iteration p:  barrier;  state product of chunk p+1 -> accumulator (p+1)&1;  exponent
+//       product of chunk p+3 -> exponent slot (p+1)&1.
+//   copy thread, iteration p:  barrier;  TMA store of h'_p;  TMA loads of g of chunk p+4 and, once the state
+//       product of chunk p has completed, of x, y of chunk p+3.
 // No compute warp ever blocks on the issue of a product or a copy.  x/y and g tiles: 3 stages each;
 // state staging: 2 tiles.
-constexpr int SCAN_THREADS = NTHREADS + 32;
+constexpr int SCAN_THREADS = NTHREADS + 64;    // 16 compute warps, a warp that issues the products, a warp that issues the copies
+constexpr int FUSED_THREADS = NTHREADS + 32;   // 16 compute warps and one driver warp (splitting it made this kernel slower)
 struct ScanShared {
   uint64_t fullg[3], fullxy[5], ebar[2], sbar[2];
   uint32_t tmem_slot;
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_scan(const __grid_constant_
   ScanShared& sh = *reinterpret_cast<ScanShared*>(hst + 2 * TILE128);
   volatile int* abort_flag = &sh.abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool driver = warp == 16;
+  const bool driver = warp >= 16;   // warp 16 issues the products, warp 17 the copies
   const int q4 = warp & 3, seg = (warp >> 2) & 3, col = q4 * 32 + lane;
   const int blk = blockIdx.x, sg = blk % p.nseg, bh = blk / p.nseg, b = bh / p.H, h = bh % p.H;
   const int NT = p.NT;
@@ -285,8 +287,11 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_scan(const __grid_constant_
     return BWD ? fast_exp(0.5f * (gnv - e0)) : fast_exp(gnv - 0.5f * e0) * p.scale;
   };
 
-  if (driver) {
-    // ------------------------------------------------------------------ products and copies
+  if (warp == 16) {
+    // ------------------------------------------------------------------ products
+    // The two issuing threads run the same barriers as the compute warps and never wait for one another: the
+    // product thread's time is the tensor core's (an issue takes about as long as the product before it runs),
+    // the copy thread's is spent waiting for products to release tiles.
     if (lane == 0) {
       issue_gate_mma(0);
       if (NT > 1) issue_gate_mma(1);
@@ -295,24 +300,33 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_scan(const __grid_constant_
     if (ok && lane == 0) {
       issue_state_mma(0);
       if (NT > 2) issue_gate_mma(2);
-      if (!SCALAR && NT > 3) issue_g(3);    // into the stage of chunk 0, whose exponent product is complete
     }
     for (int pp = 0; ok && pp < NT; ++pp) {
-      // the store of chunk pp-1 has read its staging tile: after the barrier the compute warps may
-      // overwrite it (with the state of chunk pp+1)
-      if (lane == 0) tma_store_wait_read();
       // h'_pp is staged, chunk pp+1 is gated; every thread of the block sees the same verdict, so
       // all of them leave the loop at the same barrier
       if (__syncthreads_or(*abort_flag)) break;
       if (lane == 0) {
         if (pp + 1 < NT) issue_state_mma(pp + 1);
+        if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
+      }
+      __syncwarp();
+    }
+  } else if (warp == 17) {
+    // ------------------------------------------------------------------ copies
+    bool ok = !__syncthreads_or(*abort_flag);
+    if (ok && lane == 0 && !SCALAR && NT > 3) issue_g(3);    // into the stage of chunk 0, whose exponent product is complete
+    for (int pp = 0; ok && pp < NT; ++pp) {
+      // the store of chunk pp-1 has read its staging tile: after the barrier the compute warps may
+      // overwrite it (with the state of chunk pp+1)
+      if (lane == 0) tma_store_wait_read();
+      if (__syncthreads_or(*abort_flag)) break;
+      if (lane == 0) {
         if (keep_states) {
           const int hrow = ((b * (p.T / C) + chunk_of(pp)) * p.H + h) * D;
           tma_store_2d(&p.mst, hst + (pp & 1) * TILE128, 0, hrow);
           tma_store_2d(&p.mst, hst + (pp & 1) * TILE128 + TILE128 / 2, 64, hrow);
           tma_store_commit();
         }
-        if (pp + 3 < NT) issue_gate_mma(pp + 3);   // its exponent slot was read by the gating of chunk pp+1
         if (!SCALAR && pp + 4 < NT) issue_g(pp + 4);   // the stage of chunk pp+1, whose exponent product is complete
         if (pp + NXY < NT) {                       // the x/y stage of chunk pp is free once its state product is done
           if (!mbar_wait(&sh.sbar[pp & 1], (pp >> 1) & 1)) { *abort_flag = 1; fail(2); }
@@ -638,7 +652,7 @@ constexpr size_t FUSED_SMEM = 2 * FUSED_STAGE + 2 * TILE128 + 2 * SLAB64 + 2048 
 // SCALAR: no gate tile is fetched and no exponent product issued; every compute warp cumulates the chunk's 64
 // gates in registers (warp_cumulate), which gives its threads E of their time row, G_n and mid directly.
 template <bool SCALAR>
-__global__ void __launch_bounds__(SCAN_THREADS) k_fwd_fused(const __grid_constant__ FusedParams p) {
+__global__ void __launch_bounds__(FUSED_THREADS) k_fwd_fused(const __grid_constant__ FusedParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* in = smem;                         // 2 stages x (q, k, g, v)
   uint8_t* hst = in + 2 * FUSED_STAGE;        // 2 x (128 x 128) bf16: h' of the current chunk
@@ -1530,8 +1544,8 @@ int chunk_fwd(const tops_chunk_fwd_params& p, void* ws, size_t, cudaStream_t st)
     up.T = pb.T; up.H = pb.H; up.NT = NT / nseg; up.nseg = nseg; up.scale = pb.scale;
     if ((rc = opt_in_smem(k_fwd_fused<true>, FUSED_SMEM)) || (rc = opt_in_smem(k_fwd_fused<false>, FUSED_SMEM))) return rc;
     KernelScope ks("sm100_fwd_fused", st);
-    if (scalar) k_fwd_fused<true><<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
-    else k_fwd_fused<false><<<pb.B * pb.H * nseg, SCAN_THREADS, FUSED_SMEM, st>>>(up);
+    if (scalar) k_fwd_fused<true><<<pb.B * pb.H * nseg, FUSED_THREADS, FUSED_SMEM, st>>>(up);
+    else k_fwd_fused<false><<<pb.B * pb.H * nseg, FUSED_THREADS, FUSED_SMEM, st>>>(up);
     return post_launch();
   }
   rc = run_scan(false, pb, nseg, p.k, p.g, p.v, start, h, last, nullptr, st);

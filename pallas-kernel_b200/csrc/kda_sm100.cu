@@ -720,6 +720,9 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_bwd_scan(const __grid_const
       fence_async_smem();
       tc_fence_before();
       if (__syncthreads_or(*abort_flag)) break;   // B1
+      // (beta of the next chunk: loaded here, stored to shared memory three barriers later)
+      __nv_bfloat16 beta_in = __float2bfloat16(0.f);
+      if (tid < C && pp + 1 < NT) beta_in = p.beta[((size_t)b * p.T + chunk_of(pp + 1) * C + tid) * p.H + h];
       const float av = sh.a[col], g0v = sh.g0[col];
       const float decay = fast_exp(2.f * av + g0v);   // exp(G_n)
       const float cmid = fast_exp(av + g0v);          // exp(mid)
@@ -791,7 +794,7 @@ __global__ void __launch_bounds__(KDA_THREADS) k_kda_bwd_scan(const __grid_const
           atomicAdd(&sh.db[ri], dot);
         }
       }
-      if (tid < C && pp + 1 < NT) load_beta(pp + 1);
+      if (tid < C && pp + 1 < NT) sh.beta[(pp + 1) & 1][tid] = __bfloat162float(beta_in);
       fence_async_smem();
       tc_fence_before();
       if (__syncthreads_or(*abort_flag)) break;   // B4
