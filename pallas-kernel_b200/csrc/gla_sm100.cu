@@ -405,6 +405,8 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1) k_scan(const __grid_constant_
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
     }
     if (ok && p.gsum && seg == 0) p.gsum[(size_t)blk * D + col] = gtot;
+    // (a loop left early may leave gate copies of this thread in flight: they land before the block ends)
+    if (SCALAR) asm volatile("cp.async.wait_all;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
