@@ -120,7 +120,7 @@ __device__ __forceinline__ void invert_unit_lower(const float* __restrict__ Lm, 
 //       meanwhile the compute warps invert I + L
 //   B3  T (bf16) and R = beta (v - k^ h') are out        -> v' = T R
 //   B4  v' is in shared memory                           -> k~^T v', o += Aqk v'; exponents of the next chunk
-__global__ void __launch_bounds__(KDA_THREADS) k_kda_fwd(const __grid_constant__ KdaFwdParams p) {
+__global__ void __launch_bounds__(KDA_THREADS, 1) k_kda_fwd(const __grid_constant__ KdaFwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* in = smem;                       // 2 stages x (q, k, g); the g tile later holds L in fp32
   uint8_t* vs = in + 2 * KDA_STAGE;         // v
@@ -511,7 +511,7 @@ struct KdaScanShared {
 constexpr uint32_t KDA_SCAN_STAGE = 2 * TILE64 + SLAB64;   // q, k, T
 constexpr size_t KDA_SCAN_SMEM = 2 * KDA_SCAN_STAGE + 5 * TILE64 + TILE128 + SLAB64 + 2 * SLAB64 + sizeof(KdaScanShared);
 
-__global__ void __launch_bounds__(KDA_THREADS) k_kda_bwd_scan(const __grid_constant__ KdaScanParams p) {
+__global__ void __launch_bounds__(KDA_THREADS, 1) k_kda_bwd_scan(const __grid_constant__ KdaScanParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* in = smem;                        // 2 stages x (q, k, T)
   uint8_t* gs = in + 2 * KDA_SCAN_STAGE;     // g
