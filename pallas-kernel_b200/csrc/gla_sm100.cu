@@ -827,6 +827,7 @@ __global__ void __launch_bounds__(FUSED_THREADS) k_fwd_fused(const __grid_consta
       }
       // per-channel factors of this thread's state row
       float decay, c2;
+      float em[16];
       {
         float w[8];
         if (SCALAR) {
@@ -834,6 +835,8 @@ __global__ void __launch_bounds__(FUSED_THREADS) k_fwd_fused(const __grid_consta
           w[1] = wg.gn - wg.mid();
         } else {
           tmem_ld8(tmem_addr(tm, lane_base, cW), w);
+          // (the exponents of the gating below are fetched now: their exponentials interleave with the staging)
+          tmem_ld16(tmem_addr(tm, lane_base, cE + ((q4 >> 1) * 4 + seg) * 16), em);
         }
         decay = fast_exp(w[0]);                    // exp(G_n)
         c2 = fast_exp(w[1]);                       // exp(G_n - mid)
@@ -860,8 +863,6 @@ __global__ void __launch_bounds__(FUSED_THREADS) k_fwd_fused(const __grid_consta
       } else {
         const int i = (q4 * 32 + lane) & 63;
         const int cg = (q4 >> 1) * 4 + seg;
-        float em[16];
-        tmem_ld16(tmem_addr(tm, lane_base, cE + cg * 16), em);
         const uint32_t rowoff = (uint32_t)(cg >> 2) * SLAB64 + (uint32_t)i * 128u;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
