@@ -152,3 +152,22 @@ def test_golden_vectors_reproduce(name):
     out = run_case(CASES[blob["case"]])
     for key, ref in blob["outputs"].items():
         assert torch.allclose(out[key].float(), ref.float(), rtol=1e-5, atol=1e-6), key
+
+
+@pytest.mark.parametrize("C,g_scale", [(64, 0.8), (128, 0.8), (128, 1.0)])
+def test_large_gates_stay_finite_and_exact(C, g_scale):
+    """Per-step gates uniform in (-g_scale, 0): their chunk-local sums reach -C g_scale, where exp() of the raw
+    cumulative gate over- or underflows fp32; the mid-point anchored factorisation must stay finite and equal to the
+    token recurrence (the reference's tests/ops/gla/test_exp_overflow_stabilization.py:62-221, same gate law)."""
+    g = torch.Generator().manual_seed(42)
+    B, T, H, Kd = 1, 2 * C, 2, 32
+    q, k, v, do = (torch.randn(B, T, H, Kd, generator=g) for _ in range(4))
+    gate = -g_scale * torch.rand(B, T, H, Kd, generator=g)
+    scale = Kd ** -0.5
+    o, ht = G.chunk_gla(q, k, v, gate, scale, None, True, chunk_size=C)
+    grads = G.chunk_gla_bwd(q, k, v, gate, None, scale, None, None, None, do, None, chunk_size=C)
+    for t in (o, ht, *grads[:4]):
+        assert torch.isfinite(t).all()
+    o_ref, ht_ref = G.naive_recurrent_gla(q.double(), k.double(), v.double(), gate.double(), output_final_state=True)
+    assert (o.double() - o_ref).abs().max() < 1e-3
+    assert (ht.double() - ht_ref).abs().max() < 1e-3

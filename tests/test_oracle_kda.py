@@ -92,3 +92,27 @@ def test_staged_chunk_backward_equals_autodiff(B, T, H, Kd, V, C, use_h0):
     exp = K.fused_recurrent_kda_bwd(q, k, v, g, beta, do, None, h0, dht)
     for a, b in zip((dq, dk, dv, dg, db), exp):
         assert (a - b).abs().max() < 1e-7
+
+
+def test_chunk_matrices_against_a_literal_construction():
+    """Aqk and Akk of `kda_intra_chunk_fwd` against loops over (i, j) and a general linear solve — the way the
+    reference's own test builds them (tests/ops/kda/test_chunk_kda_bwd_tpu.py:56-97), with the convention of the
+    accelerator kernel: Akk = (I + stril(beta_i k_i.k_j 2^(G_i - G_j)))^-1 (tops/ops/kda/chunk_intra.py:141-153)."""
+    B, T, H, Kd, C = 1, 16, 2, 8, 8
+    q, k, _, gate, beta, _ = _rand(11, B, T, H, Kd, 8)
+    scale = Kd ** -0.5
+    g2 = K.kda_gate_chunk_cumsum(gate, C)          # chunk-local cumulative gate in log2 space
+    Aqk, Akk = K.kda_intra_chunk_fwd(q, k, g2, beta, scale, C)
+    for h in range(H):
+        for c0 in range(0, T, C):
+            Lm = torch.zeros(C, C, dtype=DT)
+            Am = torch.zeros(C, C, dtype=DT)
+            for i in range(C):
+                for j in range(i + 1):
+                    w = torch.exp2(g2[0, c0 + i, h] - g2[0, c0 + j, h])
+                    Am[i, j] = scale * (q[0, c0 + i, h] * k[0, c0 + j, h] * w).sum()
+                    if j < i:
+                        Lm[i, j] = beta[0, c0 + i, h] * (k[0, c0 + i, h] * k[0, c0 + j, h] * w).sum()
+            inv = torch.linalg.solve(torch.eye(C, dtype=DT) + Lm, torch.eye(C, dtype=DT))
+            assert (Aqk[0, c0:c0 + C, h] - Am).abs().max() < 1e-12
+            assert (Akk[0, c0:c0 + C, h] - inv).abs().max() < 1e-12

@@ -158,3 +158,29 @@ def test_bounded_wait_runs_out_and_the_kernel_returns_by_itself():
     assert_close("o", o2.cpu(), o_ref, torch.bfloat16)
     assert_close("ht", ht2.cpu(), ht_ref, torch.bfloat16)
     assert L.device_error() == 0
+
+
+@pytest.mark.parametrize("g_scale", [0.8, 1.0])
+def test_sm100_large_gates_stay_finite(g_scale):
+    """Per-step gates uniform in (-g_scale, 0) (the gate law of the reference's
+    tests/ops/gla/test_exp_overflow_stabilization.py): chunk sums near -64 g_scale, where the raw cumulative gate
+    leaves the range of exp().  The mid-point anchored exponents of the tensor-core kernels must stay finite and
+    keep the bf16 bar, forward and backward."""
+    from tops_b200 import _lib as L
+    g = torch.Generator().manual_seed(42)
+    B, T, H = 1, 256, 2
+    x = {n: torch.randn(B, T, H, 128, generator=g).to(torch.bfloat16) for n in ("q", "k", "v", "do")}
+    x["g"] = (-g_scale * torch.rand(B, T, H, 128, generator=g)).to(torch.bfloat16)
+    x["h0"] = 0.1 * torch.randn(B, H, 128, 128, generator=g)
+    x["dht"] = 0.1 * torch.randn(B, H, 128, 128, generator=g)
+    scale = 128 ** -0.5
+    o_ref, ht_ref = O.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale, x["h0"], True, chunk_size=64)
+    ref = O.chunk_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], None, None, x["do"], x["dht"],
+                          chunk_size=64)
+    got = _run(to_cuda(x), B, T, H, L.IMPL_SM100, True)
+    torch.cuda.synchronize()
+    assert L.device_error() == 0
+    want = dict(o=o_ref, ht=ht_ref, dq=ref[0], dk=ref[1], dv=ref[2], dg=ref[3], dh0=ref[4])
+    for name, r in want.items():
+        assert torch.isfinite(got[name]).all(), name
+        assert_close(name, got[name], r, torch.bfloat16)
