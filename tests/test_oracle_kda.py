@@ -116,3 +116,92 @@ def test_chunk_matrices_against_a_literal_construction():
             inv = torch.linalg.solve(torch.eye(C, dtype=DT) + Lm, torch.eye(C, dtype=DT))
             assert (Aqk[0, c0:c0 + C, h] - Am).abs().max() < 1e-12
             assert (Akk[0, c0:c0 + C, h] - inv).abs().max() < 1e-12
+
+
+# --- the intra-chunk backward on its own: the properties the reference checks in
+# tests/ref/kda/test_chunk_kda.py:180-397 (zero cotangents, beta = 0, chunks of one token, linearity),
+# and, beyond them, equality with autodiff of the two matrices' definitions ---
+
+def _intra_inputs(seed, B, NT, H, C, Kd):
+    gen = torch.Generator().manual_seed(seed)
+    T = NT * C
+    q = torch.randn(B, T, H, Kd, dtype=DT, generator=gen)
+    k = torch.randn(B, T, H, Kd, dtype=DT, generator=gen)
+    raw = torch.nn.functional.logsigmoid(torch.randn(B, T, H, Kd, dtype=DT, generator=gen))
+    g = raw.reshape(B, NT, C, H, Kd).cumsum(2).reshape(B, T, H, Kd)
+    beta = torch.sigmoid(torch.randn(B, T, H, dtype=DT, generator=gen))
+    lower = torch.tril(torch.ones(C, C, dtype=torch.bool))[None, None, :, None, :]
+    strict = torch.tril(torch.ones(C, C, dtype=torch.bool), -1)[None, None, :, None, :]
+    dAqk = torch.where(lower, torch.randn(B, NT, C, H, C, dtype=DT, generator=gen), 0.0).reshape(B, T, H, C)
+    dAkk = torch.where(strict, torch.randn(B, NT, C, H, C, dtype=DT, generator=gen), 0.0).reshape(B, T, H, C)
+    return q, k, g, beta, dAqk, dAkk
+
+
+def _intra(q, k, g, beta, dAqk, dAkk, C):
+    z = torch.zeros_like(q)
+    return K.chunk_kda_bwd_intra(q, k, g, beta, dAqk, dAkk, z, z.clone(), torch.zeros_like(beta), z.clone(), C)
+
+
+INTRA_SHAPES = [(2, 2, 4, 16, 32), (1, 4, 2, 16, 16), (2, 1, 4, 32, 16), (1, 1, 1, 4, 1), (1, 2, 1, 2, 8),
+                (1, 3, 2, 16, 32), (1, 2, 2, 64, 32)]
+
+
+@pytest.mark.parametrize("B,NT,H,C,Kd", INTRA_SHAPES)
+def test_intra_backward_zero_cotangents(B, NT, H, C, Kd):
+    q, k, g, beta, dAqk, dAkk = _intra_inputs(42, B, NT, H, C, Kd)
+    dq, dk, db, dg = _intra(q, k, g, beta, dAqk, torch.zeros_like(dAkk), C)
+    assert dq.shape == q.shape and dk.shape == k.shape and db.shape == beta.shape and dg.shape == g.shape
+    assert dq.abs().max() > 0 and db.abs().max() <= 1e-15
+    dq2, _, db2, _ = _intra(q, k, g, beta, torch.zeros_like(dAqk), dAkk, C)
+    assert dq2.abs().max() <= 1e-15
+    if C > 1 and dAkk.abs().max() > 0:
+        assert db2.abs().max() > 0
+
+
+def test_intra_backward_beta_zero_and_single_token_chunks():
+    q, k, g, _, dAqk, dAkk = _intra_inputs(55, 1, 2, 2, 8, 4)
+    beta0 = torch.zeros(1, 16, 2, dtype=DT)
+    dq, dk, db, _ = _intra(q, k, g, beta0, torch.zeros_like(dAqk), dAkk, 8)
+    assert dq.abs().max() <= 1e-15 and dk.abs().max() <= 1e-15 and db.abs().max() > 0
+    # chunks of one token: the strictly lower triangle is empty
+    q, k, g, beta, dAqk, dAkk = _intra_inputs(33, 1, 8, 2, 1, 4)
+    assert dAkk.abs().max() == 0
+    dq, _, db, _ = _intra(q, k, g, beta, dAqk, dAkk, 1)
+    assert dq.abs().max() > 0 and db.abs().max() <= 1e-15
+
+
+def test_intra_backward_is_linear_in_its_cotangents():
+    q, k, g, beta, dAqk, dAkk = _intra_inputs(88, 1, 2, 2, 8, 4)
+    zq, zk = torch.zeros_like(dAqk), torch.zeros_like(dAkk)
+    one = _intra(q, k, g, beta, dAqk, zk, 8)
+    pi = _intra(q, k, g, beta, 3.14 * dAqk, zk, 8)
+    for a, b in zip(one, pi):
+        assert (b - 3.14 * a).abs().max() <= 1e-10 * (1 + a.abs().max())
+    one = _intra(q, k, g, beta, zq, dAkk, 8)
+    e = _intra(q, k, g, beta, zq, 2.71 * dAkk, 8)
+    for a, b in zip(one, e):
+        assert (b - 2.71 * a).abs().max() <= 1e-10 * (1 + a.abs().max())
+    both = _intra(q, k, g, beta, dAqk, dAkk, 8)
+    parts = _intra(q, k, g, beta, dAqk, zk, 8)
+    for a, b, c in zip(both, parts, one):
+        assert (a - b - c).abs().max() <= 1e-10 * (1 + a.abs().max())
+
+
+@pytest.mark.parametrize("B,NT,H,C,Kd", [(1, 2, 2, 8, 4), (2, 3, 1, 16, 8)])
+def test_intra_backward_equals_autodiff_of_the_definitions(B, NT, H, C, Kd):
+    """dq, dk, dbeta and the gate gradient (before its reverse cumsum: with respect to the cumulative
+    gate in log2 space, times ln 2 folded as the stage formulas do) against torch autograd through
+    Aqk[i,j] = sum_k q_i k_j 2^(G_i - G_j) (j <= i), Lkk[i,j] = beta_i sum_k k_i k_j 2^(G_i - G_j) (j < i)."""
+    q, k, g, beta, dAqk, dAkk = _intra_inputs(7, B, NT, H, C, Kd)
+    qa, ka, ga, ba = (x.clone().requires_grad_(True) for x in (q, k, g, beta))
+    ch = lambda x: x.reshape(B, NT, C, H, -1)
+    qc, kc, gc, bc = ch(qa), ch(ka), ch(ga), ba.reshape(B, NT, C, H)
+    dec = torch.exp2(gc[:, :, :, None] - gc[:, :, None, :])                          # [B,NT,i,j,H,K]
+    qk = torch.einsum("bnihk,bnijhk,bnjhk->bnihj", qc, dec, kc)
+    kk = torch.einsum("bnihk,bnijhk,bnjhk->bnihj", kc, dec, kc) * bc[..., None]
+    loss = (qk * ch(dAqk)).sum() + (kk * ch(dAkk)).sum()       # the cotangents are masked already
+    loss.backward()
+    dq, dk, db, dg = _intra(q, k, g, beta, dAqk, dAkk, C)
+    ln2 = 0.6931471805599453
+    for name, got, want in (("dq", dq, qa.grad), ("dk", dk, ka.grad), ("db", db, ba.grad), ("dg", dg, ga.grad / ln2)):
+        assert (got - want).abs().max() <= 1e-10 * (1 + want.abs().max()), name
