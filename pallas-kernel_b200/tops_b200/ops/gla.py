@@ -50,6 +50,8 @@ def chunk_gla_fwd(q, k, v, g, g_cumsum, scale, initial_state, output_final_state
     Returns (g_cumsum fp32, A fp32 `[B,T,H,C]`, h `[B,NT,H,K,V]` k.dtype, ht, o).
     `g_cumsum` is accepted for signature parity and recomputed."""
     _check_qkvg(q, k, v, g, initial_state, cu_seqlens)
+    assert chunk_size in (16, 32, 64), \
+        f"chunk_gla_fwd returns per-chunk tensors; the kernels hold chunks of 16, 32 or 64, got {chunk_size}"
     cu = _cu_list(cu_seqlens)
     o, ht, gcum, A, h = chunk_fwd_call(q, k, v, g, L.GATE_PER_CHANNEL, scale, initial_state,
                                        output_final_state, chunk_size, cu, want_gcum=True, want_A=True,
@@ -60,9 +62,13 @@ def chunk_gla_fwd(q, k, v, g, g_cumsum, scale, initial_state, output_final_state
 def chunk_gla_bwd(q, k, v, g, g_cumsum, scale, initial_state, h, A, do, dht, chunk_size=64,
                   cu_seqlens=None):
     """Backward orchestrator (reference `tops/cpu/ops/gla/chunk.py:469-640`).
-    `g_cumsum`, `h`, `A` are accepted for signature parity and recomputed.
+    `g_cumsum`, `h`, `A` are accepted for signature parity and recomputed, so the gradients do not depend
+    on `chunk_size` beyond rounding: a power of two the kernels do not hold (128) runs with the nearest.
     Returns (dq fp32, dk fp32, dv do.dtype, dg fp32, dh0 fp32 or None)."""
     _check_qkvg(q, k, v, g, initial_state, cu_seqlens)
+    assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, \
+        f"chunk_size must be a power of 2, got {chunk_size}"   # tops/ops/common/cumsum.py:506-508
+    chunk_size = min(max(int(chunk_size), 16), 64)
     return chunk_bwd_call(q, k, v, g, L.GATE_PER_CHANNEL, scale, initial_state, do, dht, chunk_size,
                           torch.float32, True, initial_state is not None, _cu_list(cu_seqlens))
 

@@ -51,9 +51,20 @@ def _cu(cu_seqlens):
     return None if cu_seqlens is None else [int(x) for x in cu_seqlens]
 
 
+def _kernel_chunk(chunk_size):
+    """The chunk length the kernels run with.  Neither (o, ht) nor the gradients depend on it beyond where
+    roundings fall, and the orchestrators of this family hand no chunk-shaped tensor to the caller: the kernels
+    hold chunks of 16, 32 or 64 time steps, other powers of two (the reference's tests use 128) run with the
+    nearest."""
+    assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, \
+        f"chunk_size must be a power of 2, got {chunk_size}"   # tops/ops/common/cumsum.py:506-508
+    return min(max(int(chunk_size), 16), 64)
+
+
 def _fwd(q, k, v, g, g_gamma, scale, initial_state, output_final_state, chunk_size, cu_seqlens, want_saved):
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
+    chunk_size = _kernel_chunk(chunk_size)
     o, ht, _, _, saved = chunk_fwd_call(q, k, v, gate, kind, scale, initial_state, output_final_state, chunk_size,
                                         _cu(cu_seqlens), want_saved=want_saved)
     return o, ht, saved
@@ -75,7 +86,7 @@ def chunk_simple_gla_bwd(q, k, v, g, g_gamma, initial_state, do, dht, scale, chu
     forward kept (None recomputes them, as the reference does)."""
     _check(q, k, v, g, g_gamma, initial_state, cu_seqlens)
     gate, kind = _gate(g, g_gamma)
-    return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, chunk_size, q.dtype,
+    return chunk_bwd_call(q, k, v, gate, kind, scale, initial_state, do, dht, _kernel_chunk(chunk_size), q.dtype,
                           g is not None, initial_state is not None, _cu(cu_seqlens), h_saved=h_saved)
 
 
@@ -111,11 +122,7 @@ def chunk_simple_gla(q, k, v, g=None, g_gamma=None, scale=None, initial_state=No
         scale = K ** -0.5
     if initial_state is not None:
         initial_state = initial_state.to(torch.float32)
-    assert chunk_size >= 1 and (chunk_size & (chunk_size - 1)) == 0, \
-        f"chunk_size must be a power of 2, got {chunk_size}"   # tops/ops/common/cumsum.py:506-508
-    # results do not depend on the chunk length beyond where roundings fall: the kernels hold chunks of
-    # 16, 32 or 64 time steps, other powers of two (the reference's tests use 128) run with the nearest
-    chunk_size = min(max(int(chunk_size), 16), 64)
+    chunk_size = _kernel_chunk(chunk_size)
     o, ht = _ChunkSimpleGLA.apply(q, k, v, g, g_gamma, initial_state, float(scale), bool(output_final_state),
                                   _cu(cu_seqlens), int(chunk_size))
     return o, (ht if output_final_state else None)

@@ -294,3 +294,13 @@ def test_chunk_sizes_beyond_the_kernel_tiles(chunk_size):
     assert_close("simple_gla o", o2, o3.cpu(), torch.float32)
     with pytest.raises(AssertionError):
         chunk_gla(c["q"], c["k"], c["v"], c["g"], chunk_size=48)
+    # the explicit backward hands no per-chunk tensor back either; the forward orchestrator does and says so
+    from tops_b200.ops.gla import chunk_gla_bwd, chunk_gla_fwd
+    do = torch.randn_like(c["v"])
+    got = chunk_gla_bwd(c["q"], c["k"], c["v"], c["g"], None, K ** -0.5, c["h0"], None, None, do, None,
+                        chunk_size=chunk_size)
+    want = chunk_gla_bwd(c["q"], c["k"], c["v"], c["g"], None, K ** -0.5, c["h0"], None, None, do, None, chunk_size=64)
+    for name, a, b in zip(("dq", "dk", "dv", "dg", "dh0"), got, want):
+        assert_close(name, a, b.cpu(), torch.float32)
+    with pytest.raises(AssertionError):
+        chunk_gla_fwd(c["q"], c["k"], c["v"], c["g"], None, K ** -0.5, None, False, chunk_size=chunk_size)

@@ -135,3 +135,26 @@ def test_scalar_gate_on_tensor_core_kernels(B, T, H):
     assert got[0].dtype == torch.bfloat16 and got[3].shape == (B, T, H)
     for name, a, b in zip(("dq", "dk", "dv", "dg", "dh0"), got, ref):
         assert_close(name, a, b, torch.bfloat16)
+
+
+@pytest.mark.parametrize("C", [64, 128])
+@pytest.mark.parametrize("gamma_val", [-0.5, -0.8, -1.0])
+def test_large_constant_decay_stays_finite(gamma_val, C):
+    """|g_gamma|·(C−1) beyond the range of fp32 exp() (the no-NaN cases of the reference's
+    tests/ops/simple_gla/test_chunk_simple_gla_tpu.py:309-383): every exponent the kernels form is anchored,
+    so outputs and gradients stay finite and keep the bf16 bar."""
+    from tops_b200.ops.simple_gla import chunk_simple_gla, chunk_simple_gla_bwd
+    B, T, H, K, V = 1, 256, 2, 128, 128
+    gen = torch.Generator().manual_seed(42)
+    x = {n: torch.randn(B, T, H, 128, generator=gen).to(torch.bfloat16) for n in ("q", "k", "v", "do")}
+    gamma = torch.full((H,), gamma_val)
+    scale = K ** -0.5
+    o_ref, ht_ref = O.chunk_simple_gla(x["q"], x["k"], x["v"], None, gamma, None, None, True, chunk_size=C)
+    ref = O.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], None, gamma, None, x["do"], None, scale, chunk_size=C)
+    c = to_cuda(x)
+    o, ht = chunk_simple_gla(c["q"], c["k"], c["v"], None, gamma.cuda(), None, None, True, chunk_size=C)
+    got = chunk_simple_gla_bwd(c["q"], c["k"], c["v"], None, gamma.cuda(), None, c["do"], None, scale, chunk_size=C)
+    for name, a, b in (("o", o, o_ref), ("ht", ht, ht_ref), ("dq", got[0], ref[0]), ("dk", got[1], ref[1]),
+                       ("dv", got[2], ref[2])):
+        assert torch.isfinite(a.float()).all(), name
+        assert_close(name, a, b, torch.bfloat16)
