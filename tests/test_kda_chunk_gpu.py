@@ -165,3 +165,35 @@ def test_kda_time_shards_chain_on_one_gpu():
     for i, name in enumerate(("dq", "dk", "dv", "dg", "dbeta")):
         e = rel_l2(torch.cat([b[i] for b in bw], 1), ref[i])
         assert e <= 2e-2, (name, e)
+
+
+@pytest.mark.parametrize("h0", [False, True])
+def test_chunk_kda_bwd_unnormalised_inputs_and_strong_gates(h0):
+    """The input law of the reference's backward tests (tests/ops/kda/test_chunk_kda_bwd_tpu.py:33-58): q, k, v,
+    do ~ 0.1 N(0,1) without L2 normalisation, per-step gates -0.3 |N(0,1)| (a chunk decays by about e^-15 per
+    channel), h0 and dht ~ 0.01 N(0,1).  Forward and every gradient against the token recurrence."""
+    from tops_b200 import _lib as L
+    from tops_b200.ops.kda import chunk_kda_bwd, chunk_kda_fwd
+    B, T, H = 1, 256, 2
+    gen = torch.Generator().manual_seed(99)
+    host = {n: (0.1 * torch.randn(B, T, H, 128, generator=gen)).to(BF16) for n in ("q", "k", "v", "do")}
+    host["g"] = (-0.3 * torch.randn(B, T, H, 128, generator=gen).abs()).to(BF16)
+    host["beta"] = torch.sigmoid(torch.randn(B, T, H, generator=gen)).to(BF16)
+    host["h0"] = 0.01 * torch.randn(B, H, 128, 128, generator=gen) if h0 else None
+    host["dht"] = 0.01 * torch.randn(B, H, 128, 128, generator=gen)
+    x = {n: (None if t is None else t.cuda()) for n, t in host.items()}
+    scale = 128 ** -0.5
+    o, ht, _, _, _ = chunk_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+    dq, dk, dv, db, dg, dh0 = chunk_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
+    torch.cuda.synchronize()
+    assert L.device_error() == 0
+    f = {n: host[n].float() for n in ("q", "k", "v", "g", "beta", "do")}
+    o_ref, ht_ref = O.naive_recurrent_kda(f["q"], f["k"], f["v"], f["g"], f["beta"], scale, host["h0"], True)
+    ref = O.fused_recurrent_kda_bwd(f["q"], f["k"], f["v"], f["g"], f["beta"], f["do"], scale, host["h0"], host["dht"])
+    assert_close("o", o.float().cpu(), o_ref, BF16)
+    assert_close("ht", ht.cpu(), ht_ref, BF16)
+    for name, a, r in zip(("dq", "dk", "dv", "dg", "dbeta"), (dq, dk, dv, dg, db), ref[:5]):
+        assert torch.isfinite(a).all(), name
+        assert_close(name, a.float().cpu(), r.float(), BF16)
+    if h0:
+        assert_close("dh0", dh0.cpu(), ref[5], BF16)
