@@ -21,6 +21,16 @@ def acc_dtype(dtype: torch.dtype) -> torch.dtype:
     return torch.float64 if dtype == torch.float64 else torch.float32
 
 
+def weak_scalar(x: float, dtype: torch.dtype) -> float:
+    """The value a python scalar takes when the reference multiplies an array of `dtype` by it.
+    jax.numpy gives the scalar the array's dtype before the operation (weak typing), so `q_bf16 * scale`
+    is bf16(q * bf16(scale)); torch keeps the scalar in fp32 and would give bf16(q * scale).  Only half
+    types are affected, and only for scalars that are not exactly representable in them."""
+    if dtype in (torch.bfloat16, torch.float16):
+        return float(torch.tensor(x, dtype=dtype))
+    return x
+
+
 def dot(spec: str, a: torch.Tensor, b: torch.Tensor, acc: torch.dtype) -> torch.Tensor:
     """einsum with accumulator-dtype operands (`utils.py:194-208`): half inputs
     are widened first, which is exact, so the product matches a tensor-core
@@ -214,12 +224,13 @@ def chunk_bwd_dh(q, do, *, g=None, g_gamma=None, gk=None, h0=None, dht=None,
         out[c] = dh
         sl = slice(c * C, (c + 1) * C)
         bq, bdo = q[:, sl], do[:, sl]
+        s_in = weak_scalar(scale, q.dtype)      # `b_q * scale` with b_q in q.dtype (chunk_h.py:401-404)
         if gk is not None:
             bgk = gk[:, sl]
-            bq = (bq * scale * torch.exp(bgk)).to(q.dtype)
+            bq = (bq * s_in * torch.exp(bgk)).to(q.dtype)
             dh = dh * torch.exp(bgk[:, -1])[..., None]
         else:
-            bq = (bq * scale).to(q.dtype)
+            bq = (bq * s_in).to(q.dtype)
         if g is not None:
             bg = g[:, sl]
             bq = (bq * torch.exp(bg[..., None])).to(q.dtype)

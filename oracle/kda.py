@@ -58,6 +58,7 @@ def naive_chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_fin
     """
     B, T0, H, K, V = _check(q, k, v, g, beta, initial_state)
     acc = acc_dtype(q.dtype)
+    out_dtype = v.dtype
     C = chunk_size
     if scale is None:
         scale = K ** -0.5
@@ -92,7 +93,7 @@ def naive_chunk_kda(q, k, v, g, beta, scale=None, initial_state=None, output_fin
         last = Gn[:, :, -1]
         S = S * torch.exp(last)[..., None] + torch.einsum("bhck,bhcv->bhkv", torch.exp(last[:, :, None] - Gn) * kn, vc)
     o = torch.stack(outs, 2).reshape(B, H, T, V).permute(0, 2, 1, 3)[:, :T0]
-    return o.to(v.dtype), (S if output_final_state else None)
+    return o.to(out_dtype), (S if output_final_state else None)
 
 
 def fused_recurrent_kda(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=False):

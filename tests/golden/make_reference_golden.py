@@ -1,0 +1,218 @@
+"""Freeze outputs of the REFERENCE's own CPU implementation as fixtures (`ref_*.pt` in this directory).
+
+    python -m tests.golden.make_reference_golden --reference <checkout of Fred33146/pallas-kernel>
+
+`tops/cpu/ops/**` is pure `jax.numpy`, and JAX is not installed where this repository is built.  The
+script therefore puts `tests/golden/jax_standin/` (a numpy-backed stand-in for the few `jax` names those
+files use) in front of `sys.path` and imports the reference's source files from the checkout, unmodified:
+every number in the fixtures is computed by the reference's code, only the array library underneath
+is numpy instead of XLA (see the stand-in's docstring for what that does and does not preserve).
+`tops/ops/__init__.py` imports the Pallas kernels, which need the real JAX; the CPU files only want
+`tops/ops/utils.py` from that package, so an empty package object with the same search path is registered
+in its place before anything is imported.
+
+Inputs come from `tops_b200.synth.make_inputs` (seeded numpy draws), the same call the tests make, so the
+fixtures hold outputs only.  The checkout is needed to REGENERATE the fixtures, never to run the tests.
+"""
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+
+# name -> case (float64 cases run with jax_enable_x64 on, the others with it off, as the reference's tests do)
+CASES = {
+    "ref_gla_f64": dict(op="gla", seed=301, B=2, T=80, H=2, K=16, V=24, C=32, dtype="float64"),
+    "ref_gla_f32": dict(op="gla", seed=302, B=2, T=80, H=2, K=32, V=24, C=32, dtype="float32"),
+    "ref_gla_bf16": dict(op="gla", seed=303, B=1, T=128, H=2, K=32, V=64, C=64, dtype="bfloat16"),
+    "ref_gla_varlen_f64": dict(op="gla", seed=304, B=1, T=80, H=2, K=16, V=32, C=16, dtype="float64",
+                               cu_seqlens=[0, 16, 53, 80]),
+    "ref_recurrent_f64": dict(op="recurrent", seed=305, B=2, T=24, H=2, K=32, V=16, dtype="float64", reverse=False),
+    "ref_recurrent_rev_f32": dict(op="recurrent", seed=306, B=1, T=20, H=2, K=16, V=24, dtype="float32", reverse=True),
+    "ref_simple_gla_f64": dict(op="simple_gla", seed=307, B=2, T=50, H=2, K=16, V=32, C=16, dtype="float64", gate="g"),
+    "ref_simple_gla_gamma_f32": dict(op="simple_gla", seed=308, B=1, T=70, H=3, K=32, V=16, C=32, dtype="float32",
+                                     gate="gamma"),
+    "ref_simple_gla_bf16": dict(op="simple_gla", seed=309, B=1, T=128, H=2, K=32, V=64, C=64, dtype="bfloat16",
+                                gate="g"),
+    "ref_simple_gla_gamma_bf16": dict(op="simple_gla", seed=312, B=1, T=100, H=2, K=32, V=32, C=32, dtype="bfloat16",
+                                      gate="gamma"),
+    "ref_gla_f16": dict(op="gla", seed=313, B=1, T=64, H=2, K=32, V=32, C=16, dtype="float16"),
+    "ref_recurrent_bf16": dict(op="recurrent", seed=314, B=1, T=16, H=2, K=32, V=16, dtype="bfloat16", reverse=False),
+    "ref_kda_bf16": dict(op="kda", seed=315, B=1, T=32, H=2, K=32, V=32, C=16, dtype="bfloat16"),
+    "ref_kda_f64": dict(op="kda", seed=310, B=1, T=64, H=2, K=32, V=16, C=16, dtype="float64"),   # V, K powers of two:
+    # the staged backward slices blocks of min(next_power_of_2(V), 64) columns (tops/cpu/ops/kda/chunk_bwd.py:91-92)
+    "ref_kda_f32": dict(op="kda", seed=311, B=2, T=64, H=2, K=32, V=32, C=32, dtype="float32"),
+    # the shapes the tensor-core kernels take (bf16, K = V = 128, chunks of 64); outputs and gradients only
+    "ref_gla_bf16_k128": dict(op="gla", seed=318, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16", slim=True),
+    "ref_simple_gla_bf16_k128": dict(op="simple_gla", seed=319, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16",
+                                     gate="g", slim=True),
+    "ref_kda_bf16_k128": dict(op="kda", seed=320, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16", slim=True),
+    "ref_kda_gate_f32": dict(op="kda_gate", seed=316, B=2, T=48, H=4, K=16, V=16, C=16, dtype="float32"),
+    "ref_kda_gate_bf16": dict(op="kda_gate", seed=317, B=1, T=32, H=2, K=32, V=32, C=16, dtype="bfloat16"),
+}
+
+
+def gate_inputs(c):
+    """Raw gate pre-activations ~ N(0,1) in the case's dtype, A_log `[H]` and dt_bias `[H*K]` in fp32."""
+    rng = np.random.Generator(np.random.PCG64(c["seed"]))
+    g = torch.from_numpy(rng.standard_normal((c["B"], c["T"], c["H"], c["K"]), dtype=np.float32)).to(getattr(torch, c["dtype"]))
+    A_log = torch.from_numpy(rng.standard_normal(c["H"], dtype=np.float32) * 0.5)
+    dt_bias = torch.from_numpy(rng.standard_normal(c["H"] * c["K"], dtype=np.float32) * 0.5)
+    return dict(g=g, A_log=A_log, dt_bias=dt_bias)
+
+
+def case_inputs(c):
+    """The case's inputs as CPU torch tensors (what the tests regenerate)."""
+    if os.path.join(ROOT, "pallas-kernel_b200") not in sys.path:
+        sys.path.insert(0, os.path.join(ROOT, "pallas-kernel_b200"))
+    from tops_b200.synth import make_inputs
+    dtype = getattr(torch, c["dtype"])
+    kda = c["op"] == "kda"
+    gate = "scalar" if c["op"] == "simple_gla" else "per_channel"
+    x = make_inputs(c["seed"], c["B"], c["T"], c["H"], c["K"], c["V"], dtype=dtype, gate=gate, with_h0=True,
+                    with_grads=True, with_beta=kda, l2norm_qk=kda, gate_norm=4.0,
+                    gate_dtype=torch.float32 if (gate == "scalar" and dtype != torch.float64) else None)
+    rng = np.random.Generator(np.random.PCG64(c["seed"] + 1000))
+    if "cu_seqlens" in c:        # one state per packed sequence
+        N = len(c["cu_seqlens"]) - 1
+        st = torch.float64 if dtype == torch.float64 else torch.float32
+        x["h0"] = torch.from_numpy(0.1 * rng.standard_normal((N, c["H"], c["K"], c["V"]))).to(st)
+        x["dht"] = torch.from_numpy(0.1 * rng.standard_normal((N, c["H"], c["K"], c["V"]))).to(x["h0"].dtype)
+    if c["op"] == "recurrent":
+        gv = np.log(1.0 / (1.0 + np.exp(-rng.standard_normal((c["B"], c["T"], c["H"], c["V"]))))) / 4.0
+        x["gv"] = torch.from_numpy(gv).to(dtype)
+    if c.get("gate") == "gamma":
+        x["gamma"] = torch.from_numpy(-(0.02 + 0.1 * rng.random(c["H"]))).to(torch.float32)
+    if dtype == torch.float64:
+        x = {k: (v.to(torch.float64) if v.is_floating_point() else v) for k, v in x.items()}
+    return x
+
+
+def _to_standin(t):
+    import jax.numpy as jnp
+    import ml_dtypes
+    if t is None:
+        return None
+    if t.dtype == torch.bfloat16:
+        return jnp.asarray(t.view(torch.int16).numpy().view(ml_dtypes.bfloat16))
+    return jnp.asarray(t.numpy())
+
+
+def _to_torch(a):
+    if a is None:
+        return None
+    a = np.asarray(a)
+    if a.dtype.name == "bfloat16":
+        return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def run_case(c):
+    import jax
+    import jax.numpy as jnp
+    jax.config.update("jax_enable_x64", c["dtype"] == "float64")
+    if c["op"] == "kda_gate":
+        from tops.cpu.ops.kda.gate import fused_kda_gate, kda_gate_chunk_cumsum
+        x = gate_inputs(c)
+        j = {k: _to_standin(v) for k, v in x.items()}
+        out = dict(plain=fused_kda_gate(j["g"], j["A_log"]),
+                   biased=fused_kda_gate(j["g"], j["A_log"], dt_bias=j["dt_bias"]),
+                   bounded=fused_kda_gate(j["g"], j["A_log"], dt_bias=j["dt_bias"], lower_bound=-5.0),
+                   cumsum_log2=kda_gate_chunk_cumsum(j["g"], j["A_log"], c["C"], scale=1.4426950408889634,
+                                                     dt_bias=j["dt_bias"]))
+        return {k: _to_torch(v) for k, v in out.items()}
+    x = case_inputs(c)
+    j = {k: _to_standin(v) for k, v in x.items()}
+    scale = c["K"] ** -0.5
+    out = {}
+    if c["op"] == "gla":
+        from tops.cpu.ops.gla.chunk import chunk_gla, chunk_gla_bwd, chunk_gla_fwd
+        from tops.cpu.ops.gla.naive import naive_recurrent_gla
+        cu = None if "cu_seqlens" not in c else jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
+        o, ht = chunk_gla(j["q"], j["k"], j["v"], j["g"], scale=scale, initial_state=j["h0"], output_final_state=True,
+                          cu_seqlens=cu, chunk_size=c["C"])
+        dq, dk, dv, dg, dh0 = chunk_gla_bwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], None, None, j["do"],
+                                            j["dht"], chunk_size=c["C"], cu_seqlens=cu)
+        out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+        if cu is None and not c.get("slim"):
+            gcum, A, h, _, _ = chunk_gla_fwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], True, chunk_size=c["C"])
+            out.update(g_cumsum=gcum, A=A, h=h)
+            if c["dtype"] not in ("bfloat16", "float16"):
+                on, htn = naive_recurrent_gla(j["q"], j["k"], j["v"], j["g"], initial_state=j["h0"], output_final_state=True)
+                out.update(o_naive=on, ht_naive=htn)
+    elif c["op"] == "recurrent":
+        from tops.cpu.ops.gla.fused_recurrent import fused_recurrent_bwd, fused_recurrent_fwd
+        o, ht = fused_recurrent_fwd(j["q"], j["k"], j["v"], j["g"], j["gv"], scale, j["h0"], True, c["reverse"])
+        dq, dk, dv, dgk, dgv, dh0 = fused_recurrent_bwd(j["q"], j["k"], j["v"], j["g"], j["gv"], o, j["do"], j["dht"],
+                                                        scale, j["h0"], c["reverse"])
+        out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0)
+    elif c["op"] == "simple_gla":
+        from tops.cpu.ops.simple_gla.chunk import chunk_simple_gla, chunk_simple_gla_bwd
+        from tops.cpu.ops.simple_gla.naive import naive_simple_gla
+        g = j["g"] if c["gate"] == "g" else None
+        gam = j["gamma"] if c["gate"] == "gamma" else None
+        o, ht = chunk_simple_gla(j["q"], j["k"], j["v"], g, gam, scale, j["h0"], True, chunk_size=c["C"])
+        dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(j["q"], j["k"], j["v"], g, gam, j["h0"], j["do"], j["dht"], scale,
+                                                   chunk_size=c["C"])
+        out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+        if c["dtype"] not in ("bfloat16", "float16"):
+            on, htn = naive_simple_gla(j["q"], j["k"], j["v"], g=g, g_gamma=gam, scale=scale, initial_state=j["h0"],
+                                       output_final_state=True)
+            out.update(o_naive=on, ht_naive=htn)
+    elif c["op"] == "kda":
+        from tops.cpu.ops.kda.chunk_bwd import chunk_kda_bwd
+        from tops.cpu.ops.kda.fused_recurrent import fused_recurrent_kda_bwd, fused_recurrent_kda_fwd
+        from tops.cpu.ops.kda.naive import naive_chunk_kda, naive_recurrent_kda
+        o, ht = naive_recurrent_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], True)
+        oc, htc = naive_chunk_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], True, chunk_size=c["C"])
+        of, htf = fused_recurrent_kda_fwd(j["q"], j["k"], j["v"], j["g"], j["beta"], initial_state=j["h0"], scale=scale,
+                                          output_final_state=True)
+        dq, dk, dv, dg, db, dh0 = fused_recurrent_kda_bwd(j["q"], j["k"], j["v"], j["g"], j["beta"], j["do"],
+                                                          initial_state=j["h0"], dht=j["dht"], scale=scale)
+        out.update(o=o, ht=ht, o_chunk=oc, ht_chunk=htc, o_fused=of, ht_fused=htf, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db,
+                   dh0=dh0)
+        # the staged chunk backward wants the forward's chunk matrices, which no CPU file of the reference
+        # computes (its tests take them from another library): they come from this repository's oracle
+        # (pinned against a literal construction in tests/test_oracle_kda.py) and are stored with the outputs
+        if ROOT not in sys.path:
+            sys.path.insert(0, ROOT)
+        from oracle import kda as OK
+        g2 = OK.kda_gate_chunk_cumsum(x["g"], c["C"])
+        Aqk, Akk = OK.kda_intra_chunk_fwd(x["q"], x["k"], g2, x["beta"], scale, c["C"])
+        st = chunk_kda_bwd(j["q"], j["k"], j["v"], j["beta"], _to_standin(Aqk), _to_standin(Akk), scale, j["h0"], j["do"],
+                           j["dht"], g=_to_standin(g2), chunk_size=c["C"])
+        out.update(g2=_to_standin(g2), Aqk=_to_standin(Aqk), Akk=_to_standin(Akk), st_dq=st[0], st_dk=st[1], st_dv=st[2],
+                   st_dbeta=st[3], st_dg=st[4], st_dh0=st[5])
+        if c.get("slim"):
+            out = {k: v for k, v in out.items() if k in ("o", "ht", "dq", "dk", "dv", "dg", "dbeta", "dh0", "st_dq",
+                                                         "st_dk", "st_dg", "st_dbeta")}
+    return {k: _to_torch(v) for k, v in out.items()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
+    ap.add_argument("--only", default=None)
+    args = ap.parse_args()
+    ref = os.path.abspath(args.reference)
+    sys.path.insert(0, ref)
+    sys.path.insert(0, os.path.join(HERE, "jax_standin"))
+    import tops  # noqa: F401  (the reference's package)
+    pkg = types.ModuleType("tops.ops")
+    pkg.__path__ = [os.path.join(ref, "tops", "ops")]
+    sys.modules["tops.ops"] = pkg
+    for name, c in CASES.items():
+        if args.only and args.only != name:
+            continue
+        out = run_case(c)
+        torch.save(out, os.path.join(HERE, name + ".pt"))
+        print(name, {k: (tuple(v.shape), str(v.dtype).replace("torch.", "")) for k, v in out.items() if v is not None})
+
+
+if __name__ == "__main__":
+    main()

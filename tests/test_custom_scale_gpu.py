@@ -61,7 +61,8 @@ def test_chunk_simple_gla_custom_scale(B, T, H, K, V, dtype, scale):
         assert_close(name, a, b, dtype)
 
 
-@pytest.mark.parametrize("T,K,V,dtype,scale", [(128, 128, 128, torch.bfloat16, 0.1)])    # chunked WY kernels
+@pytest.mark.parametrize("T,K,V,dtype,scale", [(128, 128, 128, torch.bfloat16, 0.1),    # chunked WY kernels
+                                               (64, 32, 64, torch.float32, 0.1)])       # token-serial kernels
 def test_chunk_kda_custom_scale(T, K, V, dtype, scale):
     from tops_b200.ops.kda import chunk_kda
     from tops_b200.synth import make_inputs

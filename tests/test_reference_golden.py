@@ -1,0 +1,143 @@
+"""The oracle against outputs of the REFERENCE's own CPU implementation (no GPU).
+
+`tests/golden/ref_*.pt` hold what the reference's unmodified `tops/cpu/ops/**` source files returned on the
+seeded inputs of `tests/golden/make_reference_golden.py` (run on a numpy-backed stand-in for the jax API;
+the generator's docstring says what that preserves).  This is the pin of `oracle/` to the reference itself:
+float64 cases must agree to summation-order rounding, float32 cases to float32 rounding, and bf16 cases,
+where every cast point matters, to a fraction of a bf16 step."""
+import os
+
+import pytest
+import torch
+
+from oracle import gla as G
+from oracle import kda as K
+from oracle import simple_gla as S
+from oracle import aux as A
+from oracle.common import chunk_local_cumsum
+from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs
+
+HERE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# |got - ref| <= tol * max|ref| per tensor
+TOL = {"float64": 1e-12, "float32": 2e-5, "bfloat16": 2e-5, "float16": 2e-5}
+HALF_STEP = {"bfloat16": 2.0 ** -8, "float16": 2.0 ** -11}   # one rounding step, relative to the tensor's largest value
+
+
+def _load(name):
+    return torch.load(os.path.join(HERE, name + ".pt"))
+
+
+def _compare(name, got, ref, dtype, tol=None):
+    for key, r in ref.items():
+        if key not in got:
+            continue
+        g = got[key]
+        if r is None:
+            assert g is None, (name, key)
+            continue
+        assert g is not None, (name, key)
+        assert g.dtype == r.dtype, (name, key, g.dtype, r.dtype)
+        assert g.shape == r.shape, (name, key, g.shape, r.shape)
+        diff = (g.double() - r.double()).abs()
+        top = max(r.double().abs().max().item(), 1e-30)
+        if dtype in ("bfloat16", "float16"):
+            # numpy's and torch's float32 sums differ in their last bits; where such a sum is then rounded to bf16
+            # (chunk states, gated operands) a value next to a rounding boundary can land on the other side and
+            # move the few outputs that use it by one bf16 step.  So: no element further than one step, and all
+            # but a few percent of the elements equal to float32 rounding.
+            assert diff.max().item() <= HALF_STEP[dtype] * top, (name, key, diff.max().item(), top)
+            assert (diff > TOL[dtype] * top).double().mean().item() <= 0.05, (name, key)
+        else:
+            assert diff.max().item() <= (tol or TOL[dtype]) * top, (name, key, diff.max().item(), top)
+
+
+def _run(c, x):
+    scale = c["K"] ** -0.5
+    if c["op"] == "gla":
+        cu = c.get("cu_seqlens")
+        o, ht = G.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale, x["h0"], True, cu_seqlens=cu, chunk_size=c["C"])
+        dq, dk, dv, dg, dh0 = G.chunk_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], None, None, x["do"],
+                                              x["dht"], chunk_size=c["C"], cu_seqlens=cu)
+        out = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+        if cu is None and not c.get("slim"):
+            gc, A, h, _, _ = G.chunk_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True, chunk_size=c["C"])
+            out.update(g_cumsum=gc, A=A, h=h)
+            if c["dtype"] not in ("bfloat16", "float16"):
+                on, htn = G.naive_recurrent_gla(x["q"], x["k"], x["v"], x["g"], x["h0"], True)
+                out.update(o_naive=on, ht_naive=htn)
+        return out
+    if c["op"] == "recurrent":
+        o, ht = G.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"])
+        dq, dk, dv, dgk, dgv, dh0 = G.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], x["gv"], o, x["do"], x["dht"],
+                                                          scale, x["h0"], c["reverse"])
+        return dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0)
+    if c["op"] == "simple_gla":
+        g = x["g"] if c["gate"] == "g" else None
+        gam = x["gamma"] if c["gate"] == "gamma" else None
+        o, ht = S.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, chunk_size=c["C"])
+        dq, dk, dv, dg, dh0 = S.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], g, gam, x["h0"], x["do"], x["dht"], scale,
+                                                     chunk_size=c["C"])
+        out = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+        if c["dtype"] not in ("bfloat16", "float16"):
+            on, htn = S.naive_recurrent_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True)
+            out.update(o_naive=on, ht_naive=htn)
+        return out
+    raise AssertionError(c["op"])
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] not in ("kda", "kda_gate")])
+def test_oracle_equals_the_reference_cpu_code(name):
+    c = CASES[name]
+    ref = _load(name)
+    got = _run(c, case_inputs(c))
+    assert set(got) == set(ref), (sorted(got), sorted(ref))
+    _compare(name, got, ref, c["dtype"])
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda"])
+def test_kda_oracle_equals_the_reference_cpu_code(name):
+    """Token recurrence, chunked form, the explicit token-level backward, and the six-stage chunk backward
+    (which the reference computes in float32 whatever the inputs are: its exp2 helper casts)."""
+    c = CASES[name]
+    ref = _load(name)
+    x = case_inputs(c)
+    scale = c["K"] ** -0.5
+    o, ht = K.naive_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+    oc, htc = K.naive_chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True, chunk_size=c["C"])
+    of, htf = K.fused_recurrent_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+    dq, dk, dv, dg, db, dh0 = K.fused_recurrent_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale,
+                                                        x["h0"], x["dht"])
+    got = dict(o=o, ht=ht, o_chunk=oc, ht_chunk=htc, o_fused=of, ht_fused=htf, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db,
+               dh0=dh0)
+    _compare(name, got, ref, c["dtype"])
+    # the staged chunk backward on the chunk matrices of the oracle's chunk forward
+    g2 = K.kda_gate_chunk_cumsum(x["g"], c["C"])
+    Aqk, Akk = K.kda_intra_chunk_fwd(x["q"], x["k"], g2, x["beta"], scale, c["C"])
+    st = K.chunk_kda_bwd(x["q"], x["k"], x["v"], x["beta"], Aqk, Akk, scale, x["h0"], x["do"], x["dht"], g=g2,
+                         chunk_size=c["C"])
+    names = ("st_dq", "st_dk", "st_dv", "st_dbeta", "st_dg", "st_dh0")
+    for n, a in zip(names, st):
+        if n not in ref:
+            continue
+        r = ref[n]
+        err = (a.double() - r.double()).abs().max().item()
+        top = r.double().abs().max().item()
+        assert err <= 2e-5 * top, (name, n, err, top)
+    # and the stored matrices (what the generator fed the reference's staged backward) are these
+    if "Aqk" in ref:
+        assert torch.equal(Aqk, ref["Aqk"]) and torch.equal(Akk, ref["Akk"]) and torch.equal(g2, ref["g2"])
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda_gate"])
+def test_kda_gate_oracle_equals_the_reference_cpu_code(name):
+    """-exp(A_log) softplus(g + dt_bias), its lower-bounded form, and gate -> chunk cumsum -> log2 scaling."""
+    c = CASES[name]
+    ref = _load(name)
+    x = gate_inputs(c)
+    biased = A.kda_gate_fwd(x["g"], x["A_log"], x["dt_bias"])
+    got = dict(plain=A.kda_gate_fwd(x["g"], x["A_log"]), biased=biased,
+               bounded=A.kda_gate_fwd(x["g"], x["A_log"], x["dt_bias"], lower_bound=-5.0),
+               cumsum_log2=chunk_local_cumsum(biased, c["C"]) * 1.4426950408889634)
+    assert set(got) == set(ref)
+    _compare(name, got, ref, "float32")      # the gate is computed and returned in float32 for every input dtype

@@ -1,0 +1,114 @@
+"""The CUDA kernels against outputs of the REFERENCE's own CPU implementation (`tests/golden/ref_*.pt`,
+produced by `tests/golden/make_reference_golden.py` from the reference's unmodified source files): the direct
+link kernel <-> reference, without the oracle in between.  float64 cases run in float32 on the GPU (the
+kernels' widest type) and meet the float32 bar; half-precision cases meet the relative-L2 bar."""
+import os
+
+import pytest
+import torch
+
+from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs
+from tests.util import assert_close, to_cuda
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _inputs(c):
+    x = case_inputs(c)
+    if c["dtype"] == "float64":
+        x = {k: (v.float() if v.is_floating_point() else v) for k, v in x.items()}
+    return x, (torch.float32 if c["dtype"] == "float64" else getattr(torch, c["dtype"]))
+
+
+def _check(ref, got, dtype):
+    for key, a in got.items():
+        r = ref[key]
+        if r is None:
+            assert a is None, key
+            continue
+        assert_close(key, a.float() if a.dtype != torch.float32 else a, r.float(), dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "gla"])
+def test_gla_kernels_match_the_reference(name):
+    from tops_b200.ops import gla
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    host, dtype = _inputs(c)
+    x = to_cuda(host)
+    scale = c["K"] ** -0.5
+    cu = c.get("cu_seqlens")
+    o, ht = gla.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale=scale, initial_state=x["h0"], output_final_state=True,
+                          cu_seqlens=cu, chunk_size=c["C"])
+    dq, dk, dv, dg, dh0 = gla.chunk_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], None, None, x["do"],
+                                            x["dht"], chunk_size=c["C"], cu_seqlens=cu)
+    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0), dtype)
+    if "A" in ref:        # the per-chunk tensors of the forward orchestrator
+        gcum, A, h, _, _ = gla.chunk_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True, chunk_size=c["C"])
+        _check(ref, dict(g_cumsum=gcum, A=A, h=h), dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "recurrent"])
+def test_recurrent_kernels_match_the_reference(name):
+    from tops_b200.ops import gla
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    host, dtype = _inputs(c)
+    x = to_cuda(host)
+    scale = c["K"] ** -0.5
+    o, ht = gla.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"])
+    dq, dk, dv, dgk, dgv, dh0 = gla.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], x["gv"], o, x["do"], x["dht"],
+                                                        scale, x["h0"], c["reverse"])
+    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0), dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "simple_gla"])
+def test_simple_gla_kernels_match_the_reference(name):
+    from tops_b200.ops import simple_gla
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    host, dtype = _inputs(c)
+    x = to_cuda(host)
+    scale = c["K"] ** -0.5
+    g = x["g"] if c["gate"] == "g" else None
+    gam = x["gamma"] if c["gate"] == "gamma" else None
+    o, ht = simple_gla.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, chunk_size=c["C"])
+    dq, dk, dv, dg, dh0 = simple_gla.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], g, gam, x["h0"], x["do"], x["dht"],
+                                                          scale, chunk_size=c["C"])
+    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0), dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda"])
+def test_kda_kernels_match_the_reference(name):
+    """The token-serial kernels on the small shapes, the chunked tensor-core kernels at K = V = 128, against the
+    reference's token recurrence and its explicit token-level backward."""
+    from tops_b200.ops import kda
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    host, dtype = _inputs(c)
+    x = to_cuda(host)
+    scale = c["K"] ** -0.5
+    if c["K"] == 128:
+        assert kda.chunk_kernels_take(x["q"], x["k"], x["v"], x["g"], x["beta"], 64)
+        o, ht, _, _, _ = kda.chunk_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+        dq, dk, dv, db, dg, dh0 = kda.chunk_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"],
+                                                    x["dht"])
+    else:
+        o, ht = kda.kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+        dq, dk, dv, dg, db, dh0 = kda.kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
+    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db, dh0=dh0), dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda_gate"])
+def test_kda_gate_kernels_match_the_reference(name):
+    from tops_b200.ops import gate
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    x = to_cuda(gate_inputs(c))
+    got = dict(plain=gate.kda_gate_fwd(x["g"], x["A_log"]),
+               biased=gate.kda_gate_fwd(x["g"], x["A_log"], x["dt_bias"]),
+               bounded=gate.kda_gate_fwd(x["g"], x["A_log"], x["dt_bias"], lower_bound=-5.0),
+               cumsum_log2=gate.kda_gate_chunk_cumsum(x["g"], x["A_log"], c["C"], scale=1.4426950408889634,
+                                                      dt_bias=x["dt_bias"]))
+    _check(ref, got, torch.float32)
