@@ -48,11 +48,20 @@ def chunk_local_cumsum(g: torch.Tensor, chunk_size: int, reverse: bool = False,
                        cu_seqlens=None) -> torch.Tensor:
     """Chunk-local inclusive cumsum of log-gates along T, fp32 out
     (reference `tops/cpu/ops/common/chunk_o.py:18-112`).  `g` is `[B,T,H]` or
-    `[B,T,H,K]`; `reverse=True` gives suffix sums."""
+    `[B,T,H,K]`; `reverse=True` gives suffix sums.  With `cu_seqlens` (packed, B == 1) chunks restart at every
+    sequence start: one launch per sequence on its slice (the fused chunk ops do their own packed cumsum in one)."""
     assert g.ndim in (3, 4), f"g must be [B,T,H] or [B,T,H,K], got {tuple(g.shape)}"
     assert _is_pow2(chunk_size), f"chunk_size must be a power of 2, got {chunk_size}"
-    assert cu_seqlens is None, "packed cumsum is part of the fused chunk ops"
     g = g.contiguous()
+    if cu_seqlens is not None:
+        cu = [int(c) for c in cu_seqlens]
+        assert g.shape[0] == 1, f"cu_seqlens requires B=1, got B={g.shape[0]}"
+        assert cu[0] == 0 and cu[-1] == g.shape[1] and all(b > a for a, b in zip(cu[:-1], cu[1:])), \
+            f"cu_seqlens {cu} must rise from 0 to T={g.shape[1]}"
+        out = torch.empty(g.shape, dtype=torch.float32, device=g.device)
+        for a, b in zip(cu[:-1], cu[1:]):
+            out[:, a:b] = chunk_local_cumsum(g[:, a:b], chunk_size, reverse)
+        return out
     B, T, H = g.shape[:3]
     D = g.shape[3] if g.ndim == 4 else 1
     out = torch.empty(g.shape, dtype=torch.float32, device=g.device)

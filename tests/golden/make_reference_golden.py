@@ -52,6 +52,12 @@ CASES = {
     "ref_simple_gla_bf16_k128": dict(op="simple_gla", seed=319, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16",
                                      gate="g", slim=True),
     "ref_kda_bf16_k128": dict(op="kda", seed=320, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16", slim=True),
+    "ref_simple_gla_varlen_f64": dict(op="simple_gla", seed=321, B=1, T=64, H=2, K=16, V=16, C=16, dtype="float64",
+                                      gate="g", cu_seqlens=[0, 16, 37, 64]),
+    "ref_recurrent_varlen_f32": dict(op="recurrent", seed=322, B=1, T=33, H=2, K=16, V=16, dtype="float32",
+                                     reverse=False, cu_seqlens=[0, 1, 20, 33]),
+    "ref_cumsum_f32": dict(op="cumsum", seed=323, B=1, T=64, H=2, K=8, V=8, C=16, dtype="float32",
+                           cu_seqlens=[0, 5, 21, 64]),
     "ref_kda_gate_f32": dict(op="kda_gate", seed=316, B=2, T=48, H=4, K=16, V=16, C=16, dtype="float32"),
     "ref_kda_gate_bf16": dict(op="kda_gate", seed=317, B=1, T=32, H=2, K=32, V=32, C=16, dtype="bfloat16"),
 }
@@ -130,6 +136,15 @@ def run_case(c):
     j = {k: _to_standin(v) for k, v in x.items()}
     scale = c["K"] ** -0.5
     out = {}
+    if c["op"] == "cumsum":
+        from tops.cpu.ops.common.chunk_o import chunk_local_cumsum
+        cu = jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
+        gs = j["g"][..., 0]
+        out = dict(fwd4=chunk_local_cumsum(j["g"], c["C"]), rev4=chunk_local_cumsum(j["g"], c["C"], reverse=True),
+                   fwd3=chunk_local_cumsum(gs, c["C"]), rev3=chunk_local_cumsum(gs, c["C"], reverse=True),
+                   packed4=chunk_local_cumsum(j["g"], c["C"], cu_seqlens=cu),
+                   packed_rev3=chunk_local_cumsum(gs, c["C"], reverse=True, cu_seqlens=cu))
+        return {k: _to_torch(v) for k, v in out.items()}
     if c["op"] == "gla":
         from tops.cpu.ops.gla.chunk import chunk_gla, chunk_gla_bwd, chunk_gla_fwd
         from tops.cpu.ops.gla.naive import naive_recurrent_gla
@@ -147,20 +162,27 @@ def run_case(c):
                 out.update(o_naive=on, ht_naive=htn)
     elif c["op"] == "recurrent":
         from tops.cpu.ops.gla.fused_recurrent import fused_recurrent_bwd, fused_recurrent_fwd
-        o, ht = fused_recurrent_fwd(j["q"], j["k"], j["v"], j["g"], j["gv"], scale, j["h0"], True, c["reverse"])
+        cu = None if "cu_seqlens" not in c else np.asarray(c["cu_seqlens"], dtype=np.int64)
+        o, ht = fused_recurrent_fwd(j["q"], j["k"], j["v"], j["g"], j["gv"], scale, j["h0"], True, c["reverse"], cu)
         dq, dk, dv, dgk, dgv, dh0 = fused_recurrent_bwd(j["q"], j["k"], j["v"], j["g"], j["gv"], o, j["do"], j["dht"],
-                                                        scale, j["h0"], c["reverse"])
+                                                        scale, j["h0"], c["reverse"], cu)
         out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0)
     elif c["op"] == "simple_gla":
         from tops.cpu.ops.simple_gla.chunk import chunk_simple_gla, chunk_simple_gla_bwd
         from tops.cpu.ops.simple_gla.naive import naive_simple_gla
         g = j["g"] if c["gate"] == "g" else None
         gam = j["gamma"] if c["gate"] == "gamma" else None
-        o, ht = chunk_simple_gla(j["q"], j["k"], j["v"], g, gam, scale, j["h0"], True, chunk_size=c["C"])
+        cu = None if "cu_seqlens" not in c else jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
+        o, ht = chunk_simple_gla(j["q"], j["k"], j["v"], g, gam, scale, j["h0"], True, cu_seqlens=cu, chunk_size=c["C"])
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(j["q"], j["k"], j["v"], g, gam, j["h0"], j["do"], j["dht"], scale,
-                                                   chunk_size=c["C"])
+                                                   chunk_size=c["C"], cu_seqlens=cu)
         out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
-        if c["dtype"] not in ("bfloat16", "float16"):
+        if cu is None:
+            from tops.cpu.ops.simple_gla.fused_recurrent import fused_recurrent_simple_gla
+            orc, htr = fused_recurrent_simple_gla(j["q"], j["k"], j["v"], g=g, g_gamma=gam, scale=scale,
+                                                  initial_state=j["h0"], output_final_state=True)
+            out.update(o_recurrent=orc, ht_recurrent=htr)
+        if cu is None and c["dtype"] not in ("bfloat16", "float16"):
             on, htn = naive_simple_gla(j["q"], j["k"], j["v"], g=g, g_gamma=gam, scale=scale, initial_state=j["h0"],
                                        output_final_state=True)
             out.update(o_naive=on, ht_naive=htn)

@@ -68,21 +68,34 @@ def _run(c, x):
                 out.update(o_naive=on, ht_naive=htn)
         return out
     if c["op"] == "recurrent":
-        o, ht = G.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"])
+        cu = c.get("cu_seqlens")
+        o, ht = G.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"], cu)
         dq, dk, dv, dgk, dgv, dh0 = G.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], x["gv"], o, x["do"], x["dht"],
-                                                          scale, x["h0"], c["reverse"])
+                                                          scale, x["h0"], c["reverse"], cu)
         return dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0)
     if c["op"] == "simple_gla":
         g = x["g"] if c["gate"] == "g" else None
         gam = x["gamma"] if c["gate"] == "gamma" else None
-        o, ht = S.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, chunk_size=c["C"])
+        cu = c.get("cu_seqlens")
+        o, ht = S.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, cu_seqlens=cu, chunk_size=c["C"])
         dq, dk, dv, dg, dh0 = S.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], g, gam, x["h0"], x["do"], x["dht"], scale,
-                                                     chunk_size=c["C"])
+                                                     chunk_size=c["C"], cu_seqlens=cu)
         out = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
-        if c["dtype"] not in ("bfloat16", "float16"):
+        if cu is None:
+            # the recurrent form of the reference (fp32 state, output in q.dtype) against the oracle's token loop
+            orc, htr = S.naive_recurrent_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True)
+            out.update(o_recurrent=orc.to(x["q"].dtype), ht_recurrent=htr)
+        if cu is None and c["dtype"] not in ("bfloat16", "float16"):
             on, htn = S.naive_recurrent_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True)
             out.update(o_naive=on, ht_naive=htn)
         return out
+    if c["op"] == "cumsum":
+        from oracle.common import chunk_local_cumsum as cs
+        cu = c["cu_seqlens"]
+        gs = x["g"][..., 0]
+        return dict(fwd4=cs(x["g"], c["C"]), rev4=cs(x["g"], c["C"], reverse=True), fwd3=cs(gs, c["C"]),
+                    rev3=cs(gs, c["C"], reverse=True), packed4=cs(x["g"], c["C"], cu_seqlens=cu),
+                    packed_rev3=cs(gs, c["C"], reverse=True, cu_seqlens=cu))
     raise AssertionError(c["op"])
 
 

@@ -57,9 +57,10 @@ def test_recurrent_kernels_match_the_reference(name):
     host, dtype = _inputs(c)
     x = to_cuda(host)
     scale = c["K"] ** -0.5
-    o, ht = gla.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"])
+    cu = c.get("cu_seqlens")
+    o, ht = gla.fused_recurrent_fwd(x["q"], x["k"], x["v"], x["g"], x["gv"], scale, x["h0"], True, c["reverse"], cu)
     dq, dk, dv, dgk, dgv, dh0 = gla.fused_recurrent_bwd(x["q"], x["k"], x["v"], x["g"], x["gv"], o, x["do"], x["dht"],
-                                                        scale, x["h0"], c["reverse"])
+                                                        scale, x["h0"], c["reverse"], cu)
     _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dgk=dgk, dgv=dgv, dh0=dh0), dtype)
 
 
@@ -73,10 +74,32 @@ def test_simple_gla_kernels_match_the_reference(name):
     scale = c["K"] ** -0.5
     g = x["g"] if c["gate"] == "g" else None
     gam = x["gamma"] if c["gate"] == "gamma" else None
-    o, ht = simple_gla.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, chunk_size=c["C"])
+    cu = c.get("cu_seqlens")
+    o, ht = simple_gla.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, cu_seqlens=cu,
+                                        chunk_size=c["C"])
     dq, dk, dv, dg, dh0 = simple_gla.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], g, gam, x["h0"], x["do"], x["dht"],
-                                                          scale, chunk_size=c["C"])
-    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0), dtype)
+                                                          scale, chunk_size=c["C"], cu_seqlens=cu)
+    got = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+    if "o_recurrent" in ref:
+        orc, htr = simple_gla.fused_recurrent_simple_gla(x["q"], x["k"], x["v"], g=g, g_gamma=gam, scale=scale,
+                                                         initial_state=x["h0"], output_final_state=True)
+        got.update(o_recurrent=orc, ht_recurrent=htr)
+    _check(ref, got, dtype)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "cumsum"])
+def test_cumsum_kernel_matches_the_reference(name):
+    from tops_b200.ops.common import chunk_local_cumsum as cs
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    host, dtype = _inputs(c)
+    g = host["g"].cuda()
+    gs = g[..., 0].contiguous()
+    cu = c["cu_seqlens"]
+    got = dict(fwd4=cs(g, c["C"]), rev4=cs(g, c["C"], reverse=True), fwd3=cs(gs, c["C"]),
+               rev3=cs(gs, c["C"], reverse=True), packed4=cs(g, c["C"], cu_seqlens=cu),
+               packed_rev3=cs(gs, c["C"], reverse=True, cu_seqlens=cu))
+    _check(ref, got, dtype)
 
 
 @pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda"])
