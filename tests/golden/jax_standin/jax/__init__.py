@@ -18,7 +18,7 @@ import contextlib
 
 from . import _array
 from ._array import Array
-from . import numpy, lax, nn  # noqa: E402,F401
+from . import numpy, lax, nn, random  # noqa: E402,F401
 
 
 class _Config:

@@ -2,13 +2,12 @@
 
     python -m tests.golden.make_golden
 
-The reference (`tops.cpu`, pure jax.numpy) cannot be imported where this
-repository is built (no JAX), and it stores no golden arrays of its own, so
-the fixtures are outputs of the CPU oracle (`oracle/`, a restatement of
+These fixtures are outputs of the CPU oracle (`oracle/`, a restatement of
 `tops/cpu/ops/**`) on seeded inputs from `tops_b200.synth`.  They freeze the
 oracle: a later edit that changes its results fails
 tests/test_oracle_gla.py::test_golden_vectors_reproduce, and the GPU parity
-tests compare the kernels with the same files.
+tests compare the kernels with the same files.  Outputs of the reference's
+own code are the `ref_*.pt` files beside them (make_reference_golden.py).
 """
 import os
 import sys
