@@ -19,7 +19,10 @@ from .ops.gate import gla_gate
 from .ops.gla import chunk_gla, fused_chunk_gla, fused_recurrent_gla
 from .ops.norm import FusedRMSNormGated
 
-ACT2FN = {"swish": F.silu, "silu": F.silu, "gelu": F.gelu, "relu": F.relu, "sigmoid": torch.sigmoid, "tanh": torch.tanh}
+# "gelu" is the tanh approximation: the reference's table holds jax.nn.gelu, whose default is approximate=True
+# (tops/layers/gla.py:25-32)
+ACT2FN = {"swish": F.silu, "silu": F.silu, "gelu": lambda x: F.gelu(x, approximate="tanh"), "relu": F.relu,
+          "sigmoid": torch.sigmoid, "tanh": torch.tanh}
 
 
 class RMSNorm(nn.Module):

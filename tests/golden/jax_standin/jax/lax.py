@@ -71,3 +71,8 @@ def scan(f, init, xs=None, length=None, reverse=False, unroll=1):
 
 def stop_gradient(x):
     return x
+
+
+def rsqrt(x):
+    x = _np.asarray(x)
+    return wrap((1.0 / _np.sqrt(x)).astype(x.dtype))

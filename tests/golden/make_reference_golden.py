@@ -58,6 +58,16 @@ CASES = {
                                      reverse=False, cu_seqlens=[0, 1, 20, 33]),
     "ref_cumsum_f32": dict(op="cumsum", seed=323, B=1, T=64, H=2, K=8, V=8, C=16, dtype="float32",
                            cu_seqlens=[0, 5, 21, 64]),
+    # the GatedLinearAttention layer (tops/layers/gla.py) with its modules, fp32
+    "ref_layer_chunk": dict(op="layer", seed=401, B=2, T=96, hidden=64, heads=2, kw=dict(mode="chunk")),
+    "ref_layer_conv_gqa": dict(op="layer", seed=402, B=2, T=80, hidden=64, heads=2,
+                               kw=dict(mode="fused_chunk", num_kv_heads=1, use_short_conv=True, conv_bias=True)),
+    "ref_layer_plain_norm": dict(op="layer", seed=403, B=1, T=72, hidden=64, heads=2,
+                                 kw=dict(mode="chunk", fuse_norm=False, gate_fn="sigmoid", clamp_min=-0.04)),
+    "ref_layer_no_gate_short": dict(op="layer", seed=404, B=2, T=40, hidden=64, heads=4,
+                                    kw=dict(mode="chunk", use_output_gate=False)),
+    "ref_layer_gelu_relu": dict(op="layer", seed=405, B=1, T=72, hidden=64, heads=2,
+                                kw=dict(mode="chunk", gate_fn="gelu", feature_map="relu", elementwise_affine=False)),
     "ref_kda_gate_f32": dict(op="kda_gate", seed=316, B=2, T=48, H=4, K=16, V=16, C=16, dtype="float32"),
     "ref_kda_gate_bf16": dict(op="kda_gate", seed=317, B=1, T=32, H=2, K=32, V=32, C=16, dtype="bfloat16"),
 }
@@ -99,6 +109,48 @@ def case_inputs(c):
     return x
 
 
+def layer_inputs(c):
+    rng = np.random.Generator(np.random.PCG64(c["seed"]))
+    return torch.from_numpy(rng.standard_normal((c["B"], c["T"], c["hidden"]), dtype=np.float32))
+
+
+def _run_layer(c):
+    """The reference's layer source with its modules; its ops import (`tops.ops.gla`, the Pallas kernels) is
+    answered with the reference's CPU ops of the same names.  Returns the output and the parameters under the
+    names and layouts of `tops_b200.layers.GatedLinearAttention.state_dict()`."""
+    import jax.numpy as jnp
+    from flax import nnx
+    from tops.cpu.ops import gla as cpu_gla
+    mod = types.ModuleType("tops.ops.gla")
+    for name in ("chunk_gla", "fused_recurrent_gla", "fused_chunk_gla"):
+        setattr(mod, name, getattr(cpu_gla, name))
+    sys.modules["tops.ops.gla"] = mod
+    from tops.layers.gla import GatedLinearAttention
+    rngs = nnx.Rngs(c["seed"])
+    layer = GatedLinearAttention(hidden_size=c["hidden"], num_heads=c["heads"], rngs=rngs, **c["kw"])
+    norm = layer.g_norm_swish_gate if layer.fuse_norm_and_gate else layer.g_norm
+    if norm.weight is not None:
+        norm.weight.value = jnp.asarray(1.0 + 0.3 * np.asarray(rngs.normal((layer.head_v_dim,), 1.0)))
+    y, _, _ = layer(_to_standin(layer_inputs(c)))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(np.asarray(a, dtype=np.float32)))
+    w = {}
+    for name in ("q_proj", "k_proj", "v_proj", "g_proj", "o_proj"):
+        if hasattr(layer, name):
+            w[name + ".weight"] = t(np.asarray(getattr(layer, name).kernel.value).T)
+    w["gk_proj.0.weight"] = t(np.asarray(layer.gk_proj.layers[0].kernel.value).T)
+    w["gk_proj.1.weight"] = t(np.asarray(layer.gk_proj.layers[1].kernel.value).T)
+    w["gk_proj.1.bias"] = t(layer.gk_proj.layers[1].bias.value)
+    if layer.use_short_conv:
+        for name in ("q_conv1d", "k_conv1d", "v_conv1d"):
+            conv = getattr(layer, name).conv
+            w[name + ".conv.weight"] = t(np.asarray(conv.kernel.value).transpose(2, 1, 0))      # [W,1,D] -> [D,1,W]
+            if conv.bias is not None:
+                w[name + ".conv.bias"] = t(conv.bias.value)
+    if norm.weight is not None:
+        w[("g_norm_swish_gate" if layer.fuse_norm_and_gate else "g_norm") + ".weight"] = t(norm.weight.value)
+    return dict(y=_to_torch(y), weights=w)
+
+
 def _to_standin(t):
     import jax.numpy as jnp
     import ml_dtypes
@@ -121,7 +173,9 @@ def _to_torch(a):
 def run_case(c):
     import jax
     import jax.numpy as jnp
-    jax.config.update("jax_enable_x64", c["dtype"] == "float64")
+    jax.config.update("jax_enable_x64", c.get("dtype") == "float64")
+    if c["op"] == "layer":
+        return _run_layer(c)
     if c["op"] == "kda_gate":
         from tops.cpu.ops.kda.gate import fused_kda_gate, kda_gate_chunk_cumsum
         x = gate_inputs(c)
@@ -233,7 +287,8 @@ def main():
             continue
         out = run_case(c)
         torch.save(out, os.path.join(HERE, name + ".pt"))
-        print(name, {k: (tuple(v.shape), str(v.dtype).replace("torch.", "")) for k, v in out.items() if v is not None})
+        print(name, {k: (tuple(v.shape), str(v.dtype).replace("torch.", "")) for k, v in out.items()
+                     if isinstance(v, torch.Tensor)})
 
 
 if __name__ == "__main__":

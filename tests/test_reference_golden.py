@@ -15,7 +15,7 @@ from oracle import kda as K
 from oracle import simple_gla as S
 from oracle import aux as A
 from oracle.common import chunk_local_cumsum
-from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs
+from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs, layer_inputs
 
 HERE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -99,7 +99,7 @@ def _run(c, x):
     raise AssertionError(c["op"])
 
 
-@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] not in ("kda", "kda_gate")])
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] not in ("kda", "kda_gate", "layer")])
 def test_oracle_equals_the_reference_cpu_code(name):
     c = CASES[name]
     ref = _load(name)
@@ -154,3 +154,28 @@ def test_kda_gate_oracle_equals_the_reference_cpu_code(name):
                cumsum_log2=chunk_local_cumsum(biased, c["C"]) * 1.4426950408889634)
     assert set(got) == set(ref)
     _compare(name, got, ref, "float32")      # the gate is computed and returned in float32 for every input dtype
+
+
+def build_layer(c, ref):
+    """This package's layer with the parameters the reference's layer was run with."""
+    from tops_b200.layers import GatedLinearAttention
+    layer = GatedLinearAttention(hidden_size=c["hidden"], num_heads=c["heads"], **c["kw"])
+    missing = layer.load_state_dict(ref["weights"], strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    return layer
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "layer"])
+def test_layer_arithmetic_equals_the_reference_layer(name):
+    """The reference's `GatedLinearAttention` source (projections, short convolutions, grouped heads, gate law,
+    feature map, norm + output gate in both forms) against the same parameters pushed through this package's layer
+    wiring with the oracle's pieces: pins the oracle's gate / norm and the layer's wiring.  No kernel runs."""
+    c = CASES[name]
+    ref = _load(name)
+    layer = build_layer(c, ref)
+    x = layer_inputs(c)
+    mode = "fused_recurrent" if c["T"] <= 64 else c["kw"]["mode"]
+    with torch.no_grad():
+        from tests.layer_oracle import layer_on_cpu
+        y = layer_on_cpu(layer, x, mode)
+    _compare(name, dict(y=y), dict(y=ref["y"]), "float32")

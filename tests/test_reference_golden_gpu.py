@@ -135,3 +135,17 @@ def test_kda_gate_kernels_match_the_reference(name):
                cumsum_log2=gate.kda_gate_chunk_cumsum(x["g"], x["A_log"], c["C"], scale=1.4426950408889634,
                                                       dt_bias=x["dt_bias"]))
     _check(ref, got, torch.float32)
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "layer"])
+def test_layer_on_the_kernels_matches_the_reference_layer(name):
+    """`tops_b200.layers.GatedLinearAttention` on the GPU with the parameters the reference's layer was run with."""
+    from tests.golden.make_reference_golden import layer_inputs
+    from tests.test_reference_golden import build_layer
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    layer = build_layer(c, ref).cuda()
+    with torch.no_grad():
+        y, _, _ = layer(layer_inputs(c).cuda())
+    bar = 2e-4 * max(1.0, ref["y"].abs().max().item())
+    assert (y.cpu() - ref["y"]).abs().max().item() <= bar
