@@ -68,6 +68,10 @@ CASES = {
                                     kw=dict(mode="chunk", use_output_gate=False)),
     "ref_layer_gelu_relu": dict(op="layer", seed=405, B=1, T=72, hidden=64, heads=2,
                                 kw=dict(mode="chunk", gate_fn="gelu", feature_map="relu", elementwise_affine=False)),
+    # the pure-jax files of the accelerator-side package (tops/ops/**): public recurrent KDA, naive GLA with a
+    # `scale` argument, recurrent simple_gla with g + g_gamma together, forward and reversed
+    "ref_public_recurrent_f32": dict(op="public", seed=406, B=2, T=24, H=2, K=16, V=32, dtype="float32"),
+    "ref_public_recurrent_bf16": dict(op="public", seed=407, B=1, T=16, H=2, K=32, V=32, dtype="bfloat16"),
     "ref_kda_gate_f32": dict(op="kda_gate", seed=316, B=2, T=48, H=4, K=16, V=16, C=16, dtype="float32"),
     "ref_kda_gate_bf16": dict(op="kda_gate", seed=317, B=1, T=32, H=2, K=32, V=32, C=16, dtype="bfloat16"),
 }
@@ -121,7 +125,7 @@ def _run_layer(c):
     import jax.numpy as jnp
     from flax import nnx
     from tops.cpu.ops import gla as cpu_gla
-    mod = types.ModuleType("tops.ops.gla")
+    mod = sys.modules.get("tops.ops.gla") or types.ModuleType("tops.ops.gla")
     for name in ("chunk_gla", "fused_recurrent_gla", "fused_chunk_gla"):
         setattr(mod, name, getattr(cpu_gla, name))
     sys.modules["tops.ops.gla"] = mod
@@ -151,6 +155,44 @@ def _run_layer(c):
     return dict(y=_to_torch(y), weights=w)
 
 
+def public_inputs(c):
+    """GLA inputs + a scalar gate, a per-head constant decay and a KDA learning rate."""
+    x = case_inputs(dict(c, op="gla"))
+    rng = np.random.Generator(np.random.PCG64(c["seed"] + 2000))
+    dtype = getattr(torch, c["dtype"])
+    shape = (c["B"], c["T"], c["H"])
+    x["gs"] = torch.from_numpy(np.log(1.0 / (1.0 + np.exp(-rng.standard_normal(shape)))) / 4.0).to(torch.float32)
+    x["gamma"] = torch.from_numpy(-(0.02 + 0.1 * rng.random(c["H"]))).to(torch.float32)
+    x["beta"] = torch.from_numpy(1.0 / (1.0 + np.exp(-rng.standard_normal(shape)))).to(dtype)
+    kn = x["k"].float()
+    x["kn"] = (kn / kn.norm(dim=-1, keepdim=True)).to(dtype)
+    return x
+
+
+def _run_public(c):
+    import importlib
+    ref_ops = sys.modules["tops.ops"].__path__[0]
+    for sub in ("gla", "kda", "simple_gla"):      # package objects without their __init__ (Pallas imports)
+        m = sys.modules.get("tops.ops." + sub) or types.ModuleType("tops.ops." + sub)
+        m.__path__ = [os.path.join(ref_ops, sub)]
+        sys.modules["tops.ops." + sub] = m
+    x = public_inputs(c)
+    j = {k: _to_standin(v) for k, v in x.items()}
+    kda = importlib.import_module("tops.ops.kda.fused_recurrent").fused_recurrent_kda
+    naive = importlib.import_module("tops.ops.gla.naive").naive_recurrent_gla
+    sg = importlib.import_module("tops.ops.simple_gla.fused_recurrent").fused_recurrent_simple_gla
+    out = {}
+    out["kda_o"], out["kda_ht"] = kda(j["q"], j["kn"], j["v"], j["g"], j["beta"], scale=0.3, initial_state=j["h0"],
+                                      output_final_state=True)
+    out["gla_o"], out["gla_ht"] = naive(j["q"], j["k"], j["v"], j["g"], scale=0.3, initial_state=j["h0"],
+                                        output_final_state=True)
+    out["sg_o"], out["sg_ht"] = sg(j["q"], j["k"], j["v"], g=j["gs"], g_gamma=j["gamma"], scale=0.3,
+                                   initial_state=j["h0"], output_final_state=True)
+    out["sg_rev_o"], out["sg_rev_ht"] = sg(j["q"], j["k"], j["v"], g=j["gs"], scale=0.3, initial_state=j["h0"],
+                                           output_final_state=True, reverse=True)
+    return {k: _to_torch(v) for k, v in out.items()}
+
+
 def _to_standin(t):
     import jax.numpy as jnp
     import ml_dtypes
@@ -176,6 +218,8 @@ def run_case(c):
     jax.config.update("jax_enable_x64", c.get("dtype") == "float64")
     if c["op"] == "layer":
         return _run_layer(c)
+    if c["op"] == "public":
+        return _run_public(c)
     if c["op"] == "kda_gate":
         from tops.cpu.ops.kda.gate import fused_kda_gate, kda_gate_chunk_cumsum
         x = gate_inputs(c)

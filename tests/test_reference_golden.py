@@ -15,7 +15,7 @@ from oracle import kda as K
 from oracle import simple_gla as S
 from oracle import aux as A
 from oracle.common import chunk_local_cumsum
-from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs, layer_inputs
+from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs, layer_inputs, public_inputs
 
 HERE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -99,7 +99,7 @@ def _run(c, x):
     raise AssertionError(c["op"])
 
 
-@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] not in ("kda", "kda_gate", "layer")])
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] not in ("kda", "kda_gate", "layer", "public")])
 def test_oracle_equals_the_reference_cpu_code(name):
     c = CASES[name]
     ref = _load(name)
@@ -179,3 +179,37 @@ def test_layer_arithmetic_equals_the_reference_layer(name):
         from tests.layer_oracle import layer_on_cpu
         y = layer_on_cpu(layer, x, mode)
     _compare(name, dict(y=y), dict(y=ref["y"]), "float32")
+
+
+def public_on_oracle(x):
+    """The oracle's counterparts of the pure-jax entry points of the accelerator-side package."""
+    Kd = x["q"].shape[-1]
+    out = {}
+    out["kda_o"], out["kda_ht"] = K.fused_recurrent_kda(x["q"], x["kn"], x["v"], x["g"], x["beta"], 0.3, x["h0"], True)
+    out["gla_o"], out["gla_ht"] = G.fused_recurrent_gla(x["q"], x["k"], x["v"], gk=x["g"], scale=0.3,
+                                                        initial_state=x["h0"], output_final_state=True)
+    out["sg_o"], out["sg_ht"] = S.naive_recurrent_simple_gla(x["q"], x["k"], x["v"], x["gs"], x["gamma"], 0.3, x["h0"],
+                                                             True)
+    gk = x["gs"][..., None].expand(*x["gs"].shape, Kd).contiguous()
+    out["sg_rev_o"], out["sg_rev_ht"] = G.fused_recurrent_gla(x["q"], x["k"], x["v"], gk=gk, scale=0.3,
+                                                              initial_state=x["h0"], output_final_state=True,
+                                                              reverse=True)
+    return out
+
+
+def compare_public(name, got, ref, dtype):
+    """Values only: these reference functions carry no casts of their own, so their output dtypes follow
+    jax's promotion of whatever was passed in.  fp32: float32 rounding; bf16: the half-precision bar (the
+    reference multiplies k and v in bf16 there, the oracle and the kernels in fp32)."""
+    for key, r in ref.items():
+        a, b = got[key].double().cpu(), r.double()
+        if dtype == "float32":
+            assert (a - b).abs().max().item() <= 2e-5 * b.abs().max().item(), (name, key)
+        else:
+            assert ((a - b).norm() / b.norm()).item() <= 2e-2, (name, key, ((a - b).norm() / b.norm()).item())
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "public"])
+def test_oracle_equals_the_public_pure_jax_entry_points(name):
+    c = CASES[name]
+    compare_public(name, public_on_oracle(public_inputs(c)), _load(name), c["dtype"])

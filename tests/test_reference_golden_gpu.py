@@ -149,3 +149,26 @@ def test_layer_on_the_kernels_matches_the_reference_layer(name):
         y, _, _ = layer(layer_inputs(c).cuda())
     bar = 2e-4 * max(1.0, ref["y"].abs().max().item())
     assert (y.cpu() - ref["y"]).abs().max().item() <= bar
+
+
+@pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "public"])
+def test_public_recurrent_ops_match_the_reference(name):
+    """`fused_recurrent_kda`, recurrent GLA with an explicit scale, recurrent simple_gla with g + g_gamma and
+    reversed, against the pure-jax entry points of the reference's accelerator-side package."""
+    from tests.golden.make_reference_golden import public_inputs
+    from tests.test_reference_golden import compare_public
+    from tops_b200.ops import gla, kda, simple_gla
+    c = CASES[name]
+    ref = torch.load(os.path.join(GOLDEN, name + ".pt"))
+    x = to_cuda(public_inputs(c))
+    got = {}
+    got["kda_o"], got["kda_ht"] = kda.fused_recurrent_kda(x["q"], x["kn"], x["v"], x["g"], x["beta"], 0.3, x["h0"], True)
+    got["gla_o"], got["gla_ht"] = gla.fused_recurrent_gla(x["q"], x["k"], x["v"], gk=x["g"], scale=0.3,
+                                                          initial_state=x["h0"], output_final_state=True)
+    got["sg_o"], got["sg_ht"] = simple_gla.fused_recurrent_simple_gla(x["q"], x["k"], x["v"], g=x["gs"],
+                                                                      g_gamma=x["gamma"], scale=0.3,
+                                                                      initial_state=x["h0"], output_final_state=True)
+    got["sg_rev_o"], got["sg_rev_ht"] = simple_gla.fused_recurrent_simple_gla(x["q"], x["k"], x["v"], g=x["gs"],
+                                                                              scale=0.3, initial_state=x["h0"],
+                                                                              output_final_state=True, reverse=True)
+    compare_public(name, got, ref, "float32" if c["dtype"] == "float32" else "bfloat16")
