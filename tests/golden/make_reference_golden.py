@@ -242,6 +242,12 @@ def run_case(c):
                    fwd3=chunk_local_cumsum(gs, c["C"]), rev3=chunk_local_cumsum(gs, c["C"], reverse=True),
                    packed4=chunk_local_cumsum(j["g"], c["C"], cu_seqlens=cu),
                    packed_rev3=chunk_local_cumsum(gs, c["C"], reverse=True, cu_seqlens=cu))
+        from tops.cpu.ops.common.utils import gather_chunks, scatter_chunks
+        from tops.utils import prepare_chunk_indices
+        ci = prepare_chunk_indices(cu, c["C"])
+        chunks, valid = gather_chunks(j["g"], cu, ci, c["C"])
+        out.update(chunk_indices=ci, gathered=chunks, valid_lens=valid,
+                   scattered=scatter_chunks(jnp.zeros_like(j["g"]), chunks, cu, ci, c["C"], valid))
         return {k: _to_torch(v) for k, v in out.items()}
     if c["op"] == "gla":
         from tops.cpu.ops.gla.chunk import chunk_gla, chunk_gla_bwd, chunk_gla_fwd

@@ -93,9 +93,22 @@ def _run(c, x):
         from oracle.common import chunk_local_cumsum as cs
         cu = c["cu_seqlens"]
         gs = x["g"][..., 0]
-        return dict(fwd4=cs(x["g"], c["C"]), rev4=cs(x["g"], c["C"], reverse=True), fwd3=cs(gs, c["C"]),
-                    rev3=cs(gs, c["C"], reverse=True), packed4=cs(x["g"], c["C"], cu_seqlens=cu),
-                    packed_rev3=cs(gs, c["C"], reverse=True, cu_seqlens=cu))
+        out = dict(fwd4=cs(x["g"], c["C"]), rev4=cs(x["g"], c["C"], reverse=True), fwd3=cs(gs, c["C"]),
+                   rev3=cs(gs, c["C"], reverse=True), packed4=cs(x["g"], c["C"], cu_seqlens=cu),
+                   packed_rev3=cs(gs, c["C"], reverse=True, cu_seqlens=cu))
+        # the packed-batch helpers (tops/utils.py:71-90, tops/cpu/ops/common/utils.py:36-139): chunk table, chunks
+        # cut out of the packed tensor with zero tails, their valid lengths, and the way back
+        from oracle.common import prepare_chunk_indices
+        ci = prepare_chunk_indices(cu, c["C"])
+        rows, lens = [], []
+        for n, k in ci.tolist():
+            a = cu[n] + k * c["C"]
+            b = min(a + c["C"], cu[n + 1])
+            rows.append(torch.nn.functional.pad(x["g"][0, a:b], (0, 0, 0, 0, 0, c["C"] - (b - a))))
+            lens.append(b - a)
+        out.update(chunk_indices=ci, gathered=torch.stack(rows), valid_lens=torch.tensor(lens, dtype=torch.int32),
+                   scattered=x["g"].clone())
+        return out
     raise AssertionError(c["op"])
 
 
