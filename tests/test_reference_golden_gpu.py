@@ -22,12 +22,15 @@ def _inputs(c):
 
 
 def _check(ref, got, dtype):
+    """Every tensor inside the bar; the errors are printed (`pytest -s`) as max-abs for fp32, relative L2 for half."""
+    errs = {}
     for key, a in got.items():
         r = ref[key]
         if r is None:
             assert a is None, key
             continue
-        assert_close(key, a.float() if a.dtype != torch.float32 else a, r.float(), dtype)
+        errs[key] = assert_close(key, a.float() if a.dtype != torch.float32 else a, r.float(), dtype)
+    print({k: float(f"{v:.2e}") for k, v in errs.items()})
 
 
 @pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "gla"])
