@@ -47,6 +47,11 @@ CASES = {
     "ref_kda_f64": dict(op="kda", seed=310, B=1, T=64, H=2, K=32, V=16, C=16, dtype="float64"),   # V, K powers of two:
     # the staged backward slices blocks of min(next_power_of_2(V), 64) columns (tops/cpu/ops/kda/chunk_bwd.py:91-92)
     "ref_kda_f32": dict(op="kda", seed=311, B=2, T=64, H=2, K=32, V=32, C=32, dtype="float32"),
+    # no initial state, no final-state cotangent, ragged T: ht / dh0 must come back as None
+    "ref_gla_nostate_f32": dict(op="gla", seed=324, B=2, T=37, H=2, K=16, V=24, C=16, dtype="float32", state=False),
+    "ref_simple_gla_nostate_f32": dict(op="simple_gla", seed=325, B=1, T=37, H=3, K=16, V=16, C=16, dtype="float32",
+                                       gate="g", state=False),
+    "ref_kda_nostate_f32": dict(op="kda", seed=326, B=1, T=32, H=2, K=16, V=16, C=16, dtype="float32", state=False),
     # the shapes the tensor-core kernels take (bf16, K = V = 128, chunks of 64); outputs and gradients only
     "ref_gla_bf16_k128": dict(op="gla", seed=318, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16", slim=True),
     "ref_simple_gla_bf16_k128": dict(op="simple_gla", seed=319, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16",
@@ -110,6 +115,8 @@ def case_inputs(c):
         x["gamma"] = torch.from_numpy(-(0.02 + 0.1 * rng.random(c["H"]))).to(torch.float32)
     if dtype == torch.float64:
         x = {k: (v.to(torch.float64) if v.is_floating_point() else v) for k, v in x.items()}
+    if c.get("state") is False:
+        x["h0"] = x["dht"] = None
     return x
 
 
@@ -233,6 +240,7 @@ def run_case(c):
     x = case_inputs(c)
     j = {k: _to_standin(v) for k, v in x.items()}
     scale = c["K"] ** -0.5
+    fin = c.get("state") is not False        # ask for the final state
     out = {}
     if c["op"] == "cumsum":
         from tops.cpu.ops.common.chunk_o import chunk_local_cumsum
@@ -253,16 +261,16 @@ def run_case(c):
         from tops.cpu.ops.gla.chunk import chunk_gla, chunk_gla_bwd, chunk_gla_fwd
         from tops.cpu.ops.gla.naive import naive_recurrent_gla
         cu = None if "cu_seqlens" not in c else jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
-        o, ht = chunk_gla(j["q"], j["k"], j["v"], j["g"], scale=scale, initial_state=j["h0"], output_final_state=True,
+        o, ht = chunk_gla(j["q"], j["k"], j["v"], j["g"], scale=scale, initial_state=j["h0"], output_final_state=fin,
                           cu_seqlens=cu, chunk_size=c["C"])
         dq, dk, dv, dg, dh0 = chunk_gla_bwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], None, None, j["do"],
                                             j["dht"], chunk_size=c["C"], cu_seqlens=cu)
         out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
         if cu is None and not c.get("slim"):
-            gcum, A, h, _, _ = chunk_gla_fwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], True, chunk_size=c["C"])
+            gcum, A, h, _, _ = chunk_gla_fwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], fin, chunk_size=c["C"])
             out.update(g_cumsum=gcum, A=A, h=h)
             if c["dtype"] not in ("bfloat16", "float16"):
-                on, htn = naive_recurrent_gla(j["q"], j["k"], j["v"], j["g"], initial_state=j["h0"], output_final_state=True)
+                on, htn = naive_recurrent_gla(j["q"], j["k"], j["v"], j["g"], initial_state=j["h0"], output_final_state=fin)
                 out.update(o_naive=on, ht_naive=htn)
     elif c["op"] == "recurrent":
         from tops.cpu.ops.gla.fused_recurrent import fused_recurrent_bwd, fused_recurrent_fwd
@@ -277,27 +285,27 @@ def run_case(c):
         g = j["g"] if c["gate"] == "g" else None
         gam = j["gamma"] if c["gate"] == "gamma" else None
         cu = None if "cu_seqlens" not in c else jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
-        o, ht = chunk_simple_gla(j["q"], j["k"], j["v"], g, gam, scale, j["h0"], True, cu_seqlens=cu, chunk_size=c["C"])
+        o, ht = chunk_simple_gla(j["q"], j["k"], j["v"], g, gam, scale, j["h0"], fin, cu_seqlens=cu, chunk_size=c["C"])
         dq, dk, dv, dg, dh0 = chunk_simple_gla_bwd(j["q"], j["k"], j["v"], g, gam, j["h0"], j["do"], j["dht"], scale,
                                                    chunk_size=c["C"], cu_seqlens=cu)
         out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
         if cu is None:
             from tops.cpu.ops.simple_gla.fused_recurrent import fused_recurrent_simple_gla
             orc, htr = fused_recurrent_simple_gla(j["q"], j["k"], j["v"], g=g, g_gamma=gam, scale=scale,
-                                                  initial_state=j["h0"], output_final_state=True)
+                                                  initial_state=j["h0"], output_final_state=fin)
             out.update(o_recurrent=orc, ht_recurrent=htr)
         if cu is None and c["dtype"] not in ("bfloat16", "float16"):
             on, htn = naive_simple_gla(j["q"], j["k"], j["v"], g=g, g_gamma=gam, scale=scale, initial_state=j["h0"],
-                                       output_final_state=True)
+                                       output_final_state=fin)
             out.update(o_naive=on, ht_naive=htn)
     elif c["op"] == "kda":
         from tops.cpu.ops.kda.chunk_bwd import chunk_kda_bwd
         from tops.cpu.ops.kda.fused_recurrent import fused_recurrent_kda_bwd, fused_recurrent_kda_fwd
         from tops.cpu.ops.kda.naive import naive_chunk_kda, naive_recurrent_kda
-        o, ht = naive_recurrent_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], True)
-        oc, htc = naive_chunk_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], True, chunk_size=c["C"])
+        o, ht = naive_recurrent_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], fin)
+        oc, htc = naive_chunk_kda(j["q"], j["k"], j["v"], j["g"], j["beta"], scale, j["h0"], fin, chunk_size=c["C"])
         of, htf = fused_recurrent_kda_fwd(j["q"], j["k"], j["v"], j["g"], j["beta"], initial_state=j["h0"], scale=scale,
-                                          output_final_state=True)
+                                          output_final_state=fin, inplace_final_state=fin)
         dq, dk, dv, dg, db, dh0 = fused_recurrent_kda_bwd(j["q"], j["k"], j["v"], j["g"], j["beta"], j["do"],
                                                           initial_state=j["h0"], dht=j["dht"], scale=scale)
         out.update(o=o, ht=ht, o_chunk=oc, ht_chunk=htc, o_fused=of, ht_fused=htf, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db,

@@ -42,13 +42,19 @@ def test_gla_kernels_match_the_reference(name):
     x = to_cuda(host)
     scale = c["K"] ** -0.5
     cu = c.get("cu_seqlens")
-    o, ht = gla.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale=scale, initial_state=x["h0"], output_final_state=True,
+    fin = c.get("state") is not False
+    o, ht = gla.chunk_gla(x["q"], x["k"], x["v"], x["g"], scale=scale, initial_state=x["h0"], output_final_state=fin,
                           cu_seqlens=cu, chunk_size=c["C"])
     dq, dk, dv, dg, dh0 = gla.chunk_gla_bwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], None, None, x["do"],
                                             x["dht"], chunk_size=c["C"], cu_seqlens=cu)
-    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0), dtype)
+    got = dict(o=o, dq=dq, dk=dk, dv=dv, dg=dg)
+    if fin:
+        got.update(ht=ht, dh0=dh0)
+    else:
+        assert ht is None and dh0 is None
+    _check(ref, got, dtype)
     if "A" in ref:        # the per-chunk tensors of the forward orchestrator
-        gcum, A, h, _, _ = gla.chunk_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], True, chunk_size=c["C"])
+        gcum, A, h, _, _ = gla.chunk_gla_fwd(x["q"], x["k"], x["v"], x["g"], None, scale, x["h0"], fin, chunk_size=c["C"])
         _check(ref, dict(g_cumsum=gcum, A=A, h=h), dtype)
 
 
@@ -78,15 +84,20 @@ def test_simple_gla_kernels_match_the_reference(name):
     g = x["g"] if c["gate"] == "g" else None
     gam = x["gamma"] if c["gate"] == "gamma" else None
     cu = c.get("cu_seqlens")
-    o, ht = simple_gla.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], True, cu_seqlens=cu,
+    fin = c.get("state") is not False
+    o, ht = simple_gla.chunk_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], fin, cu_seqlens=cu,
                                         chunk_size=c["C"])
     dq, dk, dv, dg, dh0 = simple_gla.chunk_simple_gla_bwd(x["q"], x["k"], x["v"], g, gam, x["h0"], x["do"], x["dht"],
                                                           scale, chunk_size=c["C"], cu_seqlens=cu)
-    got = dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+    got = dict(o=o, dq=dq, dk=dk, dv=dv, dg=dg)
+    if fin:
+        got.update(ht=ht, dh0=dh0)
+    else:
+        assert ht is None and dh0 is None
     if "o_recurrent" in ref:
         orc, htr = simple_gla.fused_recurrent_simple_gla(x["q"], x["k"], x["v"], g=g, g_gamma=gam, scale=scale,
-                                                         initial_state=x["h0"], output_final_state=True)
-        got.update(o_recurrent=orc, ht_recurrent=htr)
+                                                         initial_state=x["h0"], output_final_state=fin)
+        got.update(o_recurrent=orc, **({"ht_recurrent": htr} if fin else {}))
     _check(ref, got, dtype)
 
 
@@ -115,15 +126,21 @@ def test_kda_kernels_match_the_reference(name):
     host, dtype = _inputs(c)
     x = to_cuda(host)
     scale = c["K"] ** -0.5
+    fin = c.get("state") is not False
     if c["K"] == 128:
         assert kda.chunk_kernels_take(x["q"], x["k"], x["v"], x["g"], x["beta"], 64)
         o, ht, _, _, _ = kda.chunk_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
         dq, dk, dv, db, dg, dh0 = kda.chunk_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"],
                                                     x["dht"])
     else:
-        o, ht = kda.kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], True)
+        o, ht = kda.kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], scale, x["h0"], fin)
         dq, dk, dv, dg, db, dh0 = kda.kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], scale, x["h0"], x["dht"])
-    _check(ref, dict(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db, dh0=dh0), dtype)
+    got = dict(o=o, dq=dq, dk=dk, dv=dv, dg=dg, dbeta=db)
+    if fin:
+        got.update(ht=ht, dh0=dh0)
+    else:
+        assert ht is None and dh0 is None
+    _check(ref, got, dtype)
 
 
 @pytest.mark.parametrize("name", [n for n, c in CASES.items() if c["op"] == "kda_gate"])
