@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
                     [--scaling strong|weak] [--grads primal|fp32]
-                    [--workload gla_train|decode|simple_gla_long|kda|kda_long]
+                    [--workload gla_train|decode|simple_gla_long|kda|kda_long|neighbours]
 
 One "step" is one forward + backward pass of `chunk_gla` over one synthetic
 batch of the headline configuration (bf16, B=8, T=4096, H=16, K=V=128,
@@ -687,6 +687,32 @@ def secondary(name, steps, seq):
         out = {"metric": "KDA chunk fwd+bwd tokens/s", "value": B * T / (ms * 1e-3), "unit": "tokens/s",
                "config": {"workload": f"KDA fwd+bwd B={B} T={T} H=32 K=V=128 chunk 64 bf16, one GPU"
                                       + (" (BASELINE configs[4])" if name == "kda" else "")}}
+    elif name == "neighbours":
+        # the elementwise steps either side of the path, each forward + backward through its public op, at the
+        # tensor sizes of BASELINE configs[1]: one [8, 4096, 16, 128] bf16 tensor is 134 MB
+        from tops_b200.ops.gate import gla_gate, kda_gate_fwd
+        from tops_b200.ops.norm import l2norm, rmsnorm_gated
+        B, T, H, D = 8, seq or 4096, 16, 128
+        gen = torch.Generator(device="cuda").manual_seed(6)
+        mk = lambda *shape, dt=torch.bfloat16: torch.randn(*shape, device="cuda", generator=gen).to(dt).requires_grad_(True)
+        x, g, dy = mk(B, T, H, D), mk(B, T, H, D), mk(B, T, H, D)
+        w, A_log, bias = mk(D, dt=torch.float32), mk(H, dt=torch.float32), mk(H * D, dt=torch.float32)
+        dy32 = dy.detach().float()
+
+        def step():
+            torch.autograd.grad(gla_gate(g), g, dy.detach())
+            torch.autograd.grad(kda_gate_fwd(g, A_log, bias), (g, A_log, bias), dy32)
+            torch.autograd.grad(l2norm(x), x, dy.detach())
+            torch.autograd.grad(rmsnorm_gated(x, g, w), (x, g, w), dy.detach())
+        ms = timed(step, max(3, min(steps, 10)), 3)
+        n = B * T * H * D
+        # gla gate 2+2 / 2+2+2; kda gate (fp32 out) 2+4 / 2+4+2; l2norm 2+2 / 2+2+2; norm+gate 2+2+2 / 2+2+2+2+2
+        per_label = {"gate_act_fwd": (4 + 6) * n / 2, "gate_act_bwd": (6 + 8) * n / 2, "l2norm_fwd": 4 * n,
+                     "l2norm_bwd": 6 * n, "rmsnorm_gated_fwd": 6 * n, "rmsnorm_gated_bwd": 10 * n}
+        nbytes = int(sum(2 * v if k.startswith("gate_act") else v for k, v in per_label.items()))
+        out = {"metric": "gate / l2norm / norm+gate forward + backward, GB/s per kernel", "value": nbytes / (ms * 1e-3) / 1e9,
+               "unit": "GB/s", "bytes_per_launch": per_label,
+               "config": {"workload": f"gla_gate, kda_gate, l2norm, rmsnorm_gated fwd+bwd on [8,{T},16,128] bf16, one GPU"}}
     else:
         raise ValueError(name)
     L.lib.tops_b200_profile_enable(0)
@@ -694,6 +720,9 @@ def secondary(name, steps, seq):
     L.lib.tops_b200_profile_read(buf, len(buf))
     out["kernels_ms_per_launch"] = {ln.split()[0]: float(ln.split()[2]) / int(ln.split()[1])
                                     for ln in buf.value.decode().splitlines()}
+    if "bytes_per_launch" in out:
+        out["kernels_gbs"] = {k: out["bytes_per_launch"][k] / (v * 1e-3) / 1e9
+                              for k, v in out["kernels_ms_per_launch"].items() if k in out["bytes_per_launch"]}
     out["ms_per_step"] = ms
     out["algorithmic_bytes"] = nbytes
     out["frac"] = nbytes / (ms * 1e-3) / 1e9 / hbm_peak
@@ -829,7 +858,7 @@ def main():
                     help="dtype of dq, dk, dg in the timed step: the primal dtypes (bf16) or fp32")
     ap.add_argument("--batch", type=int, default=0, help="override B (profiler captures on a smaller case)")
     ap.add_argument("--kernel-only", action="store_true", help="device-resident timed steps only, short JSON")
-    ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda", "kda_long"],
+    ap.add_argument("--workload", default="gla_train", choices=["gla_train", "decode", "simple_gla_long", "kda", "kda_long", "neighbours"],
                     help="gla_train is the headline metric; the others are secondary one-GPU measurements")
     ap.add_argument("--seq", type=int, default=0, help="override T of a secondary workload")
     args = ap.parse_args()

@@ -130,23 +130,45 @@ __global__ void k_gate_bwd(const TI* __restrict__ g, const TD* __restrict__ dy, 
   if (part_A) Vec4<float>::store(part_A + (size_t)blockIdx.y * HK + col, sa);
 }
 
-// out[col] = sum over row blocks of part[blk][col] (fixed order)
-__global__ void k_sum_blocks(const float* __restrict__ part, int nblk, int ncol, float* __restrict__ out) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= ncol) return;
+// out[col] = sum over row blocks of part[blk][col]: 32 columns x 32 row lanes per block, every lane walks its
+// rows in order and the 32 lane sums are added in order, so the result does not depend on scheduling
+__global__ void __launch_bounds__(1024) k_sum_blocks(const float* __restrict__ part, int nblk, int ncol,
+                                                     float* __restrict__ out) {
+  __shared__ float sm[32][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int b = 0; b < nblk; ++b) s += part[(size_t)b * ncol + col];
-  out[col] = s;
+  if (col < ncol)
+    for (int b = ry; b < nblk; b += 32) s += part[(size_t)b * ncol + col];
+  sm[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < ncol) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) t += sm[r][cx];
+    out[col] = t;
+  }
 }
-// dA[h] = sum over row blocks and the K columns of head h; one warp per head
-__global__ void k_sum_heads(const float* __restrict__ part, int nblk, int H, int K, float* __restrict__ out) {
-  const int h = blockIdx.x, lane = threadIdx.x;
+// dA[h] = sum over row blocks and the K columns of head h; one block of 32 warps per head, warp w takes the
+// row blocks w, w + 32, ...
+__global__ void __launch_bounds__(1024) k_sum_heads(const float* __restrict__ part, int nblk, int H, int K,
+                                                    float* __restrict__ out) {
+  __shared__ float sm[32];
+  const int h = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   float s = 0.f;
-  for (int b = 0; b < nblk; ++b)
+  for (int b = w; b < nblk; b += 32)
     for (int k = lane; k < K; k += 32) s += part[((size_t)b * H + h) * K + k];
   s = warp_sum(s);
-  if (lane == 0) out[h] = s;
+  if (lane == 0) sm[w] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += sm[i];
+    out[h] = t;
+  }
 }
+
 
 // ---------------------------------------------------------------------------
 // L2 normalisation over the last dimension (D <= 1024, D % 4 == 0): one warp per row
@@ -406,13 +428,13 @@ int gate_bwd(const tops_gate_act_bwd_params& p, void* ws, cudaStream_t st) {
   }
   if (part_bias) {
     KernelScope ks("gate_act_bwd_sum", st);
-    k_sum_blocks<<<(HK + 255) / 256, 256, 0, st>>>(part_bias, nblk, HK, p.dbias);
+    k_sum_blocks<<<(HK + 31) / 32, 1024, 0, st>>>(part_bias, nblk, HK, p.dbias);
     int rc = post_launch();
     if (rc) return rc;
   }
   if (part_A) {
     KernelScope ks("gate_act_bwd_sum", st);
-    k_sum_heads<<<f.H, 32, 0, st>>>(part_A, nblk, f.H, f.K, p.dA_log);
+    k_sum_heads<<<f.H, 1024, 0, st>>>(part_A, nblk, f.H, f.K, p.dA_log);
     return post_launch();
   }
   return TOPS_OK;
@@ -488,7 +510,7 @@ int rmsnorm_gated_bwd(const tops_norm_params& p, void* ws, cudaStream_t st) {
   }
   if (part) {
     KernelScope ks("rmsnorm_gated_bwd_sum", st);
-    k_sum_blocks<<<(p.D + 255) / 256, 256, 0, st>>>(part, (int)warps, p.D, p.dweight);
+    k_sum_blocks<<<(p.D + 31) / 32, 1024, 0, st>>>(part, (int)warps, p.D, p.dweight);
     return post_launch();
   }
   return TOPS_OK;
