@@ -52,6 +52,10 @@ CASES = {
     "ref_simple_gla_nostate_f32": dict(op="simple_gla", seed=325, B=1, T=37, H=3, K=16, V=16, C=16, dtype="float32",
                                        gate="g", state=False),
     "ref_kda_nostate_f32": dict(op="kda", seed=326, B=1, T=32, H=2, K=16, V=16, C=16, dtype="float32", state=False),
+    # the public wrappers with every default (g = None -> zeros, scale = None -> K^-0.5, chunk_size 16, no
+    # states), the fused_chunk alias, the recurrent wrapper's cast of o to q.dtype (compared with the oracle only)
+    "ref_gla_defaults_bf16": dict(op="defaults", seed=327, B=2, T=40, H=2, K=32, V=16, dtype="bfloat16", cpu_only=True),
+    "ref_gla_defaults_f32": dict(op="defaults", seed=328, B=1, T=33, H=3, K=16, V=24, dtype="float32", cpu_only=True),
     # the shapes the tensor-core kernels take (bf16, K = V = 128, chunks of 64); outputs and gradients only
     "ref_gla_bf16_k128": dict(op="gla", seed=318, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16", slim=True),
     "ref_simple_gla_bf16_k128": dict(op="simple_gla", seed=319, B=1, T=128, H=1, K=128, V=128, C=64, dtype="bfloat16",
@@ -242,6 +246,16 @@ def run_case(c):
     scale = c["K"] ** -0.5
     fin = c.get("state") is not False        # ask for the final state
     out = {}
+    if c["op"] == "defaults":
+        from tops.cpu.ops.gla import chunk_gla, fused_chunk_gla, fused_recurrent_gla
+        out["o_nogate"], none1 = chunk_gla(j["q"], j["k"], j["v"])
+        out["o_chunk"], none2 = chunk_gla(j["q"], j["k"], j["v"], j["g"])
+        out["o_fused"], out["ht_fused"] = fused_chunk_gla(j["q"], j["k"], j["v"], j["g"], output_final_state=True)
+        out["o_rec"], out["ht_rec"] = fused_recurrent_gla(j["q"], j["k"], j["v"], j["g"], initial_state=j["h0"],
+                                                          output_final_state=True)
+        out["o_rec_nogate"], none3 = fused_recurrent_gla(j["q"], j["k"], j["v"])
+        assert none1 is None and none2 is None and none3 is None
+        return {k: _to_torch(v) for k, v in out.items()}
     if c["op"] == "cumsum":
         from tops.cpu.ops.common.chunk_o import chunk_local_cumsum
         cu = jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))

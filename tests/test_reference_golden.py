@@ -90,6 +90,16 @@ def _run(c, x):
             on, htn = S.naive_recurrent_simple_gla(x["q"], x["k"], x["v"], g, gam, scale, x["h0"], fin)
             out.update(o_naive=on, ht_naive=htn)
         return out
+    if c["op"] == "defaults":
+        out = {}
+        out["o_nogate"], none1 = G.chunk_gla(x["q"], x["k"], x["v"])
+        out["o_chunk"], none2 = G.chunk_gla(x["q"], x["k"], x["v"], x["g"])
+        out["o_fused"], out["ht_fused"] = G.fused_chunk_gla(x["q"], x["k"], x["v"], x["g"], output_final_state=True)
+        out["o_rec"], out["ht_rec"] = G.fused_recurrent_gla(x["q"], x["k"], x["v"], x["g"], initial_state=x["h0"],
+                                                            output_final_state=True)
+        out["o_rec_nogate"], none3 = G.fused_recurrent_gla(x["q"], x["k"], x["v"])
+        assert none1 is None and none2 is None and none3 is None
+        return out
     if c["op"] == "cumsum":
         from oracle.common import chunk_local_cumsum as cs
         cu = c["cu_seqlens"]

@@ -7,10 +7,11 @@ import os
 import pytest
 import torch
 
-from tests.golden.make_reference_golden import CASES, case_inputs, gate_inputs
+from tests.golden.make_reference_golden import CASES as ALL_CASES, case_inputs, gate_inputs
 from tests.util import assert_close, to_cuda
 
 pytestmark = pytest.mark.gpu
+CASES = {n: c for n, c in ALL_CASES.items() if not c.get("cpu_only")}
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
