@@ -336,6 +336,13 @@ def run_case(c):
                            j["dht"], g=_to_standin(g2), chunk_size=c["C"])
         out.update(g2=_to_standin(g2), Aqk=_to_standin(Aqk), Akk=_to_standin(Akk), st_dq=st[0], st_dk=st[1], st_dv=st[2],
                    st_dbeta=st[3], st_dg=st[4], st_dh0=st[5])
+        # the forward stages behind that backward: WY vectors and the delta-rule state scan
+        from tops.cpu.ops.common.chunk_delta_h import chunk_gated_delta_rule_fwd_h
+        from tops.cpu.ops.kda.wy_fast import recompute_w_u_fwd
+        w, u, qg, kg = recompute_w_u_fwd(j["k"], j["v"], j["beta"], _to_standin(Akk), q=j["q"], gk=_to_standin(g2))
+        h, v_new, ht_scan = chunk_gated_delta_rule_fwd_h(kg, w, u, gk=_to_standin(g2), initial_state=j["h0"],
+                                                         output_final_state=fin, chunk_size=c["C"], use_exp2=True)
+        out.update(fw_w=w, fw_u=u, fw_qg=qg, fw_kg=kg, fw_h=h, fw_v_new=v_new, fw_ht=ht_scan)
         if c.get("slim"):
             out = {k: v for k, v in out.items() if k in ("o", "ht", "dq", "dk", "dv", "dg", "dbeta", "dh0", "st_dq",
                                                          "st_dk", "st_dg", "st_dbeta")}

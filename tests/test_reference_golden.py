@@ -165,6 +165,13 @@ def test_kda_oracle_equals_the_reference_cpu_code(name):
         err = (a.double() - r.double()).abs().max().item()
         top = r.double().abs().max().item()
         assert err <= 2e-5 * top, (name, n, err, top)
+    # the forward stages behind it (WY vectors, delta-rule state scan)
+    if "fw_w" in ref:
+        w, u, qg, kg = K.recompute_w_u_fwd(x["k"], x["v"], x["beta"], Akk, q=x["q"], gk=g2)
+        h, v_new, ht_scan = K.chunk_gated_delta_rule_fwd_h(kg, w, u, gk=g2, initial_state=x["h0"],
+                                                          output_final_state=fin, chunk_size=c["C"])
+        _compare(name, dict(fw_w=w, fw_u=u, fw_qg=qg, fw_kg=kg, fw_h=h, fw_v_new=v_new, fw_ht=ht_scan),
+                 {k: v for k, v in ref.items() if k.startswith("fw_")}, c["dtype"] if c["dtype"] != "float64" else "float32")
     # and the stored matrices (what the generator fed the reference's staged backward) are these
     if "Aqk" in ref:
         assert torch.equal(Aqk, ref["Aqk"]) and torch.equal(Akk, ref["Akk"]) and torch.equal(g2, ref["g2"])
