@@ -52,6 +52,10 @@ CASES = {
     "ref_simple_gla_nostate_f32": dict(op="simple_gla", seed=325, B=1, T=37, H=3, K=16, V=16, C=16, dtype="float32",
                                        gate="g", state=False),
     "ref_kda_nostate_f32": dict(op="kda", seed=326, B=1, T=32, H=2, K=16, V=16, C=16, dtype="float32", state=False),
+    # BASELINE configs[0], the reference's own CPU-runnable case, on the inputs the benchmark and the tests draw for
+    # it (seed 1): forward only, fp32, no initial state, o and the final state
+    "ref_gla_config0_f32": dict(op="gla", seed=1, B=2, T=512, H=4, K=64, V=64, C=64, dtype="float32", gate_norm=16.0,
+                                h0=False, fwd_only=True, slim=True),
     # the public wrappers with every default (g = None -> zeros, scale = None -> K^-0.5, chunk_size 16, no
     # states), the fused_chunk alias, the recurrent wrapper's cast of o to q.dtype (compared with the oracle only)
     "ref_gla_defaults_bf16": dict(op="defaults", seed=327, B=2, T=40, H=2, K=32, V=16, dtype="bfloat16", cpu_only=True),
@@ -104,7 +108,7 @@ def case_inputs(c):
     kda = c["op"] == "kda"
     gate = "scalar" if c["op"] == "simple_gla" else "per_channel"
     x = make_inputs(c["seed"], c["B"], c["T"], c["H"], c["K"], c["V"], dtype=dtype, gate=gate, with_h0=True,
-                    with_grads=True, with_beta=kda, l2norm_qk=kda, gate_norm=4.0,
+                    with_grads=True, with_beta=kda, l2norm_qk=kda, gate_norm=c.get("gate_norm", 4.0),
                     gate_dtype=torch.float32 if (gate == "scalar" and dtype != torch.float64) else None)
     rng = np.random.Generator(np.random.PCG64(c["seed"] + 1000))
     if "cu_seqlens" in c:        # one state per packed sequence
@@ -121,6 +125,8 @@ def case_inputs(c):
         x = {k: (v.to(torch.float64) if v.is_floating_point() else v) for k, v in x.items()}
     if c.get("state") is False:
         x["h0"] = x["dht"] = None
+    if c.get("h0") is False:
+        x["h0"] = None
     return x
 
 
@@ -277,9 +283,11 @@ def run_case(c):
         cu = None if "cu_seqlens" not in c else jnp.asarray(np.asarray(c["cu_seqlens"], dtype=np.int32))
         o, ht = chunk_gla(j["q"], j["k"], j["v"], j["g"], scale=scale, initial_state=j["h0"], output_final_state=fin,
                           cu_seqlens=cu, chunk_size=c["C"])
-        dq, dk, dv, dg, dh0 = chunk_gla_bwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], None, None, j["do"],
-                                            j["dht"], chunk_size=c["C"], cu_seqlens=cu)
-        out.update(o=o, ht=ht, dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
+        out.update(o=o, ht=ht)
+        if not c.get("fwd_only"):
+            dq, dk, dv, dg, dh0 = chunk_gla_bwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], None, None, j["do"],
+                                                j["dht"], chunk_size=c["C"], cu_seqlens=cu)
+            out.update(dq=dq, dk=dk, dv=dv, dg=dg, dh0=dh0)
         if cu is None and not c.get("slim"):
             gcum, A, h, _, _ = chunk_gla_fwd(j["q"], j["k"], j["v"], j["g"], None, scale, j["h0"], fin, chunk_size=c["C"])
             out.update(g_cumsum=gcum, A=A, h=h)

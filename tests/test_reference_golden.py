@@ -128,6 +128,8 @@ def test_oracle_equals_the_reference_cpu_code(name):
     c = CASES[name]
     ref = _load(name)
     got = _run(c, case_inputs(c))
+    if c.get("fwd_only"):
+        got = {k: v for k, v in got.items() if k in ("o", "ht")}
     assert set(got) == set(ref), (sorted(got), sorted(ref))
     _compare(name, got, ref, c["dtype"])
 
